@@ -1,0 +1,148 @@
+"""The engine: a loaded model, its cache, and the one step function.
+
+`Engine.step` runs a batch of sequences: each entry brings the next tokens of one
+sequence (a whole prompt, a part of it, or one decoded token) and names the places
+among them whose logits are wanted.  The step runs exactly the tokens it is given,
+as one batch, on top of what earlier steps left in the cache, and returns the
+float32 logits of the wanted places.  Padding changes no result: kernels see the
+packed tokens and each sequence's own length.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache import PagedCache
+from ..config.registry import load_config
+from ..kernels import build as kernel_build
+from ..parts.base import StepContext
+from ..weights.loader import load_checkpoint
+from .model import DecoderModel
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: list
+    want: list = field(default_factory=list)  # indices into `tokens`
+
+
+def require_gpu(device) -> torch.device:
+    if not torch.cuda.is_available():
+        raise EngineError("hymt2sharp_b200 needs a CUDA device (sm_100a); none is visible, and there is no CPU path")
+    device = torch.device(device)
+    major, minor = torch.cuda.get_device_capability(device)
+    if major != 10:
+        raise EngineError(f"the kernels are built for sm_100a; device {device} is sm_{major}{minor}")
+    return device
+
+
+class Engine:
+    def __init__(self, model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_batch: int = 8,
+                 block_tokens: int = 64, device="cuda:0", max_sequence_tokens: int | None = None,
+                 spec_override=None):
+        if dtype not in DTYPES:
+            raise EngineError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
+        self.dtype = DTYPES[dtype]
+        self.device = require_gpu(device)
+        kernel_build.load_library()  # fails loudly when the CUDA library cannot be built or loaded
+        self.architecture, self.config = load_config(model_dir)
+        spec = self.architecture.build_spec(self.config) if spec_override is None else spec_override(self.config)
+        self.model = DecoderModel(spec)
+        weights = load_checkpoint(model_dir, self.model.tensors())
+        with torch.cuda.device(self.device):
+            self.model.load(weights, self.device, self.dtype)
+            self.cache = PagedCache(self.model.groups, self.dtype, self.device, capacity_tokens=max_tokens,
+                                    block_tokens=block_tokens, max_slots=max_batch,
+                                    state_bytes=self.model.state_bytes, max_sequence_tokens=max_sequence_tokens)
+            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            self._meta = torch.zeros(4096, dtype=torch.int32, device=self.device)
+        self.vocab = spec.vocab
+        self.steps_run = 0
+
+    # -- slots ------------------------------------------------------------------
+    def alloc_slots(self, n: int) -> list[int]:
+        with torch.cuda.device(self.device):
+            return self.cache.alloc_slots(n)
+
+    def free_slots(self, slots) -> None:
+        self.cache.free_slots(list(slots))
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # -- the step ---------------------------------------------------------------
+    def _upload_meta(self, parts: list[np.ndarray]) -> list[torch.Tensor]:
+        sizes = [len(p) for p in parts]
+        total = sum(sizes)
+        if total > self._meta.numel():
+            self._meta = torch.zeros(max(total, 2 * self._meta.numel()), dtype=torch.int32, device=self.device)
+        host = np.concatenate(parts).astype(np.int32, copy=False) if total else np.zeros(0, np.int32)
+        self._meta[:total].copy_(torch.from_numpy(host))
+        views, o = [], 0
+        for n in sizes:
+            views.append(self._meta[o:o + n])
+            o += n
+        return views
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Runs one step; returns float32 logits [wanted places, vocab] on the device, in the
+        order of the entries and of each entry's `want`."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
+        tokens, token_seq, token_pos, cu, slots, kv_lens, want = [], [], [], [0], [], [], []
+        starts, news = [], []
+        for b, e in enumerate(entries):
+            n = len(e.tokens)
+            start = self.cache.length(e.slot)
+            for t in e.tokens:
+                if not (0 <= int(t) < self.vocab):
+                    raise EngineError(f"token id {t} is outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise EngineError(f"wanted place {w} is outside the {n} tokens of the entry")
+                want.append(cu[-1] + int(w))
+            tokens.extend(int(t) for t in e.tokens)
+            token_seq.extend([b] * n)
+            token_pos.extend(range(start, start + n))
+            cu.append(cu[-1] + n)
+            slots.append(e.slot)
+            kv_lens.append(start + n)
+            starts.append(start)
+            news.append(n)
+        plan = list(zip(slots, news))
+        with torch.cuda.device(self.device):
+            self.cache.begin_step(plan)  # raises CacheFull before anything changed
+            arrays = [np.asarray(a, dtype=np.int32) for a in (tokens, token_seq, token_pos, cu, slots, kv_lens, want)]
+            v = self._upload_meta(arrays)
+            ctx = StepContext(device=self.device, dtype=self.dtype, num_tokens=len(tokens), num_seqs=len(entries),
+                              tokens=v[0], token_seq=v[1], token_pos=v[2], cu_seqlens=v[3], slot_ids=v[4],
+                              kv_lens=v[5], max_new_tokens=max(news), max_kv_len=max(kv_lens), cache=self.cache,
+                              status=self.status, host_slots=slots, host_new_tokens=news, host_starts=starts)
+            logits = self.model.forward(ctx, v[6] if want else None, len(want))
+            self.cache.end_step(plan)
+        self.steps_run += 1
+        return logits
+
+    def check(self) -> None:
+        """Waits for the device and raises if a kernel flagged a fault (a token id outside the
+        embedding table, a bounded wait that gave up)."""
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            raise EngineError(f"a kernel reported device status {code}")
+
+    # -- convenience --------------------------------------------------------------
+    def generate(self, prompts, **kwargs):
+        from .generate import generate
+        return generate(self, prompts, **kwargs)

@@ -1,0 +1,120 @@
+"""A decoder model put together from a ModelSpec: token embedding, the layers in
+their order, the final norm and the output head.  It owns the weights and says
+what cache and state it needs; the step function drives it."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.allocator import GroupSpec
+from ..kernels import ops
+from ..parts.base import MixerSlot, build_part
+from ..parts.linear import Linear, compute_form
+from ..weights.loader import TensorSpec
+from .spec import ModelSpec
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.blocks = [build_part("block", b) for b in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.embedding = None
+        self.head = None
+        self.groups: list[GroupSpec] = []
+        self.slots: list[MixerSlot] = []
+        self.state_bytes = 0
+        self._plan_memory()
+
+    # -- what the checkpoint must hold -----------------------------------------
+    def tensors(self) -> dict[str, TensorSpec]:
+        s = self.spec
+        t = {s.embedding: TensorSpec((s.vocab, s.hidden))}
+        for b in self.blocks:
+            t.update(b.tensors())
+        t.update(self.final_norm.tensors())
+        if s.head is not None:
+            t[s.head] = TensorSpec((s.vocab, s.hidden))
+        return t
+
+    # -- cache planes and state offsets of every run ---------------------------
+    def _plan_memory(self) -> None:
+        keys: list[tuple] = []
+        planes: list[int] = []
+        specs: list[GroupSpec] = []
+        offset = 0
+        for i, run in enumerate(self.spec.order):
+            mixer = self.blocks[run.layer].mixer
+            need = mixer.cache_need()
+            slot = MixerSlot()
+            sb = int(mixer.state_bytes())
+            if sb:
+                offset = -(-offset // 16) * 16
+                slot.state_offset, slot.state_bytes = offset, sb
+                offset += sb
+            if need is not None:
+                if run.cache_from is not None:
+                    src = self.slots[run.cache_from]
+                    src_need = self.blocks[self.spec.order[run.cache_from].layer].mixer.cache_need()
+                    if src_need is None or src_need.key() != need.key():
+                        raise ValueError(f"order[{i}] cannot read the cache of entry {run.cache_from}: different needs")
+                    slot.group, slot.plane, slot.writes = src.group, src.plane, False
+                else:
+                    if need.key() not in keys:
+                        keys.append(need.key())
+                        planes.append(0)
+                        specs.append(need)
+                    g = keys.index(need.key())
+                    slot.group, slot.plane = g, planes[g]
+                    planes[g] += 1
+            self.slots.append(slot)
+        self.groups = [GroupSpec(s.kind, s.kv_heads, s.head_dim, planes[g], s.window) for g, s in enumerate(specs)]
+        self.state_bytes = offset
+
+    # -- weights ------------------------------------------------------------------
+    def load(self, weights: dict, device, dtype: torch.dtype) -> None:
+        s = self.spec
+        self.embedding = compute_form(weights[s.embedding], device, dtype)
+        for b in self.blocks:
+            b.load(weights, device, dtype)
+        self.final_norm.load(weights, device, dtype)
+        self.head = Linear(self.embedding if s.head is None else compute_form(weights[s.head], device, dtype))
+
+    def streamed_weight_bytes(self) -> int:
+        """Bytes of weights that a step reads whatever its tokens are: every layer that runs,
+        the final norm and the output head (an embedding table that is not the head is only
+        read row by row and is left out)."""
+        seen: set[int] = set()
+        total = 0
+
+        def visit(obj, depth=0):
+            nonlocal total
+            if isinstance(obj, torch.Tensor):
+                if obj.is_floating_point() and obj.data_ptr() not in seen:
+                    seen.add(obj.data_ptr())
+                    total += obj.numel() * obj.element_size()
+            elif isinstance(obj, (list, tuple)):
+                for v in obj:
+                    visit(v, depth + 1)
+            elif hasattr(obj, "__dict__") and depth < 6:
+                for v in vars(obj).values():
+                    visit(v, depth + 1)
+
+        for layer in sorted({run.layer for run in self.spec.order}):
+            visit(self.blocks[layer])
+        visit(self.final_norm)
+        visit(self.head)
+        return total
+
+    # -- one step -----------------------------------------------------------------
+    def forward(self, ctx, want_rows: torch.Tensor | None, num_want: int) -> torch.Tensor:
+        """Runs the step's tokens through all layers; returns float32 logits [num_want, vocab]
+        of the token rows that `want_rows` names (int32, device)."""
+        T = ctx.num_tokens
+        residual = torch.empty((T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
+        ops.embed(residual, self.embedding, ctx.tokens, ctx.status)
+        for run, slot in zip(self.spec.order, self.slots):
+            self.blocks[run.layer].forward(residual, ctx, slot)
+        if num_want == 0:
+            return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=ctx.device)
+        normed = self.final_norm.forward(residual, ctx, ctx.dtype, rows_index=want_rows, rows=num_want)
+        return self.head(normed, out_dtype=torch.float32)

@@ -1,0 +1,229 @@
+"""Python face of the CUDA library: every function checks its tensors, passes raw
+pointers and the current torch stream to one exported C function and raises
+KernelError when that function refuses.  Nothing here computes; there is no
+fallback to torch operators."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+EPILOGUE_STORE, EPILOGUE_ACCUMULATE, EPILOGUE_SWIGLU = 0, 1, 2
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return F32
+    if t == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {t} is not supported by the kernels (float32 and bfloat16 are)")
+
+
+def _lib():
+    return load_library()
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = _lib().hymt2_last_error().decode(errors="replace")
+        raise KernelError(f"{what} failed ({rc}): {msg}")
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got {t.dim()}")
+
+
+# ---------------------------------------------------------------------------
+def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] = float32(table[ids[t]]); out is [T, hidden] float32."""
+    _need(out, "out", torch.float32, 2); _need(table, "table", None, 2); _need(ids, "ids", torch.int32, 1)
+    T, H = out.shape
+    if table.shape[1] != H or ids.shape[0] < T:
+        raise KernelError(f"embed: shapes out {tuple(out.shape)} table {tuple(table.shape)} ids {tuple(ids.shape)}")
+    _check(_lib().hymt2_embed(_ptr(out), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), c_int(T),
+                              c_int(H), c_int(table.shape[0]), _ptr(status), _stream()), "embed")
+
+
+def rmsnorm(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float,
+            rows_index: torch.Tensor | None = None) -> None:
+    """out[r] = rmsnorm(x[rows_index[r]] or x[r]) * gain, computed in float32."""
+    _need(out, "out", None, 2); _need(x, "x", None, 2); _need(gain, "gain", None, 1)
+    rows, dim = out.shape
+    if x.shape[1] != dim or gain.shape[0] != dim:
+        raise KernelError(f"rmsnorm: shapes out {tuple(out.shape)} x {tuple(x.shape)} gain {tuple(gain.shape)}")
+    if rows_index is not None:
+        _need(rows_index, "rows_index", torch.int32, 1)
+        if rows_index.shape[0] < rows:
+            raise KernelError("rmsnorm: rows_index is shorter than out")
+    elif x.shape[0] < rows:
+        raise KernelError("rmsnorm: x has fewer rows than out")
+    _check(_lib().hymt2_rmsnorm(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(x), c_int(dtype_code(x.dtype)),
+                                _ptr(gain), c_int(dtype_code(gain.dtype)), _ptr(rows_index), c_int(rows),
+                                c_int(dim), c_float(eps), _stream()), "rmsnorm")
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, width + c]."""
+    _need(out, "out", None, 2); _need(gate_up, "gate_up", out.dtype, 2)
+    rows, width = out.shape
+    if gate_up.shape != (rows, 2 * width):
+        raise KernelError(f"silu_mul: shapes out {tuple(out.shape)} gate_up {tuple(gate_up.shape)}")
+    _check(_lib().hymt2_silu_mul(_ptr(out), _ptr(gate_up), c_int(dtype_code(out.dtype)), c_int(rows), c_int(width),
+                                 _stream()), "silu_mul")
+
+
+def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
+    """out[M, N] = epilogue(a[M, K] @ w[N, K]^T) on CUDA cores, float32 accumulation in K order.
+    With EPILOGUE_SWIGLU w has 2N rows (gate rows, then up rows)."""
+    for t, n in ((out, "out"), (a, "a"), (w, "w")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm: {n} must be a CUDA matrix with contiguous rows")
+    M, N = out.shape
+    K = a.shape[1]
+    rows_w = 2 * N if epilogue == EPILOGUE_SWIGLU else N
+    if a.shape[0] != M or w.shape != (rows_w, K):
+        raise KernelError(f"gemm: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)} epilogue {epilogue}")
+    _check(_lib().hymt2_gemm_simt(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), c_int(dtype_code(a.dtype)),
+                                  _ptr(w), c_int(dtype_code(w.dtype)), c_int(M), c_int(N), c_int(K),
+                                  c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)),
+                                  c_int(epilogue), _stream()), "gemm_simt")
+
+
+def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,
+            block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor,
+            slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int, q_gain: torch.Tensor | None,
+            k_gain: torch.Tensor | None, eps: float, nh: int, nkv: int, d: int) -> None:
+    """Rotation, per-head norm and cache append for the fused projection qkv[T, (nh+2nkv)*d].
+    k_plane/v_plane are one layer's cache planes [blocks, nkv, block_tokens, d], or None to
+    write no keys and values (a layer that reads another layer's cache)."""
+    _need(qkv, "qkv", None, 2); _need(q_out, "q_out", qkv.dtype, 2)
+    T = q_out.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d or q_out.shape[1] != nh * d or qkv.shape[0] < T:
+        raise KernelError(f"rope_kv: shapes qkv {tuple(qkv.shape)} q_out {tuple(q_out.shape)} for nh={nh} nkv={nkv} d={d}")
+    write = k_plane is not None
+    if write:
+        for t, n in ((k_plane, "k_plane"), (v_plane, "v_plane")):
+            _need(t, n, qkv.dtype, 4)
+            if t.shape[1:] != (nkv, block_tokens, d):
+                raise KernelError(f"rope_kv: {n} is {tuple(t.shape)}, expected [blocks, {nkv}, {block_tokens}, {d}]")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slot_ids, "slot_ids")):
+        _need(t, n, torch.int32, 1)
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rope_dim // 2:
+            raise KernelError("rope_kv: inv_freq must hold rope_dim/2 values")
+    gain_dtype = F32
+    if q_gain is not None:
+        _need(q_gain, "q_gain", None, 1); _need(k_gain, "k_gain", q_gain.dtype, 1)
+        if q_gain.shape[0] != d or k_gain.shape[0] != d:
+            raise KernelError("rope_kv: the q and k gains must have head_dim entries")
+        gain_dtype = dtype_code(q_gain.dtype)
+    _check(_lib().hymt2_rope_kv(_ptr(qkv), _ptr(q_out), _ptr(k_plane), _ptr(v_plane), c_int(dtype_code(qkv.dtype)),
+                                _ptr(block_table), c_int(block_table.stride(0)), c_int(block_tokens),
+                                _ptr(token_seq), _ptr(token_pos), _ptr(slot_ids), _ptr(inv_freq), c_int(rope_dim),
+                                _ptr(q_gain), _ptr(k_gain), c_int(gain_dtype), c_float(eps), c_int(T), c_int(nh),
+                                c_int(nkv), c_int(d), c_int(1 if write else 0), _stream()), "rope_kv")
+
+
+def attention_simt_scratch(tokens: int, nh: int, d: int, max_splits: int) -> tuple[int, int]:
+    """Floats of scratch (partial outputs, partial max/sum) that a split run needs."""
+    return tokens * nh * max_splits * d, tokens * nh * max_splits * 2
+
+
+def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                   block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor,
+                   kv_lens: torch.Tensor, batch: int, max_new_tokens: int, nh: int, nkv: int, d: int,
+                   scale: float, window: int = 0, split_keys: int = 0, max_splits: int = 0,
+                   part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> None:
+    """Causal grouped-query attention of the new tokens over the paged cache (CUDA cores)."""
+    _need(out, "out", None, 2); _need(q, "q", out.dtype, 2)
+    _need(k_plane, "k_plane", out.dtype, 4); _need(v_plane, "v_plane", out.dtype, 4)
+    T = out.shape[0]
+    block_tokens = k_plane.shape[2]
+    if out.shape[1] != nh * d or q.shape[1] != nh * d or q.shape[0] < T or k_plane.shape[1] != nkv \
+            or k_plane.shape[3] != d or v_plane.shape != k_plane.shape:
+        raise KernelError(f"attention: shapes out {tuple(out.shape)} q {tuple(q.shape)} k {tuple(k_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    if split_keys > 0:
+        need_acc, need_ml = attention_simt_scratch(T, nh, d, max_splits)
+        _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+            raise KernelError("attention: the split scratch is too small")
+    _check(_lib().hymt2_attention_simt(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), c_int(dtype_code(out.dtype)),
+                                       _ptr(block_table), c_int(block_table.stride(0)), c_int(block_tokens),
+                                       _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(T),
+                                       c_int(max_new_tokens), c_int(nh), c_int(nkv), c_int(d), c_float(scale),
+                                       c_int(window), c_int(split_keys), c_int(max_splits), _ptr(part_acc),
+                                       _ptr(part_ml), _stream()), "attention_simt")
+
+
+# ---------------------------------------------------------------------------
+def argmax(out: torch.Tensor, logits: torch.Tensor, row_active: torch.Tensor | None = None) -> None:
+    """out[r] = first index of the maximum of logits[r]; rows with row_active < 0 are skipped."""
+    _need(out, "out", torch.int32, 1)
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be a float32 CUDA matrix with contiguous rows")
+    rows, vocab = logits.shape
+    _check(_lib().hymt2_argmax(_ptr(out), _ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
+                               _ptr(row_active), _stream()), "argmax")
+
+
+def seed_rng(states: torch.Tensor, rows: torch.Tensor, seeds: torch.Tensor) -> None:
+    """states[rows[i]] = xoshiro256** state seeded with seeds[i] through SplitMix64."""
+    _need(states, "states", torch.int64, 2); _need(rows, "rows", torch.int32, 1); _need(seeds, "seeds", torch.int64, 1)
+    _check(_lib().hymt2_seed_rng(_ptr(states), _ptr(rows), _ptr(seeds), c_int(rows.shape[0]), _stream()), "seed_rng")
+
+
+def sample(out: torch.Tensor, logits: torch.Tensor, inv_temperature: torch.Tensor, rng_states: torch.Tensor,
+           rng_rows: torch.Tensor, row_active: torch.Tensor | None = None) -> None:
+    """Temperature sampling of one token per row; advances each row's random stream by one draw."""
+    _need(out, "out", torch.int32, 1); _need(inv_temperature, "inv_temperature", torch.float32, 1)
+    _need(rng_states, "rng_states", torch.int64, 2); _need(rng_rows, "rng_rows", torch.int32, 1)
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be a float32 CUDA matrix with contiguous rows")
+    rows, vocab = logits.shape
+    _check(_lib().hymt2_sample(_ptr(out), _ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
+                               _ptr(inv_temperature), _ptr(rng_states), _ptr(rng_rows), _ptr(row_active),
+                               _stream()), "sample")
+
+
+def filter_logits(logits: torch.Tensor, inv_temperature: torch.Tensor, top_k: torch.Tensor | None,
+                  top_p: torch.Tensor | None, min_p: torch.Tensor | None, penalty: torch.Tensor | None,
+                  history: torch.Tensor | None, row_active: torch.Tensor | None = None) -> None:
+    """In place: repetition penalty, then top-k / min-p / top-p drops (dropped entries become -inf)."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("filter: logits must be a float32 CUDA matrix with contiguous rows")
+    rows, vocab = logits.shape
+    hs = 0
+    if history is not None:
+        _need(history, "history", torch.int32, 2)
+        hs = history.shape[1]
+    _check(_lib().hymt2_filter_logits(_ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
+                                      _ptr(inv_temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(penalty),
+                                      _ptr(history), c_int(hs), _ptr(row_active), _stream()), "filter_logits")

@@ -1,0 +1,106 @@
+"""What the parts of a layer have in common.
+
+A layer is put together from parts: a *mixer* (attention here), a
+*feed-forward*, *norms*, a *position encoding*, and a *block* that arranges
+them.  Every part gets its sizes and constants as parameters, names the
+checkpoint tensors it reads, and computes on what a StepContext tells it
+about the running step.  No part knows which model it is in.
+
+Interfaces (duck-typed, see the classes in this package for examples):
+
+  every part
+      tensors() -> {checkpoint name: TensorSpec}
+      load(weights: {name: CPU tensor}, device, dtype) -> None
+  norm
+      forward(x [rows, dim], ctx, out_dtype, rows_index=None) -> [rows, dim]
+  position encoding
+      rotary_table() -> (inv_freq float32 [rope_dim/2], rope_dim) or None
+      apply(qkv, ctx, heads, kv_heads, head_dim) -> None   (in place; used when rotary_table() is None)
+  mixer
+      cache_need() -> GroupSpec or None      (planes is filled in by the model)
+      state_bytes() -> int                   (fixed-size state per sequence)
+      forward(x [T, hidden], residual float32 [T, hidden], ctx, slot: MixerSlot) -> None
+          adds its output to `residual`
+  feed-forward
+      forward(x [T, hidden], residual float32 [T, hidden], ctx) -> None
+  block
+      forward(residual, ctx, slot: MixerSlot) -> None
+
+New kinds are added with `register_part(category, kind, factory)`; a model
+spec names parts by (category, kind) and gives the factory's parameters.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable
+
+import torch
+
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+_REGISTRY: dict[tuple[str, str], Callable] = {}
+
+
+def register_part(category: str, kind: str, factory: Callable) -> None:
+    if category not in CATEGORIES:
+        raise ValueError(f"unknown part category '{category}' (known: {', '.join(CATEGORIES)})")
+    _REGISTRY[(category, kind)] = factory
+
+
+def build_part(category: str, spec: "PartSpec"):
+    try:
+        factory = _REGISTRY[(category, spec.kind)]
+    except KeyError:
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise ValueError(f"unknown {category} kind '{spec.kind}' (known: {', '.join(known)})") from None
+    return factory(**spec.params)
+
+
+@dataclass
+class PartSpec:
+    kind: str
+    params: dict = field(default_factory=dict)
+
+
+@dataclass
+class MixerSlot:
+    """Where one run of a mixer keeps what it remembers."""
+    group: int | None = None      # cache group of its keys and values
+    plane: int | None = None      # its plane inside the group
+    writes: bool = True           # False: it reads the plane that another run wrote
+    state_offset: int = 0         # byte offset of its fixed-size state in a sequence's state row
+    state_bytes: int = 0
+
+
+@dataclass
+class StepContext:
+    """One step as the parts see it.  All index tensors are int32 on the device.
+
+    The step runs T new tokens of B sequences; sequence b contributes the tokens
+    cu_seqlens[b]..cu_seqlens[b+1], sits in cache slot slot_ids[b] (or -1 for a
+    padding row) and is kv_lens[b] tokens long once this step's tokens are in."""
+    device: torch.device
+    dtype: torch.dtype
+    num_tokens: int
+    num_seqs: int
+    tokens: torch.Tensor
+    token_seq: torch.Tensor
+    token_pos: torch.Tensor
+    cu_seqlens: torch.Tensor
+    slot_ids: torch.Tensor
+    kv_lens: torch.Tensor
+    max_new_tokens: int          # the longest sequence's new tokens
+    max_kv_len: int              # the longest sequence after the step (an upper bound is allowed)
+    cache: object                # cache.PagedCache
+    status: torch.Tensor         # int32 [4] device error word(s)
+    host_slots: list = field(default_factory=list)       # the same facts on the host, for parts
+    host_new_tokens: list = field(default_factory=list)  # that plan their work there
+    host_starts: list = field(default_factory=list)
+
+    @property
+    def decode(self) -> bool:
+        return self.max_new_tokens == 1
+
+    def state_view(self, slot: MixerSlot, dtype: torch.dtype, shape: tuple) -> torch.Tensor:
+        """The state rows of all slots as [max_slots, *shape] of `dtype`."""
+        raw = self.cache.state[:, slot.state_offset: slot.state_offset + slot.state_bytes]
+        return raw.view(dtype).view(raw.shape[0], *shape)

@@ -1,0 +1,36 @@
+"""Pre-norm residual block: h += mixer(norm1(h)); h += ffn(norm2(h))
+(src/HyMT2Sharp/HunyuanDenseModel.Prefill.cs:14-36).  The residual stream h is
+float32; the normed activations have the engine's compute type."""
+from __future__ import annotations
+
+from .base import PartSpec, build_part, register_part
+
+
+class PreNormBlock:
+    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, feed_forward: PartSpec):
+        self.norm1 = build_part("norm", norm1)
+        self.mixer = build_part("mixer", mixer)
+        self.norm2 = build_part("norm", norm2)
+        self.feed_forward = build_part("feed_forward", feed_forward)
+
+    def parts(self):
+        return (self.norm1, self.mixer, self.norm2, self.feed_forward)
+
+    def tensors(self):
+        t = {}
+        for p in self.parts():
+            t.update(p.tensors())
+        return t
+
+    def load(self, weights, device, dtype):
+        for p in self.parts():
+            p.load(weights, device, dtype)
+
+    def forward(self, residual, ctx, slot) -> None:
+        x = self.norm1.forward(residual, ctx, ctx.dtype)
+        self.mixer.forward(x, residual, ctx, slot)
+        x = self.norm2.forward(residual, ctx, ctx.dtype)
+        self.feed_forward.forward(x, residual, ctx)
+
+
+register_part("block", "pre_norm", PreNormBlock)
