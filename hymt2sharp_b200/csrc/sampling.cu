@@ -21,11 +21,11 @@ constexpr int THREADS = 1024;
 
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_stride, int vocab,
-              const int* __restrict__ row_active) {
+              const int* __restrict__ row_map) {
     __shared__ float sval[32];
     __shared__ int sidx[32];
     const int row = blockIdx.x;
-    if (row_active && row_active[row] < 0) return;
+    if (row_map && row_map[row] < 0) return;
     const float* x = logits + (size_t)row * row_stride;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
@@ -116,15 +116,17 @@ __device__ __forceinline__ V block_exclusive_scan(V v, V* warp_totals, V* total)
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_stride, int vocab,
               const float* __restrict__ inv_temperature, uint64_t* __restrict__ rng_states,
-              const int* __restrict__ rng_rows, const int* __restrict__ row_active) {
+              const int* __restrict__ row_map) {
     __shared__ float scratch[33];
     __shared__ float warp_totals[32];
     __shared__ float total_s;
     __shared__ int pick_s, owner_s;
     const int row = blockIdx.x;
-    if (row_active && row_active[row] < 0) return;
+    const int srow = row_map ? row_map[row] : row;  // the sequence's row in the per-sequence arrays
+    if (srow < 0) return;
     const float* x = logits + (size_t)row * row_stride;
-    const float inv_t = inv_temperature[row];
+    const float inv_t = inv_temperature[srow];
+    if (!(inv_t > 0.f)) return;  // a greedy row: argmax has written its token
     const int piece = (vocab + THREADS - 1) / THREADS;
     const int begin = min(vocab, (int)threadIdx.x * piece), end = min(vocab, begin + piece);
 
@@ -142,7 +144,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
 
     float u = 0.f;
     if (threadIdx.x == 0) {
-        uint64_t* s = rng_states + (size_t)rng_rows[row] * 4;
+        uint64_t* s = rng_states + (size_t)srow * 4;
         u = (float)(xoshiro_next(s) >> 40) * (1.0f / 16777216.0f);
         scratch[0] = u;
         owner_s = 0x7fffffff;
@@ -223,14 +225,14 @@ struct FilterParams {
     float* logits;
     long row_stride;
     int vocab;
-    const float* inv_temperature;  // [rows]
-    const int* top_k;              // [rows], 0 = off
-    const float* top_p;            // [rows], >= 1 = off
-    const float* min_p;            // [rows], <= 0 = off
-    const float* penalty;          // [rows], 1 = off
-    const int* history;            // [rows, history_stride] recent tokens, -1 = empty
+    const float* inv_temperature;  // per sequence; <= 0 marks a greedy row (only the penalty applies)
+    const int* top_k;              // per sequence, 0 = off
+    const float* top_p;            // per sequence, >= 1 = off
+    const float* min_p;            // per sequence, <= 0 = off
+    const float* penalty;          // per sequence, 1 = off
+    const int* history;            // [sequence, history_stride] recent tokens, -1 = empty
     int history_stride;
-    const int* row_active;
+    const int* row_map;            // logits row -> sequence row, < 0 = skip
 };
 
 __global__ void __launch_bounds__(THREADS)
@@ -242,17 +244,18 @@ filter_kernel(FilterParams p) {
     __shared__ int iscan[32];
     __shared__ int iscan_total;
     const int row = blockIdx.x;
-    if (p.row_active && p.row_active[row] < 0) return;
+    const int srow = p.row_map ? p.row_map[row] : row;
+    if (srow < 0) return;
     float* x = p.logits + (size_t)row * p.row_stride;
     const int vocab = p.vocab;
     const int piece = (vocab + THREADS - 1) / THREADS;
     const int begin = min(vocab, (int)threadIdx.x * piece), end = min(vocab, begin + piece);
 
     // repetition penalty: every entry of the window applies once, repeats included
-    const float pen = p.penalty ? p.penalty[row] : 1.f;
+    const float pen = p.penalty ? p.penalty[srow] : 1.f;
     if (pen != 1.f && p.history) {
         if (threadIdx.x == 0) {
-            const int* h = p.history + (size_t)row * p.history_stride;
+            const int* h = p.history + (size_t)srow * p.history_stride;
             for (int i = 0; i < p.history_stride; i++) {
                 const int t = h[i];
                 if (t < 0 || t >= vocab) continue;
@@ -262,9 +265,10 @@ filter_kernel(FilterParams p) {
         }
         __syncthreads();
     }
-    const float inv_t = p.inv_temperature[row];
-    const int k = p.top_k ? p.top_k[row] : 0;
-    const float top_p = p.top_p ? p.top_p[row] : 1.f, min_p = p.min_p ? p.min_p[row] : 0.f;
+    const float inv_t = p.inv_temperature[srow];
+    if (!(inv_t > 0.f)) return;  // greedy: temperature 0 bypasses every other field (Sampling.cs:81-84)
+    const int k = p.top_k ? p.top_k[srow] : 0;
+    const float top_p = p.top_p ? p.top_p[srow] : 1.f, min_p = p.min_p ? p.min_p[srow] : 0.f;
 
     if (k > 0 && k < vocab) {
         const uint32_t kth = kth_largest_key(x, inv_t, vocab, k, hist, misc);
@@ -369,13 +373,32 @@ filter_kernel(FilterParams p) {
     }
 }
 
+// history[sequence, count % stride] = token; count += 1 (the ring of Sampling.cs:158-169)
+__global__ void record_history_kernel(int* history, int* counts, int stride, const int* tokens, const int* row_map,
+                                      int rows) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    const int srow = row_map ? row_map[row] : row;
+    if (srow < 0) return;
+    const int c = counts[srow];
+    history[(size_t)srow * stride + c % stride] = tokens[row];
+    counts[srow] = c + 1;
+}
+
 }  // namespace
 
+HYMT2_API int hymt2_record_history(int* history, int* counts, int stride, const int* tokens, const int* row_map,
+                                   int rows, cudaStream_t stream) {
+    if (rows == 0 || stride == 0) return HYMT2_OK;
+    record_history_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(history, counts, stride, tokens, row_map, rows);
+    return hymt2_check_launch("record_history");
+}
+
 HYMT2_API int hymt2_argmax(int* out, const float* logits, long row_stride, int rows, int vocab,
-                           const int* row_active, cudaStream_t stream) {
+                           const int* row_map, cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
-    argmax_kernel<<<rows, THREADS, 0, stream>>>(out, logits, row_stride, vocab, row_active);
+    argmax_kernel<<<rows, THREADS, 0, stream>>>(out, logits, row_stride, vocab, row_map);
     return hymt2_check_launch("argmax");
 }
 
@@ -386,23 +409,23 @@ HYMT2_API int hymt2_seed_rng(uint64_t* states, const int* rows, const uint64_t* 
 }
 
 HYMT2_API int hymt2_sample(int* out, const float* logits, long row_stride, int rows, int vocab,
-                           const float* inv_temperature, uint64_t* rng_states, const int* rng_rows,
-                           const int* row_active, cudaStream_t stream) {
+                           const float* inv_temperature, uint64_t* rng_states, const int* row_map,
+                           cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     sample_kernel<<<rows, THREADS, 0, stream>>>(out, logits, row_stride, vocab, inv_temperature, rng_states,
-                                                rng_rows, row_active);
+                                                row_map);
     return hymt2_check_launch("sample");
 }
 
 HYMT2_API int hymt2_filter_logits(float* logits, long row_stride, int rows, int vocab, const float* inv_temperature,
                                   const int* top_k, const float* top_p, const float* min_p, const float* penalty,
-                                  const int* history, int history_stride, const int* row_active,
+                                  const int* history, int history_stride, const int* row_map,
                                   cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "filter: bad sizes rows=%d vocab=%d", rows, vocab);
     FilterParams p{logits, row_stride, vocab, inv_temperature, top_k, top_p, min_p, penalty, history,
-                   history_stride, row_active};
+                   history_stride, row_map};
     filter_kernel<<<rows, THREADS, 0, stream>>>(p);
     return hymt2_check_launch("filter_logits");
 }

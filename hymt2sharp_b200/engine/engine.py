@@ -46,6 +46,49 @@ def require_gpu(device) -> torch.device:
     return device
 
 
+def make_context(cache, entries: list, vocab: int, dtype, device, status, meta_buffer=None):
+    """Checks the entries, takes the cache blocks that their tokens need (all or nothing) and
+    builds the StepContext: packed tokens, each token's batch row and position, the rows'
+    offsets, slots and lengths.  Returns (context, wanted rows or None, their count, plan);
+    `plan` goes to cache.end_step once the step has been launched."""
+    tokens, token_seq, token_pos, cu, slots, kv_lens, want = [], [], [], [0], [], [], []
+    starts, news = [], []
+    for b, e in enumerate(entries):
+        n = len(e.tokens)
+        start = cache.length(e.slot)
+        for t in e.tokens:
+            if not (0 <= int(t) < vocab):
+                raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
+        for w in e.want:
+            if not (0 <= int(w) < n):
+                raise EngineError(f"wanted place {w} is outside the {n} tokens of the entry")
+            want.append(cu[-1] + int(w))
+        tokens.extend(int(t) for t in e.tokens)
+        token_seq.extend([b] * n)
+        token_pos.extend(range(start, start + n))
+        cu.append(cu[-1] + n)
+        slots.append(e.slot)
+        kv_lens.append(start + n)
+        starts.append(start)
+        news.append(n)
+    plan = list(zip(slots, news))
+    cache.begin_step(plan)  # raises CacheFull before anything changed
+    arrays = [np.asarray(a, dtype=np.int32) for a in (tokens, token_seq, token_pos, cu, slots, kv_lens, want)]
+    sizes = [len(a) for a in arrays]
+    total = sum(sizes)
+    meta = meta_buffer(total) if meta_buffer is not None else torch.empty(total, dtype=torch.int32, device=device)
+    meta[:total].copy_(torch.from_numpy(np.concatenate(arrays)))
+    v, o = [], 0
+    for n in sizes:
+        v.append(meta[o:o + n])
+        o += n
+    ctx = StepContext(device=torch.device(device), dtype=dtype, num_tokens=len(tokens), num_seqs=len(entries),
+                      tokens=v[0], token_seq=v[1], token_pos=v[2], cu_seqlens=v[3], slot_ids=v[4], kv_lens=v[5],
+                      max_new_tokens=max(news), max_kv_len=max(kv_lens), cache=cache, status=status,
+                      host_slots=slots, host_new_tokens=news, host_starts=starts)
+    return ctx, (v[6] if want else None), len(want), plan
+
+
 class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_batch: int = 8,
                  block_tokens: int = 64, device="cuda:0", max_sequence_tokens: int | None = None,
@@ -81,58 +124,24 @@ class Engine:
         return self.cache.length(slot)
 
     # -- the step ---------------------------------------------------------------
-    def _upload_meta(self, parts: list[np.ndarray]) -> list[torch.Tensor]:
-        sizes = [len(p) for p in parts]
-        total = sum(sizes)
-        if total > self._meta.numel():
-            self._meta = torch.zeros(max(total, 2 * self._meta.numel()), dtype=torch.int32, device=self.device)
-        host = np.concatenate(parts).astype(np.int32, copy=False) if total else np.zeros(0, np.int32)
-        self._meta[:total].copy_(torch.from_numpy(host))
-        views, o = [], 0
-        for n in sizes:
-            views.append(self._meta[o:o + n])
-            o += n
-        return views
-
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Runs one step; returns float32 logits [wanted places, vocab] on the device, in the
         order of the entries and of each entry's `want`."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
-        tokens, token_seq, token_pos, cu, slots, kv_lens, want = [], [], [], [0], [], [], []
-        starts, news = [], []
-        for b, e in enumerate(entries):
-            n = len(e.tokens)
-            start = self.cache.length(e.slot)
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab):
-                    raise EngineError(f"token id {t} is outside the vocabulary of {self.vocab}")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise EngineError(f"wanted place {w} is outside the {n} tokens of the entry")
-                want.append(cu[-1] + int(w))
-            tokens.extend(int(t) for t in e.tokens)
-            token_seq.extend([b] * n)
-            token_pos.extend(range(start, start + n))
-            cu.append(cu[-1] + n)
-            slots.append(e.slot)
-            kv_lens.append(start + n)
-            starts.append(start)
-            news.append(n)
-        plan = list(zip(slots, news))
         with torch.cuda.device(self.device):
-            self.cache.begin_step(plan)  # raises CacheFull before anything changed
-            arrays = [np.asarray(a, dtype=np.int32) for a in (tokens, token_seq, token_pos, cu, slots, kv_lens, want)]
-            v = self._upload_meta(arrays)
-            ctx = StepContext(device=self.device, dtype=self.dtype, num_tokens=len(tokens), num_seqs=len(entries),
-                              tokens=v[0], token_seq=v[1], token_pos=v[2], cu_seqlens=v[3], slot_ids=v[4],
-                              kv_lens=v[5], max_new_tokens=max(news), max_kv_len=max(kv_lens), cache=self.cache,
-                              status=self.status, host_slots=slots, host_new_tokens=news, host_starts=starts)
-            logits = self.model.forward(ctx, v[6] if want else None, len(want))
+            ctx, want, num_want, plan = make_context(self.cache, entries, self.vocab, self.dtype, self.device,
+                                                     self.status, self._meta_buffer)
+            logits = self.model.forward(ctx, want, num_want)
             self.cache.end_step(plan)
         self.steps_run += 1
         return logits
+
+    def _meta_buffer(self, n: int) -> torch.Tensor:
+        if n > self._meta.numel():
+            self._meta = torch.zeros(max(n, 2 * self._meta.numel()), dtype=torch.int32, device=self.device)
+        return self._meta
 
     def check(self) -> None:
         """Waits for the device and raises if a kernel flagged a fault (a token id outside the

@@ -1,0 +1,224 @@
+"""The generation loop: batches of unequal prompts, stop tokens, sequences that end
+earlier than others, and as many batches one after another as there are requests.
+
+The loop is the one that sdcb/HyMT2Sharp's callers write around Forward
+(src/HyMT2Sharp.Cli/Program.cs:84-110): the prompt's last logits give the first
+token; a stop token ends the reply and is not kept; the token limit ends it with
+"length".  Here it runs for a whole batch: all prompts in one step, then one token
+for every sequence that is still running.  The loop's decisions are plain Python
+over token ids (`BatchState`, `plan_batches`); the device work sits behind a
+stepper object, so the decisions can be tested without a GPU.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+from ..sampling.params import GREEDY, SamplingParams
+
+
+@dataclass
+class GenerationResult:
+    tokens: list
+    finish_reason: str          # "stop" or "length"
+    prompt_tokens: int
+
+
+@dataclass
+class GenerationStats:
+    batches: int = 0
+    prefill_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_tokens: int = 0      # tokens produced by decode steps
+    decode_steps: int = 0
+    decode_ms: float = 0.0
+
+    def line(self) -> str:
+        """The timing line of src/HyMT2Sharp.Cli/Program.cs:121-126."""
+        pre = f"prefill tokens={self.prefill_tokens}  {self.prefill_ms:.1f} ms  " \
+              f"{self.prefill_tokens / max(self.prefill_ms, 1e-9) * 1000.0:.2f} tok/s"
+        if self.decode_tokens > 0:
+            return pre + f"  |  decode tokens={self.decode_tokens}  {self.decode_ms:.1f} ms  " \
+                         f"{self.decode_tokens / max(self.decode_ms, 1e-9) * 1000.0:.2f} tok/s"
+        return pre + "  |  decode tokens=0"
+
+
+@dataclass
+class GenerationOutput:
+    results: list
+    stats: GenerationStats
+
+    def __iter__(self):
+        return iter(self.results)
+
+    def __getitem__(self, i):
+        return self.results[i]
+
+    def __len__(self):
+        return len(self.results)
+
+
+def plan_batches(prompt_lens: list, max_new_tokens: int, max_batch: int, capacity_tokens: int,
+                 block_tokens: int) -> list:
+    """Cuts the requests, in their order, into batches: at most `max_batch` sequences each, and
+    the blocks that a batch can come to hold (prompt + max_new_tokens - 1 cached tokens per
+    sequence, rounded up to whole blocks) fit the cache."""
+    if max_batch <= 0:
+        raise ValueError("max_batch must be positive")
+    capacity_blocks = capacity_tokens // block_tokens
+    batches, current, used = [], [], 0
+    for i, n in enumerate(prompt_lens):
+        if n <= 0:
+            raise ValueError(f"request {i} has an empty prompt")
+        need = -(-(n + max(0, max_new_tokens - 1)) // block_tokens)
+        if need > capacity_blocks:
+            raise ValueError(f"request {i} ({n} prompt tokens + {max_new_tokens} new) needs {need} cache blocks of "
+                             f"{block_tokens} tokens; the cache has {capacity_blocks}")
+        if current and (len(current) >= max_batch or used + need > capacity_blocks):
+            batches.append(current)
+            current, used = [], 0
+        current.append(i)
+        used += need
+    if current:
+        batches.append(current)
+    return batches
+
+
+class BatchState:
+    """What the loop knows about one running batch: each sequence's kept tokens, and which
+    sequences still run."""
+
+    def __init__(self, request_ids: list, prompt_lens: list, max_new_tokens: int, stop_token_ids):
+        self.request_ids = list(request_ids)
+        self.max_new_tokens = int(max_new_tokens)
+        self.stop = frozenset(int(t) for t in stop_token_ids)
+        self.outputs = [[] for _ in request_ids]
+        self.reasons = [None] * len(request_ids)
+        self.prompt_lens = list(prompt_lens)
+        self.live = list(range(len(request_ids)))  # rows of the batch that still run
+        if self.max_new_tokens <= 0:
+            for r in self.live:
+                self.reasons[r] = "length"
+            self.live = []
+
+    def accept(self, tokens: list) -> tuple:
+        """Takes one sampled token for every live row (in the order of `live`).  Returns
+        (rows that go on, rows that ended now)."""
+        if len(tokens) != len(self.live):
+            raise ValueError("one token for every live sequence is needed")
+        go_on, ended = [], []
+        for row, tok in zip(self.live, tokens):
+            tok = int(tok)
+            if tok in self.stop:
+                self.reasons[row] = "stop"       # a stop token is not kept
+                ended.append(row)
+                continue
+            self.outputs[row].append(tok)
+            if len(self.outputs[row]) >= self.max_new_tokens:
+                self.reasons[row] = "length"
+                ended.append(row)
+            else:
+                go_on.append(row)
+        self.live = go_on
+        return go_on, ended
+
+    def last_tokens(self) -> list:
+        return [self.outputs[r][-1] for r in self.live]
+
+    def results(self) -> list:
+        return [GenerationResult(self.outputs[r], self.reasons[r] or "length", self.prompt_lens[r])
+                for r in range(len(self.request_ids))]
+
+
+class EngineStepper:
+    """The device side of the loop for one batch: slots, the steps, the sampler."""
+
+    def __init__(self, engine, params: list, prompts: list):
+        import torch
+        from ..sampling.sampler import BatchSampler
+        from .engine import StepEntry
+        self._torch, self._StepEntry = torch, StepEntry
+        self.engine = engine
+        self.prompts = prompts
+        self.slots = engine.alloc_slots(len(prompts))
+        self.sampler = BatchSampler(params, engine.device, prompts)
+        self.held = set(range(len(prompts)))
+
+    def prefill(self) -> list:
+        entries = [self._StepEntry(s, p, [len(p) - 1]) for s, p in zip(self.slots, self.prompts)]
+        logits = self.engine.step(entries)
+        return self.sampler.sample(logits, None).tolist()
+
+    def decode(self, rows: list, tokens: list) -> list:
+        torch = self._torch
+        entries = [self._StepEntry(self.slots[r], [t], [0]) for r, t in zip(rows, tokens)]
+        logits = self.engine.step(entries)
+        row_map = torch.tensor(rows, dtype=torch.int32, device=self.engine.device)
+        return self.sampler.sample(logits, row_map).tolist()
+
+    def release(self, rows: list) -> None:
+        rows = [r for r in rows if r in self.held]
+        self.held.difference_update(rows)
+        self.engine.free_slots([self.slots[r] for r in rows])
+
+    def close(self) -> None:
+        self.release(list(self.held))
+
+
+def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None, clock=time.perf_counter) -> None:
+    """Drives one batch to its end through `stepper` (prefill(), decode(rows, tokens),
+    release(rows), close())."""
+    try:
+        if not state.live:
+            return
+        t0 = clock()
+        tokens = stepper.prefill()
+        stats.prefill_ms += (clock() - t0) * 1000.0
+        stats.prefill_tokens += sum(state.prompt_lens)
+        rows_before = list(state.live)
+        go_on, ended = state.accept(tokens)
+        if on_tokens:
+            on_tokens([(state.request_ids[r], t) for r, t in zip(rows_before, tokens) if state.reasons[r] != "stop"])
+        stepper.release(ended)
+        t0 = clock()
+        while state.live:
+            rows_before = list(state.live)
+            tokens = stepper.decode(rows_before, state.last_tokens())
+            stats.decode_steps += 1
+            stats.decode_tokens += len(tokens)
+            go_on, ended = state.accept(tokens)
+            if on_tokens:
+                on_tokens([(state.request_ids[r], t) for r, t in zip(rows_before, tokens)
+                           if state.reasons[r] != "stop"])
+            stepper.release(ended)
+        stats.decode_ms += (clock() - t0) * 1000.0
+    finally:
+        stepper.close()
+
+
+def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_token_ids=(),
+             max_batch: int | None = None, on_tokens=None, stepper_factory=None) -> GenerationOutput:
+    """Generates for every prompt (a list of token ids).  `sampling` is one SamplingParams for
+    all requests or a list with one per request; the default is greedy.  Returns the kept
+    tokens and the finish reason of every request, in the order of `prompts`."""
+    prompts = [list(map(int, p)) for p in prompts]
+    if sampling is None:
+        sampling = GREEDY
+    params = [sampling] * len(prompts) if isinstance(sampling, SamplingParams) else list(sampling)
+    if len(params) != len(prompts):
+        raise ValueError("one SamplingParams for every prompt is needed")
+    max_batch = max_batch or engine.cache.max_slots
+    capacity = engine.cache.num_blocks * engine.cache.block_tokens
+    batches = plan_batches([len(p) for p in prompts], max_new_tokens, max_batch, capacity, engine.cache.block_tokens)
+    factory = stepper_factory or EngineStepper
+    stats = GenerationStats()
+    results = [None] * len(prompts)
+    for ids in batches:
+        state = BatchState(ids, [len(prompts[i]) for i in ids], max_new_tokens, stop_token_ids)
+        stepper = factory(engine, [params[i] for i in ids], [prompts[i] for i in ids])
+        run_batch(stepper, state, stats, on_tokens)
+        stats.batches += 1
+        for i, res in zip(ids, state.results()):
+            results[i] = res
+    engine.check()
+    return GenerationOutput(results, stats)

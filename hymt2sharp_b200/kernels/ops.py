@@ -184,14 +184,18 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
 
 
 # ---------------------------------------------------------------------------
-def argmax(out: torch.Tensor, logits: torch.Tensor, row_active: torch.Tensor | None = None) -> None:
-    """out[r] = first index of the maximum of logits[r]; rows with row_active < 0 are skipped."""
-    _need(out, "out", torch.int32, 1)
+def _logits_ok(logits: torch.Tensor, what: str) -> None:
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
-        raise KernelError("argmax: logits must be a float32 CUDA matrix with contiguous rows")
+        raise KernelError(f"{what}: logits must be a float32 CUDA matrix with contiguous rows")
+
+
+def argmax(out: torch.Tensor, logits: torch.Tensor, row_map: torch.Tensor | None = None) -> None:
+    """out[r] = first index of the maximum of logits[r]; rows with row_map[r] < 0 are skipped."""
+    _need(out, "out", torch.int32, 1)
+    _logits_ok(logits, "argmax")
     rows, vocab = logits.shape
     _check(_lib().hymt2_argmax(_ptr(out), _ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
-                               _ptr(row_active), _stream()), "argmax")
+                               _ptr(row_map), _stream()), "argmax")
 
 
 def seed_rng(states: torch.Tensor, rows: torch.Tensor, seeds: torch.Tensor) -> None:
@@ -201,24 +205,24 @@ def seed_rng(states: torch.Tensor, rows: torch.Tensor, seeds: torch.Tensor) -> N
 
 
 def sample(out: torch.Tensor, logits: torch.Tensor, inv_temperature: torch.Tensor, rng_states: torch.Tensor,
-           rng_rows: torch.Tensor, row_active: torch.Tensor | None = None) -> None:
-    """Temperature sampling of one token per row; advances each row's random stream by one draw."""
+           row_map: torch.Tensor | None = None) -> None:
+    """Temperature sampling of one token for every logits row whose sequence has a temperature
+    above 0; advances that sequence's random stream by one draw.  row_map[r] is the row of the
+    per-sequence arrays (inv_temperature, rng_states) that logits row r belongs to; < 0 skips."""
     _need(out, "out", torch.int32, 1); _need(inv_temperature, "inv_temperature", torch.float32, 1)
-    _need(rng_states, "rng_states", torch.int64, 2); _need(rng_rows, "rng_rows", torch.int32, 1)
-    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
-        raise KernelError("sample: logits must be a float32 CUDA matrix with contiguous rows")
+    _need(rng_states, "rng_states", torch.int64, 2)
+    _logits_ok(logits, "sample")
     rows, vocab = logits.shape
     _check(_lib().hymt2_sample(_ptr(out), _ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
-                               _ptr(inv_temperature), _ptr(rng_states), _ptr(rng_rows), _ptr(row_active),
-                               _stream()), "sample")
+                               _ptr(inv_temperature), _ptr(rng_states), _ptr(row_map), _stream()), "sample")
 
 
 def filter_logits(logits: torch.Tensor, inv_temperature: torch.Tensor, top_k: torch.Tensor | None,
                   top_p: torch.Tensor | None, min_p: torch.Tensor | None, penalty: torch.Tensor | None,
-                  history: torch.Tensor | None, row_active: torch.Tensor | None = None) -> None:
-    """In place: repetition penalty, then top-k / min-p / top-p drops (dropped entries become -inf)."""
-    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
-        raise KernelError("filter: logits must be a float32 CUDA matrix with contiguous rows")
+                  history: torch.Tensor | None, row_map: torch.Tensor | None = None) -> None:
+    """In place: repetition penalty, then (temperature > 0 only) top-k / min-p / top-p drops;
+    dropped entries become -inf."""
+    _logits_ok(logits, "filter")
     rows, vocab = logits.shape
     hs = 0
     if history is not None:
@@ -226,4 +230,13 @@ def filter_logits(logits: torch.Tensor, inv_temperature: torch.Tensor, top_k: to
         hs = history.shape[1]
     _check(_lib().hymt2_filter_logits(_ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
                                       _ptr(inv_temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(penalty),
-                                      _ptr(history), c_int(hs), _ptr(row_active), _stream()), "filter_logits")
+                                      _ptr(history), c_int(hs), _ptr(row_map), _stream()), "filter_logits")
+
+
+def record_history(history: torch.Tensor, counts: torch.Tensor, tokens: torch.Tensor,
+                   row_map: torch.Tensor | None, rows: int) -> None:
+    """history[sequence, count % width] = tokens[r]; count += 1, for every logits row r."""
+    _need(history, "history", torch.int32, 2); _need(counts, "counts", torch.int32, 1)
+    _need(tokens, "tokens", torch.int32, 1)
+    _check(_lib().hymt2_record_history(_ptr(history), _ptr(counts), c_int(history.shape[1]), _ptr(tokens),
+                                       _ptr(row_map), c_int(rows), _stream()), "record_history")

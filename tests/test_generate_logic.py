@@ -1,0 +1,98 @@
+"""The generation loop's decisions, without a GPU: a scripted stepper stands in for the device."""
+import pytest
+
+from hymt2sharp_b200.engine.generate import (BatchState, GenerationStats, plan_batches, run_batch)
+
+
+class ScriptedStepper:
+    """Gives every sequence its scripted tokens; records what the loop asks of the device."""
+
+    def __init__(self, scripts):
+        self.scripts = scripts
+        self.cursor = [0] * len(scripts)
+        self.calls = []
+        self.released = []
+        self.closed = False
+
+    def _next(self, rows):
+        out = []
+        for r in rows:
+            out.append(self.scripts[r][self.cursor[r]])
+            self.cursor[r] += 1
+        return out
+
+    def prefill(self):
+        self.calls.append(("prefill", list(range(len(self.scripts)))))
+        return self._next(range(len(self.scripts)))
+
+    def decode(self, rows, tokens):
+        self.calls.append(("decode", list(rows), list(tokens)))
+        return self._next(rows)
+
+    def release(self, rows):
+        self.released += list(rows)
+
+    def close(self):
+        self.closed = True
+
+
+def test_stop_token_is_not_kept_and_others_go_on():
+    scripts = [[5, 6, 99, 1, 1], [7, 99, 1, 1, 1], [8, 9, 10, 11, 12]]
+    stepper = ScriptedStepper(scripts)
+    state = BatchState(["a", "b", "c"], [3, 4, 5], max_new_tokens=4, stop_token_ids=[99])
+    stats = GenerationStats()
+    seen = []
+    run_batch(stepper, state, stats, on_tokens=seen.extend, clock=lambda: 0.0)
+    res = state.results()
+    assert [r.tokens for r in res] == [[5, 6], [7], [8, 9, 10, 11]]
+    assert [r.finish_reason for r in res] == ["stop", "stop", "length"]
+    # the batch shrinks: b leaves after step 1, a after step 2; each step feeds the last kept tokens
+    assert stepper.calls == [("prefill", [0, 1, 2]), ("decode", [0, 1, 2], [5, 7, 8]),
+                             ("decode", [0, 2], [6, 9]), ("decode", [2], [10])]
+    assert stepper.released == [1, 0, 2] and stepper.closed
+    assert stats.prefill_tokens == 12 and stats.decode_steps == 3 and stats.decode_tokens == 6
+    assert seen == [("a", 5), ("b", 7), ("c", 8), ("a", 6), ("c", 9), ("c", 10), ("c", 11)]
+
+
+def test_first_token_can_stop_and_limits():
+    stepper = ScriptedStepper([[99], [4, 5]])
+    state = BatchState([0, 1], [2, 2], max_new_tokens=1, stop_token_ids={99})
+    run_batch(stepper, state, GenerationStats())
+    assert [r.tokens for r in state.results()] == [[], [4]]
+    assert [r.finish_reason for r in state.results()] == ["stop", "length"]
+    assert stepper.calls == [("prefill", [0, 1])]  # one token each needs no decode step
+    zero = BatchState([0], [2], max_new_tokens=0, stop_token_ids=())
+    s2 = ScriptedStepper([[1]])
+    run_batch(s2, zero, GenerationStats())
+    assert zero.results()[0].tokens == [] and s2.calls == [] and s2.closed
+
+
+def test_stepper_is_closed_when_a_step_fails():
+    class Failing(ScriptedStepper):
+        def decode(self, rows, tokens):
+            raise RuntimeError("device fault")
+    stepper = Failing([[1, 2]])
+    with pytest.raises(RuntimeError):
+        run_batch(stepper, BatchState([0], [1], 5, ()), GenerationStats())
+    assert stepper.closed
+
+
+def test_accept_needs_one_token_per_live_row():
+    state = BatchState([0, 1], [1, 1], 3, ())
+    with pytest.raises(ValueError):
+        state.accept([1])
+
+
+def test_plan_batches():
+    # 5 requests, batches of at most 2, enough cache: in order
+    assert plan_batches([10, 20, 30, 40, 50], 16, 2, 64 * 100, 64) == [[0, 1], [2, 3], [4]]
+    # the cache bounds a batch: 100+28 tokens = 2 blocks each, 5 blocks in all
+    assert plan_batches([100, 100, 100], 29, 8, 64 * 5, 64) == [[0, 1], [2]]
+    # a prompt that ends exactly at a block's end needs the next block only for its second token
+    assert plan_batches([64, 64], 1, 8, 64 * 2, 64) == [[0, 1]]
+    assert plan_batches([64, 64], 2, 8, 64 * 2, 64) == [[0], [1]]
+    with pytest.raises(ValueError):
+        plan_batches([1000], 100, 8, 64 * 4, 64)
+    with pytest.raises(ValueError):
+        plan_batches([0], 1, 8, 64 * 4, 64)
+    assert plan_batches([], 5, 8, 640, 64) == []

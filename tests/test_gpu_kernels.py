@@ -1,0 +1,303 @@
+"""Each kernel alone against a plain torch float32 reference of the same formula, at sizes
+other than the engine's tiny configurations (odd widths, tails, many heads and groups)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from hymt2sharp_b200.kernels import ops
+    return ops
+
+
+def _tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    ops = _ops()
+    table = torch.randn(301, 70, device=DEV).to(dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 70, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.embed(out, table, ids, status)
+    assert torch.equal(out, table.float()[ids.long()]) and status[0].item() == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    out2 = torch.full((2, 70), 9.0, device=DEV)
+    ops.embed(out2, table, bad, status)
+    assert status[0].item() == 1 and torch.equal(out2[1], torch.zeros(70, device=DEV))  # flagged, nothing read outside
+
+
+@pytest.mark.parametrize("xdt, gdt, ydt", [(torch.float32, torch.float32, torch.float32),
+                                           (torch.float32, torch.bfloat16, torch.bfloat16),
+                                           (torch.float32, torch.float32, torch.bfloat16),
+                                           (torch.bfloat16, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("dim", [70, 1000, 2052])
+def test_rmsnorm(xdt, gdt, ydt, dim):
+    ops = _ops()
+    x = (torch.randn(37, dim, device=DEV) * 3).to(xdt)
+    g = (1 + 0.1 * torch.randn(dim, device=DEV)).to(gdt)
+    eps = 1e-3
+    ref = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + eps) * g.float()
+    out = torch.empty(37, dim, dtype=ydt, device=DEV)
+    ops.rmsnorm(out, x, g, eps)
+    assert torch.allclose(out.float(), ref, **_tol(ydt))
+    idx = torch.tensor([36, 0, 5], dtype=torch.int32, device=DEV)
+    out3 = torch.empty(3, dim, dtype=ydt, device=DEV)
+    ops.rmsnorm(out3, x, g, eps, idx)
+    assert torch.equal(out3, out[idx.long()])
+
+
+@pytest.mark.parametrize("adt, wdt, cdt", [(torch.float32, torch.float32, torch.float32),
+                                           (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                           (torch.bfloat16, torch.bfloat16, torch.float32),
+                                           (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("M, N, K", [(1, 67, 70), (5, 64, 64), (130, 131, 257), (64, 1000, 33)])
+def test_gemm_simt_epilogues(adt, wdt, cdt, M, N, K):
+    ops = _ops()
+    a = torch.randn(M, K, device=DEV).to(adt)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(wdt)
+    ref = a.double() @ w.double().T
+    tol = _tol(cdt)
+    out = torch.empty(M, N, dtype=cdt, device=DEV)
+    ops.gemm_simt(out, a, w[:N], ops.EPILOGUE_STORE)
+    assert torch.allclose(out.double(), ref[:, :N], **tol)
+    base = torch.randn(M, N, device=DEV).to(cdt)
+    acc = base.clone()
+    ops.gemm_simt(acc, a, w[:N], ops.EPILOGUE_ACCUMULATE)
+    assert torch.allclose(acc.double(), base.double() + ref[:, :N], **tol)
+    glu = torch.empty(M, N, dtype=cdt, device=DEV)
+    ops.gemm_simt(glu, a, w, ops.EPILOGUE_SWIGLU)
+    g, u = ref[:, :N], ref[:, N:]
+    assert torch.allclose(glu.double(), g / (1 + torch.exp(-g)) * u, **tol)
+    # row strides larger than the rows (a view into a wider matrix)
+    wide = torch.zeros(M, K + 8, device=DEV).to(adt)
+    wide[:, :K] = a
+    out2 = torch.empty(M, N, dtype=cdt, device=DEV)
+    ops.gemm_simt(out2, wide[:, :K], w[:N], ops.EPILOGUE_STORE)
+    assert torch.equal(out2, out)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    ops = _ops()
+    a = torch.randn(200, 300, device=DEV)
+    w = torch.randn(77, 300, device=DEV)
+    full = torch.empty(200, 77, device=DEV)
+    ops.gemm_simt(full, a, w)
+    one = torch.empty(1, 77, device=DEV)
+    ops.gemm_simt(one, a[131:132].contiguous(), w)
+    assert torch.equal(one[0], full[131])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    ops = _ops()
+    gu = torch.randn(9, 2 * 35, device=DEV).to(dtype)
+    out = torch.empty(9, 35, dtype=dtype, device=DEV)
+    ops.silu_mul(out, gu)
+    g, u = gu.float()[:, :35], gu.float()[:, 35:]
+    assert torch.allclose(out.float(), g / (1 + torch.exp(-g)) * u, **_tol(dtype))
+
+
+def _paged(keys, values, block_tokens, dtype, shuffle_seed=0):
+    """keys/values: list per sequence of [len, nkv, d] → cache planes with shuffled blocks, table."""
+    nkv, d = keys[0].shape[1:]
+    need = [-(-k.shape[0] // block_tokens) for k in keys]
+    total = sum(need) + 3
+    perm = np.random.default_rng(shuffle_seed).permutation(total)
+    kp = torch.full((total, nkv, block_tokens, d), 99.0, device=DEV).to(dtype)  # unused rows would poison a sum
+    vp = torch.full((total, nkv, block_tokens, d), -99.0, device=DEV).to(dtype)
+    table = torch.full((len(keys), max(need) + 1), -1, dtype=torch.int32)
+    nxt = 0
+    for s, (k, v) in enumerate(zip(keys, values)):
+        for b in range(need[s]):
+            phys = int(perm[nxt]); nxt += 1
+            table[s, b] = phys
+            chunk = slice(b * block_tokens, min((b + 1) * block_tokens, k.shape[0]))
+            n = chunk.stop - chunk.start
+            kp[phys, :, :n] = k[chunk].transpose(0, 1).to(dtype)
+            vp[phys, :, :n] = v[chunk].transpose(0, 1).to(dtype)
+    return kp, vp, table.to(DEV)
+
+
+def _ref_attention(q, k, v, new, window, scale):
+    """q [new, nh, d] are the last `new` positions of a sequence with keys k [len, nkv, d]."""
+    L, nkv, d = k.shape
+    nh = q.shape[1]
+    g = nh // nkv
+    out = torch.empty(new, nh, d, dtype=torch.float64, device=q.device)
+    for i in range(new):
+        p = L - new + i
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(nh):
+            s = (k[lo:p + 1, h // g].double() @ q[i, h].double()) * scale
+            w = torch.softmax(s, dim=0)
+            out[i, h] = w @ v[lo:p + 1, h // g].double()
+    return out.reshape(new, nh * d)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, d, window", [(8, 2, 64, 0), (5, 5, 16, 0), (20, 1, 48, 0), (6, 3, 128, 37),
+                                                (4, 2, 256, 0), (12, 4, 80, 100)])
+def test_attention_prefill_and_decode(dtype, nh, nkv, d, window):
+    ops = _ops()
+    torch.manual_seed(nh * 100 + d)
+    lens, news = [70, 1, 200, 33], [70, 1, 45, 2]   # whole prompt, single token, chunk after a prefix, 2 tokens
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    qs = [torch.randn(n, nh, d, device=DEV).to(dtype) for n in news]
+    kp, vp, table = _paged(keys, vals, 64, dtype)
+    scale = 1 / math.sqrt(d)
+    q = torch.cat([x.reshape(x.shape[0], nh * d) for x in qs])
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(news)]), dtype=torch.int32, device=DEV)
+    slots = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.zeros(sum(news), nh * d, dtype=dtype, device=DEV)
+    ops.attention_simt(out, q, kp, vp, table, cu, slots, kv, len(lens), max(news), nh, nkv, d, scale, window)
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), news[i], window, scale)
+                     for i in range(len(lens))])
+    assert torch.allclose(out.double(), ref, **_tol(dtype))
+
+    # decode with split keys: one token per sequence, partials merged in order
+    lens2 = [700, 1, 257, 64]
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens2]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens2]
+    qs = [torch.randn(1, nh, d, device=DEV).to(dtype) for _ in lens2]
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=1)
+    q = torch.cat([x.reshape(1, nh * d) for x in qs])
+    cu = torch.arange(5, dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens2, dtype=torch.int32, device=DEV)
+    splits = -(-max(lens2) // 256)
+    na, nm = ops.attention_simt_scratch(4, nh, d, splits)
+    acc = torch.full((na,), float("nan"), device=DEV)
+    ml = torch.full((nm,), float("nan"), device=DEV)
+    out = torch.zeros(4, nh * d, dtype=dtype, device=DEV)
+    ops.attention_simt(out, q, kp, vp, table, cu, slots, kv, 4, 1, nh, nkv, d, scale, window, 256, splits, acc, ml)
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, window, scale) for i in range(4)])
+    assert torch.allclose(out.double(), ref, **_tol(dtype))
+    # a padding row (slot -1) is left alone
+    slots2 = torch.tensor([0, -1, 2, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.full((4, nh * d), 5.0, dtype=dtype, device=DEV)
+    ops.attention_simt(out2, q, kp, vp, table, cu, slots2, kv, 4, 1, nh, nkv, d, scale, window, 256, splits, acc, ml)
+    assert torch.equal(out2[0], out[0]) and torch.equal(out2[2:], out[2:]) and (out2[1] == 5.0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, d, rope_dim, norm", [(8, 2, 64, 64, True), (3, 3, 16, 16, False),
+                                                        (6, 1, 48, 16, True), (4, 2, 128, 0, True)])
+def test_rope_qknorm_kv_append(dtype, nh, nkv, d, rope_dim, norm):
+    ops = _ops()
+    torch.manual_seed(d)
+    T, bt = 11, 64
+    pos = torch.tensor([0, 1, 2, 63, 64, 65, 500, 7000, 3, 4, 127], dtype=torch.int32)
+    seq = torch.tensor([0, 0, 0, 1, 1, 1, 2, 3, 4, 4, 5], dtype=torch.int32)
+    slots = torch.tensor([2, 0, 3, 1, -1, 4], dtype=torch.int32)  # batch row 4 is padding
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device=DEV).to(dtype)
+    table = torch.full((5, 120), -1, dtype=torch.int32)
+    nblocks = 0
+    for t in range(T):
+        s = int(slots[seq[t]])
+        if s >= 0 and table[s, pos[t] // bt] < 0:
+            table[s, pos[t] // bt] = nblocks
+            nblocks += 1
+    kp = torch.zeros(nblocks, nkv, bt, d, dtype=dtype, device=DEV)
+    vp = torch.zeros(nblocks, nkv, bt, d, dtype=dtype, device=DEV)
+    inv = (1.0 / (10000.0 ** (torch.arange(rope_dim // 2, dtype=torch.float32) / max(1, rope_dim // 2)))).to(DEV) \
+        if rope_dim else None
+    qg = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype) if norm else None
+    kg = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype) if norm else None
+    q_out = torch.empty(T, nh * d, dtype=dtype, device=DEV)
+    eps = 1e-5
+    ops.rope_kv(qkv, q_out, kp, vp, table.to(DEV), bt, seq.to(DEV), pos.to(DEV), slots.to(DEV), inv, rope_dim,
+                qg, kg, eps, nh, nkv, d)
+
+    x = qkv.float().reshape(T, nh + 2 * nkv, d)
+
+    def rotate(h):
+        if not rope_dim:
+            return h
+        half = rope_dim // 2
+        ang = pos.to(DEV).float()[:, None] * inv[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = h.clone()
+        out[..., :half] = h[..., :half] * c - h[..., half:rope_dim] * s
+        out[..., half:rope_dim] = h[..., :half] * s + h[..., half:rope_dim] * c
+        return out
+
+    def normed(h, g):
+        return h if g is None else h * torch.rsqrt((h ** 2).mean(-1, keepdim=True) + eps) * g.float()
+
+    q_ref = normed(rotate(x[:, :nh]), qg).reshape(T, nh * d)
+    k_ref = normed(rotate(x[:, nh:nh + nkv]), kg)
+    v_ref = x[:, nh + nkv:]
+    tol = _tol(dtype)
+    assert torch.allclose(q_out.float(), q_ref, **tol)
+    for t in range(T):
+        s = int(slots[seq[t]])
+        if s < 0:
+            continue
+        b, o = int(table[s, pos[t] // bt]), int(pos[t]) % bt
+        assert torch.allclose(kp[b, :, o].float(), k_ref[t], **tol), f"key of token {t}"
+        assert torch.allclose(vp[b, :, o].float(), v_ref[t], atol=0, rtol=0), f"value of token {t}"
+    written = sum(1 for t in range(T) if int(slots[seq[t]]) >= 0)
+    assert int((kp.float().abs().sum(-1) > 0).sum()) == written * nkv  # nothing else was touched
+    # a run that reads another layer's cache writes only q
+    q2 = torch.empty_like(q_out)
+    ops.rope_kv(qkv, q2, None, None, table.to(DEV), bt, seq.to(DEV), pos.to(DEV), slots.to(DEV), inv, rope_dim,
+                qg, kg, eps, nh, nkv, d)
+    assert torch.equal(q2, q_out)
+
+
+def test_argmax_takes_the_first_maximum():
+    ops = _ops()
+    x = torch.randn(7, 120818, device=DEV)
+    x[2, 100000] = x[2, 55] = 50.0
+    x[3, :] = -1.0
+    x[5, 120817] = 60.0
+    out = torch.full((7,), -5, dtype=torch.int32, device=DEV)
+    row_map = torch.tensor([0, 1, 2, 3, -1, 5, 6], dtype=torch.int32, device=DEV)
+    ops.argmax(out, x, row_map)
+    want = x.argmax(dim=1).tolist()
+    want[2], want[3], want[4], want[5] = 55, 0, -5, 120817
+    assert out.tolist() == want
+    wide = torch.randn(3, 1000, device=DEV)
+    view = wide[:, :509]  # rows with a stride larger than the vocabulary
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax(out, view)
+    assert out.tolist() == view.argmax(dim=1).tolist()
+
+
+def test_sampling_distribution_and_stream():
+    ops = _ops()
+    import sys, os
+    from plain.hunyuan_plain import Xoshiro256StarStar
+    vocab = 509
+    logits = torch.randn(1, vocab, device=DEV) * 2
+    probs = torch.softmax(logits[0].double() / 0.7, dim=0).cpu().numpy()
+    states = torch.zeros(3, 4, dtype=torch.int64, device=DEV)
+    seeds = torch.tensor([5, 6, 7], dtype=torch.int64, device=DEV)
+    ops.seed_rng(states, torch.arange(3, dtype=torch.int32, device=DEV), seeds)
+    ref = Xoshiro256StarStar(6)
+    assert [x & ((1 << 64) - 1) for x in states[1].tolist()] == ref.s
+    inv_t = torch.tensor([0.0, 1 / 0.7, 0.0], device=DEV)
+    row_map = torch.tensor([1], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, dtype=torch.int32, device=DEV)
+    cdf = np.cumsum(probs)
+    counts = np.zeros(vocab)
+    for i in range(3000):
+        ops.sample(out, logits, inv_t, states, row_map)
+        tok = out.item()
+        u = float(ref.next_single())
+        lo = cdf[tok - 1] if tok else 0.0
+        assert lo - 1e-5 <= u <= cdf[tok] + 1e-5, f"draw {i}: u={u} token {tok} interval [{lo}, {cdf[tok]}]"
+        counts[tok] += 1
+    top = np.argsort(-probs)[:5]
+    assert np.allclose(counts[top] / 3000, probs[top], atol=0.03)
+    assert states[0].tolist() != [0, 0, 0, 0] and [x & ((1 << 64) - 1) for x in states[1].tolist()] == ref.s
