@@ -25,3 +25,17 @@ HYMT2_API int hymt2_embed(float* out, const void* table, int table_dtype, const 
         embed_kernel<T><<<tokens, 256, 0, stream>>>(out, (const T*)table, ids, hidden, vocab, status));
     return hymt2_check_launch("embed");
 }
+
+// After a decode step: every live row of the batch is one token longer.
+__global__ void advance_decode_kernel(int* token_pos, int* kv_lens, const int* slot_ids, int rows) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= rows || slot_ids[b] < 0) return;
+    token_pos[b] += 1;
+    kv_lens[b] += 1;
+}
+
+HYMT2_API int hymt2_advance_decode(int* token_pos, int* kv_lens, const int* slot_ids, int rows, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    advance_decode_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(token_pos, kv_lens, slot_ids, rows);
+    return hymt2_check_launch("advance_decode");
+}

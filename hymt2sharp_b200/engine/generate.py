@@ -131,35 +131,47 @@ class BatchState:
 
 
 class EngineStepper:
-    """The device side of the loop for one batch: slots, the steps, the sampler."""
+    """The device side of the loop for one batch: slots, the prompts' step, then a
+    DecodeSession that keeps tokens, positions and lengths on the device."""
 
-    def __init__(self, engine, params: list, prompts: list):
-        import torch
+    def __init__(self, engine, params: list, prompts: list, max_new_tokens: int, use_graph: bool = True):
         from ..sampling.sampler import BatchSampler
         from .engine import StepEntry
-        self._torch, self._StepEntry = torch, StepEntry
+        self._StepEntry = StepEntry
         self.engine = engine
         self.prompts = prompts
+        self.max_new_tokens = max_new_tokens
+        self.use_graph = use_graph
         self.slots = engine.alloc_slots(len(prompts))
         self.sampler = BatchSampler(params, engine.device, prompts)
         self.held = set(range(len(prompts)))
+        self.session = None
+        self._first = None
 
     def prefill(self) -> list:
         entries = [self._StepEntry(s, p, [len(p) - 1]) for s, p in zip(self.slots, self.prompts)]
         logits = self.engine.step(entries)
-        return self.sampler.sample(logits, None).tolist()
+        self._first = self.sampler.sample(logits, None)
+        return self._first.tolist()
 
     def decode(self, rows: list, tokens: list) -> list:
-        torch = self._torch
-        entries = [self._StepEntry(self.slots[r], [t], [0]) for r, t in zip(rows, tokens)]
-        logits = self.engine.step(entries)
-        row_map = torch.tensor(rows, dtype=torch.int32, device=self.engine.device)
-        return self.sampler.sample(logits, row_map).tolist()
+        """One more token for the batch rows `rows` (the rows that still run), whose last tokens
+        are `tokens`: they go to the device from pinned memory, the sampled ones come back."""
+        if self.session is None:
+            from .decode_session import DecodeSession
+            longest = max(len(p) for p in self.prompts) + self.max_new_tokens
+            self.session = DecodeSession(self.engine, self.slots, self.sampler, self._first, longest, self.use_graph,
+                                         live_rows=set(self.held))
+        out = self.session.step_host(dict(zip(rows, tokens)))
+        return [out[r] for r in rows]
 
     def release(self, rows: list) -> None:
         rows = [r for r in rows if r in self.held]
         self.held.difference_update(rows)
-        self.engine.free_slots([self.slots[r] for r in rows])
+        if self.session is not None:
+            self.session.drop(rows)
+        else:
+            self.engine.free_slots([self.slots[r] for r in rows])
 
     def close(self) -> None:
         self.release(list(self.held))
@@ -208,14 +220,14 @@ def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_tok
     if len(params) != len(prompts):
         raise ValueError("one SamplingParams for every prompt is needed")
     max_batch = max_batch or engine.cache.max_slots
-    capacity = engine.cache.num_blocks * engine.cache.block_tokens
+    capacity = engine.cache.free_tokens()
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, max_batch, capacity, engine.cache.block_tokens)
     factory = stepper_factory or EngineStepper
     stats = GenerationStats()
     results = [None] * len(prompts)
     for ids in batches:
         state = BatchState(ids, [len(prompts[i]) for i in ids], max_new_tokens, stop_token_ids)
-        stepper = factory(engine, [params[i] for i in ids], [prompts[i] for i in ids])
+        stepper = factory(engine, [params[i] for i in ids], [prompts[i] for i in ids], max_new_tokens)
         run_batch(stepper, state, stats, on_tokens)
         stats.batches += 1
         for i, res in zip(ids, state.results()):

@@ -23,6 +23,8 @@ class DecoderModel:
         self.groups: list[GroupSpec] = []
         self.slots: list[MixerSlot] = []
         self.state_bytes = 0
+        # a step can be captured into a CUDA graph only if every part launches kernels and nothing else
+        self.graph_safe = all(getattr(p, "graph_safe", False) for b in self.blocks for p in b.parts())
         self._plan_memory()
 
     # -- what the checkpoint must hold -----------------------------------------

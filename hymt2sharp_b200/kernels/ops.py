@@ -39,7 +39,12 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
-def _check(rc: int, what: str) -> None:
+launches = 0  # kernels of this library launched (or captured into a graph) so far
+
+
+def _check(rc: int, what: str, kernels: int = 1) -> None:
+    global launches
+    launches += kernels
     if rc != 0:
         msg = _lib().hymt2_last_error().decode(errors="replace")
         raise KernelError(f"{what} failed ({rc}): {msg}")
@@ -65,6 +70,14 @@ def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: tor
         raise KernelError(f"embed: shapes out {tuple(out.shape)} table {tuple(table.shape)} ids {tuple(ids.shape)}")
     _check(_lib().hymt2_embed(_ptr(out), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), c_int(T),
                               c_int(H), c_int(table.shape[0]), _ptr(status), _stream()), "embed")
+
+
+def advance_decode(token_pos: torch.Tensor, kv_lens: torch.Tensor, slot_ids: torch.Tensor) -> None:
+    """After a decode step: positions and lengths of the live rows (slot >= 0) grow by one."""
+    _need(token_pos, "token_pos", torch.int32, 1); _need(kv_lens, "kv_lens", torch.int32, 1)
+    _need(slot_ids, "slot_ids", torch.int32, 1)
+    _check(_lib().hymt2_advance_decode(_ptr(token_pos), _ptr(kv_lens), _ptr(slot_ids), c_int(slot_ids.shape[0]),
+                                       _stream()), "advance_decode")
 
 
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float,
@@ -180,7 +193,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                                        _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(T),
                                        c_int(max_new_tokens), c_int(nh), c_int(nkv), c_int(d), c_float(scale),
                                        c_int(window), c_int(split_keys), c_int(max_splits), _ptr(part_acc),
-                                       _ptr(part_ml), _stream()), "attention_simt")
+                                       _ptr(part_ml), _stream()), "attention_simt", 2 if split_keys > 0 else 1)
 
 
 # ---------------------------------------------------------------------------

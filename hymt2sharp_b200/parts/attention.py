@@ -23,6 +23,8 @@ SPLIT_KEYS = 256  # decode: keys per partial, a constant so that the cut depends
 
 
 class GQAAttention:
+    graph_safe = True  # its forward only launches kernels on the current stream
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, eps: float, qk_norm: bool,
                  position: PartSpec | None, q_proj: str, k_proj: str, v_proj: str, o_proj: str,
                  q_norm: str | None = None, k_norm: str | None = None, window: int | None = None):

@@ -11,6 +11,8 @@ from .linear import compute_form
 
 
 class RMSNorm:
+    graph_safe = True  # its forward only launches kernels on the current stream
+
     def __init__(self, dim: int, eps: float, weight: str):
         self.dim, self.eps, self.weight_name = int(dim), float(eps), weight
         self.gain = None

@@ -13,6 +13,8 @@ from .linear import Linear, compute_form
 
 
 class SwiGLU:
+    graph_safe = True  # its forward only launches kernels on the current stream
+
     def __init__(self, hidden: int, intermediate: int, gate_proj: str, up_proj: str, down_proj: str):
         self.hidden, self.intermediate = int(hidden), int(intermediate)
         self.names = dict(g=gate_proj, u=up_proj, d=down_proj)

@@ -75,3 +75,17 @@ class BatchSampler:
         if self.any_filter and self.history is not None:
             ops.record_history(self.history, self.counts, out, row_map, rows)
         return out
+
+    def snapshot(self):
+        """The state that sampling changes (random streams, penalty rings), to put back later."""
+        rng = self.rng.clone() if not self.all_greedy else None
+        hist = (self.history.clone(), self.counts.clone()) if self.any_filter and self.history is not None else None
+        return rng, hist
+
+    def restore(self, snap) -> None:
+        rng, hist = snap
+        if rng is not None:
+            self.rng.copy_(rng)
+        if hist is not None:
+            self.history.copy_(hist[0])
+            self.counts.copy_(hist[1])
