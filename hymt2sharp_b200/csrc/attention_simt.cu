@@ -258,3 +258,69 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
     });
     return rc;
 }
+
+// ---------------------------------------------------------------------------
+// The entry point that allocates nothing (see hymt2_noalloc.h).
+// ---------------------------------------------------------------------------
+#include "hymt2_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+// Room for the partial results of hymt2_attention_decode_noalloc: [acc | max,sum].  In host
+// code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_noalloc_scratch[HYMT2_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {};
+
+// Once per device, with that device current: the array's address on that device.
+int noalloc_setup(int device, float** scratch) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_scratch_ptr[device]) {
+        float* s = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&s, g_noalloc_scratch);
+        if (e != cudaSuccess || !s) {
+            hymt2_set_error("attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return HYMT2_ERR_LAUNCH;
+        }
+        g_noalloc_scratch_ptr[device] = s;
+    }
+    *scratch = g_noalloc_scratch_ptr[device];
+    return HYMT2_OK;
+}
+
+}  // namespace
+
+HYMT2_API int hymt2_attention_decode_noalloc(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                             int dtype, const int* block_table, int table_stride, int block_tokens,
+                                             const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int rows,
+                                             int nh, int nkv,
+                                             int d, float scale, int window, int split_keys, int max_splits,
+                                             cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0, "attention_decode_noalloc: rows %d must be positive", rows);
+    HYMT2_REQUIRE(split_keys > 0 && max_splits > 0, "attention_decode_noalloc: split_keys and max_splits must be positive");
+    HYMT2_REQUIRE(nh > 0 && d > 0, "attention_decode_noalloc: bad sizes");
+    const long long need = (long long)rows * nh * max_splits * (d + 2);
+    HYMT2_REQUIRE(need <= HYMT2_NOALLOC_SCRATCH_FLOATS,
+                  "attention_decode_noalloc: rows %d x heads %d x splits %d x (head_dim %d + 2) = %lld floats of "
+                  "partial results exceed the built-in scratch of %d floats",
+                  rows, nh, max_splits, d, need, (int)HYMT2_NOALLOC_SCRATCH_FLOATS);
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= NOALLOC_MAX_DEVICES) {
+        hymt2_set_error("attention_decode_noalloc: no usable current device (%s)", cudaGetErrorString(e));
+        return HYMT2_ERR_LAUNCH;
+    }
+    float* scratch = nullptr;
+    const int rc = noalloc_setup(device, &scratch);
+    if (rc != HYMT2_OK) return rc;
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)rows * nh * max_splits * d;
+    return hymt2_attention_simt(out, q, k_cache, v_cache, dtype, block_table, table_stride, block_tokens, cu_seqlens,
+                                slot_ids, kv_lens, rows, rows, 1, nh, nkv, d, scale, window, split_keys, max_splits,
+                                part_acc, part_ml, stream);
+}
