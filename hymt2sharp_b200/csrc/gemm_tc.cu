@@ -1,0 +1,502 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   C = epilogue(X[T,K] · W[N,K]^T), float32 accumulation in tensor memory (TMEM).
+//
+// One CTA computes one 128 x BN tile with `tcgen05.mma` (cta_group::1, M = 128, K = 16 per
+// instruction).  Operand tiles of 64 K-elements (128 bytes a row, 128-byte swizzle) are brought
+// into shared memory by TMA (`cp.async.bulk.tensor.2d`) through a ring of stages guarded by
+// mbarriers; one thread issues the TMA loads, one thread issues the MMAs, four warps read the
+// accumulator back with `tcgen05.ld` and run the epilogue.
+//
+// Two orientations:
+//   normal   the 128-row side holds tokens, the BN side holds output features (prefill);
+//   swapped  the 128-row side holds output features (weight rows), the BN side holds tokens
+//            (BN = 16..128): a decode step streams every weight tile once at full tile height
+//            whatever the batch is.  With `splits` > 1 the K range is cut over gridDim.z; every
+//            CTA writes its partial tile to a workspace, and the CTA that arrives last at the
+//            tile's counter adds the partials in split order (so the sum does not depend on
+//            arrival order) and runs the epilogue.
+// Epilogues: store, accumulate into float32 C, SwiGLU (silu(gate) * up; W holds N gate rows,
+// then N up rows; src/HyMT2Sharp/Ops.cs:1053).  Rows and K beyond the matrices are zero-filled
+// by TMA and masked in the epilogue, so any T and N are taken; K, lda and ldw must be multiples
+// of 8 elements (TMA's 16-byte rule).
+//
+// Every wait on an mbarrier is bounded: when it gives up it sets the status word and the abort
+// flag, all roles leave their loops, TMEM is freed and the kernel returns.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int BLOCK_K = 64, UMMA_K = 16, TILE_M = 128, NUM_THREADS = 192, MAX_STAGES = 8;
+constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 21;
+
+enum { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
+
+struct GemmTcParams {
+    void* C;
+    long ldc;
+    int T, N, K;             // tokens, output features, reduction length
+    int stages;
+    int splits, k_blocks_per_split;
+    float* workspace;        // [tile][split][acc][BN][128] partial tiles (splits > 1)
+    int* counters;           // [tile] arrivals, zero between launches
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the wait gave up or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    // K-major operand, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_load(uint32_t taddr, float* v);
+template <>
+__device__ __forceinline__ void tmem_load<16>(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_load<32>(uint32_t taddr, float* v) {
+    tmem_load<16>(taddr, v);
+    tmem_load<16>(taddr + 16, v + 16);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+template <int BN, bool SWAPPED, int EPI, typename TC>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
+    constexpr int NUM_ACC = (SWAPPED && EPI == EPI_SWIGLU) ? 2 : 1;   // accumulators = A tiles per stage
+    constexpr bool SPLIT_B = !SWAPPED && EPI == EPI_SWIGLU;           // B tile = gate rows, then up rows
+    constexpr int B_TILE_BYTES = BN * BLOCK_K * 2;
+    constexpr int STAGE_BYTES = NUM_ACC * A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int ACC_COLS = NUM_ACC * BN;
+    constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+    constexpr int CH = BN >= 32 ? 32 : 16;                            // accumulator columns per epilogue chunk
+    constexpr int OUT_COLS = SPLIT_B ? BN / 2 : BN;                   // output columns that the tile covers
+    // instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s, last_s;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = p.stages;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]), done_bar = smem_u32(&bars[2 * MAX_STAGES]);
+    volatile int* abort_flag = &abort_s;
+
+    const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+    const int kb_end = min(num_k_blocks, kb_begin + p.k_blocks_per_split);
+    const int my_blocks = max(0, kb_end - kb_begin);
+    const int a_row0 = blockIdx.x * TILE_M;
+    const int b_row0 = blockIdx.y * OUT_COLS;   // swapped: first token; normal: first output feature
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(done_bar, 1);
+        abort_s = 0;
+        last_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer -------------------------------------------------------------------
+        int issued = 0;
+        for (int i = 0; i < my_blocks; i++) {
+            const int s = i % stages;
+            if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, abort_flag, p.status, 101)) break;
+            const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + NUM_ACC * A_TILE_BYTES;
+            const int k = (kb_begin + i) * BLOCK_K;
+            mbar_expect_tx(bar, STAGE_BYTES);
+            tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+            if (NUM_ACC == 2) tma_load_2d(a_dst + A_TILE_BYTES, &map_a, bar, k, p.N + a_row0);
+            if (SPLIT_B) {
+                tma_load_2d(b_dst, &map_b, bar, k, b_row0);
+                tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, bar, k, p.N + b_row0);
+            } else {
+                tma_load_2d(b_dst, &map_b, bar, k, b_row0);
+            }
+            issued = i + 1;
+        }
+        if (*abort_flag) {
+            // copies that are in flight must land before the CTA's shared memory goes away
+            for (int i = max(0, issued - stages); i < issued; i++)
+                for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full0 + 8 * (i % stages), (i / stages) & 1); t++) {}
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ---------------------------------------------------------------------
+        for (int i = 0; i < my_blocks; i++) {
+            const int s = i % stages;
+            if (!mbar_wait(full0 + 8 * s, (i / stages) & 1, abort_flag, p.status, 102)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_src = tiles + s * STAGE_BYTES, b_src = a_src + NUM_ACC * A_TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                const uint64_t bdesc = smem_desc_sw128(b_src + k * UMMA_K * 2);
+                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                umma_bf16(tmem_base, smem_desc_sw128(a_src + k * UMMA_K * 2), bdesc, IDESC, acc);
+                if (NUM_ACC == 2)
+                    umma_bf16(tmem_base + BN, smem_desc_sw128(a_src + A_TILE_BYTES + k * UMMA_K * 2), bdesc, IDESC, acc);
+            }
+            umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs have read it
+        }
+        umma_commit(done_bar);             // the accumulator is complete once all MMAs are done
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 --------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                   // row of the tile that this thread owns
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103) : true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TC* C = (TC*)p.C;
+
+        // one chunk of CH accumulator columns: g (and u for SwiGLU) -> C
+        auto emit = [&](int c, const float* g, const float* u) {
+            if (SWAPPED) {
+                const int n = a_row0 + row;                    // output feature
+                if (n >= p.N) return;
+#pragma unroll
+                for (int j = 0; j < CH; j++) {
+                    const int t = b_row0 + c + j;              // token
+                    if (t >= p.T) break;
+                    TC* dst = C + (size_t)t * p.ldc + n;
+                    if (EPI == EPI_STORE) *dst = from_float<TC>(g[j]);
+                    else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(to_float(*dst) + g[j]);
+                    else *dst = from_float<TC>(silu_mul(g[j], u[j]));
+                }
+            } else {
+                const int m = a_row0 + row;                    // token
+                if (m >= p.T) return;
+                const int n0 = b_row0 + c;                     // first output feature of the chunk
+                TC* dst = C + (size_t)m * p.ldc + n0;
+                float o[CH];
+#pragma unroll
+                for (int j = 0; j < CH; j++) o[j] = EPI == EPI_SWIGLU ? silu_mul(g[j], u[j]) : g[j];
+                const bool vec = n0 + CH <= p.N && (((uintptr_t)dst) & 15) == 0;
+                if (vec) {
+                    if constexpr (sizeof(TC) == 4) {
+                        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                        for (int j = 0; j < CH / 4; j++) {
+                            float4 v = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                            if (EPI == EPI_ACCUMULATE) {
+                                const float4 old = d4[j];
+                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                            }
+                            d4[j] = v;
+                        }
+                    } else {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                        for (int j = 0; j < CH / 8; j++) {
+                            __nv_bfloat162 h[4];
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                float a = o[8 * j + 2 * q], b = o[8 * j + 2 * q + 1];
+                                if (EPI == EPI_ACCUMULATE) {
+                                    a += to_float(dst[8 * j + 2 * q]);
+                                    b += to_float(dst[8 * j + 2 * q + 1]);
+                                }
+                                h[q] = __floats2bfloat162_rn(a, b);
+                            }
+                            d4[j] = *reinterpret_cast<uint4*>(h);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CH; j++) {
+                        if (n0 + j >= p.N) break;
+                        dst[j] = from_float<TC>(EPI == EPI_ACCUMULATE ? to_float(dst[j]) + o[j] : o[j]);
+                    }
+                }
+            }
+        };
+
+        if (p.splits == 1) {
+            if (ok) {
+                for (int c = 0; c < OUT_COLS; c += CH) {
+                    float g[CH], u[CH];
+                    tmem_load<CH>(lane_addr + c, g);
+                    if (EPI == EPI_SWIGLU) tmem_load<CH>(lane_addr + (SWAPPED ? BN : BN / 2) + c, u);
+                    emit(c, g, u);
+                }
+            }
+        } else {
+            // partial tile -> workspace [tile][split][acc][column][row]; the last arrival reduces
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            float* ws_tile = p.workspace + (size_t)tile * p.splits * (ACC_COLS * TILE_M);
+            float* mine = ws_tile + (size_t)blockIdx.z * (ACC_COLS * TILE_M);
+            for (int c = 0; c < ACC_COLS; c += CH) {
+                float g[CH];
+                if (ok && my_blocks > 0) tmem_load<CH>(lane_addr + c, g);
+                else {
+#pragma unroll
+                    for (int j = 0; j < CH; j++) g[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < CH; j++) mine[(size_t)(c + j) * TILE_M + row] = g[j];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                const int arrived = atomicAdd(&p.counters[tile], 1);
+                last_s = arrived == p.splits - 1;
+                if (last_s) p.counters[tile] = 0;              // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (last_s) {
+                __threadfence();
+                for (int c = 0; c < OUT_COLS; c += CH) {
+                    float g[CH], u[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; j++) { g[j] = 0.f; u[j] = 0.f; }
+                    for (int s = 0; s < p.splits; s++) {       // split order: the sum is the same every time
+                        const float* part = ws_tile + (size_t)s * (ACC_COLS * TILE_M);
+#pragma unroll
+                        for (int j = 0; j < CH; j++) {
+                            g[j] += __ldcg(part + (size_t)(c + j) * TILE_M + row);
+                            if (EPI == EPI_SWIGLU) u[j] += __ldcg(part + (size_t)(BN + c + j) * TILE_M + row);
+                        }
+                    }
+                    emit(c, g, u);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row stride ld (elements); boxes of 64 x box_rows, 128-byte swizzle,
+// zeros outside the matrix.
+bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool SWAPPED, int EPI, typename TC>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+    auto kernel = gemm_tc_kernel<BN, SWAPPED, EPI, TC>;
+    static bool configured = false;   // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+        configured = true;
+    }
+    kernel<<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+    return hymt2_check_launch("gemm_tc");
+}
+
+template <int BN, bool SWAPPED>
+int dispatch_epilogue(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, dim3 grid, size_t smem,
+                      int epilogue, int c_dtype, cudaStream_t stream) {
+    if (epilogue == EPI_STORE && c_dtype == HYMT2_BF16) return launch<BN, SWAPPED, EPI_STORE, __nv_bfloat16>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_STORE && c_dtype == HYMT2_F32) return launch<BN, SWAPPED, EPI_STORE, float>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_ACCUMULATE && c_dtype == HYMT2_F32) return launch<BN, SWAPPED, EPI_ACCUMULATE, float>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_SWIGLU && c_dtype == HYMT2_BF16) return launch<BN, SWAPPED, EPI_SWIGLU, __nv_bfloat16>(ma, mb, p, grid, smem, stream);
+    hymt2_set_error("gemm_tc: epilogue %d with output type %d is not built", epilogue, c_dtype);
+    return HYMT2_ERR_ARGUMENT;
+}
+
+struct Plan {
+    bool swapped;
+    int bn, splits, k_blocks_per_split, stages;
+    dim3 grid;
+    size_t smem, workspace_floats;
+    int tiles;
+};
+
+bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
+    const int num_k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    Plan& pl = *plan;
+    pl.swapped = T <= 128;
+    pl.splits = 1;
+    int num_acc = 1;
+    if (pl.swapped) {
+        pl.bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+        num_acc = epilogue == EPI_SWIGLU ? 2 : 1;
+        const int tiles = (N + TILE_M - 1) / TILE_M;
+        pl.grid = dim3(tiles, 1, 1);
+        // too few tiles to pull the whole memory bandwidth: cut K so that about one wave of CTAs runs;
+        // the cut depends on N and K only, never on the number of tokens
+        if (tiles < sm_count / 2) {
+            int want = sm_count / tiles;
+            want = want > 8 ? 8 : want;
+            while (want > 1 && num_k_blocks / want < 2) want--;
+            pl.splits = want;
+        }
+        pl.tiles = tiles;
+    } else {
+        pl.bn = 128;
+        const int out_cols = epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn;
+        pl.grid = dim3((T + TILE_M - 1) / TILE_M, (N + out_cols - 1) / out_cols, 1);
+        pl.tiles = pl.grid.x * pl.grid.y;
+    }
+    pl.k_blocks_per_split = (num_k_blocks + pl.splits - 1) / pl.splits;
+    pl.splits = (num_k_blocks + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
+    pl.grid.z = pl.splits;
+    const int stage_bytes = num_acc * A_TILE_BYTES + pl.bn * BLOCK_K * 2;
+    const int budget = pl.swapped ? 200 * 1024 : 100 * 1024;   // normal: two CTAs share an SM
+    int stages = budget / stage_bytes;
+    stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
+    if (stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
+    pl.stages = stages;
+    pl.smem = (size_t)stages * stage_bytes + 1024;
+    pl.workspace_floats = pl.splits > 1 ? (size_t)pl.tiles * pl.splits * num_acc * pl.bn * TILE_M : 0;
+    return true;
+}
+
+int sm_count_of_current_device() {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+    return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this problem, and what scratch it wants:
+// workspace_floats of float32 and counters ints (zeroed once; the kernel leaves them zero).
+HYMT2_API int hymt2_gemm_tc_plan(int T, int N, int K, int epilogue, long* workspace_floats, int* counters) {
+    Plan pl;
+    make_plan(T, N, K, epilogue, sm_count_of_current_device(), &pl);
+    *workspace_floats = (long)pl.workspace_floats;
+    *counters = pl.splits > 1 ? pl.tiles : 0;
+    return HYMT2_OK;
+}
+
+// C[T,N] (ldc) = epilogue(X[T,K] (lda) · W[N,K]^T (ldw)), X and W bfloat16; for SwiGLU W has 2N rows.
+HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
+                            long ldc, int epilogue, float* workspace, long workspace_floats, int* counters,
+                            int num_counters, int* status, cudaStream_t stream) {
+    if (T == 0 || N == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
+    HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K, lda and ldw must be multiples of 8 (K=%d lda=%ld ldw=%ld)", K, lda, ldw);
+    HYMT2_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+    HYMT2_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tc: unknown epilogue %d", epilogue);
+    HYMT2_REQUIRE(status != nullptr, "gemm_tc: a status word is needed");
+    Plan pl;
+    make_plan(T, N, K, epilogue, sm_count_of_current_device(), &pl);
+    HYMT2_REQUIRE(pl.grid.y <= 65535 && pl.grid.x <= 2147483647u, "gemm_tc: grid too large");
+    if (pl.splits > 1)
+        HYMT2_REQUIRE(workspace && counters && workspace_floats >= (long)pl.workspace_floats && num_counters >= pl.tiles,
+                      "gemm_tc: the split needs %zu floats of workspace and %d counters", pl.workspace_floats, pl.tiles);
+    const long w_rows = epilogue == EPI_SWIGLU ? 2L * N : N;
+    CUtensorMap ma, mb;
+    bool ok;
+    if (pl.swapped) {
+        ok = make_map(&ma, W, w_rows, K, ldw, TILE_M) && make_map(&mb, X, T, K, lda, pl.bn);
+    } else {
+        ok = make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, w_rows, K, ldw, epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn);
+    }
+    HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
+    GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, workspace, counters, status};
+    if (pl.swapped) {
+        switch (pl.bn) {
+            case 16: return dispatch_epilogue<16, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            case 32: return dispatch_epilogue<32, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            case 64: return dispatch_epilogue<64, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            default: return dispatch_epilogue<128, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+        }
+    }
+    return dispatch_epilogue<128, false>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+}

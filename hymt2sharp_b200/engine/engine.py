@@ -16,7 +16,7 @@ import torch
 
 from ..cache import PagedCache
 from ..config.registry import load_config
-from ..kernels import build as kernel_build
+from ..kernels import build as kernel_build, ops
 from ..parts.base import StepContext
 from ..weights.loader import load_checkpoint
 from .model import DecoderModel
@@ -107,7 +107,7 @@ class Engine:
             self.cache = PagedCache(self.model.groups, self.dtype, self.device, capacity_tokens=max_tokens,
                                     block_tokens=block_tokens, max_slots=max_batch,
                                     state_bytes=self.model.state_bytes, max_sequence_tokens=max_sequence_tokens)
-            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            self.status = ops.device_status(self.device)
             self._meta = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.vocab = spec.vocab
         self.steps_run = 0

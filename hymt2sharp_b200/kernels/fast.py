@@ -7,7 +7,12 @@ import torch
 
 
 def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int) -> bool:
-    return False
+    """bfloat16 operands with 16-byte aligned rows go to the tcgen05 kernel; anything else is refused."""
+    from . import ops
+    if not ops.gemm_tc_supported(out, x, w, epilogue):
+        return False
+    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device))
+    return True
 
 
 def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale, window) -> bool:

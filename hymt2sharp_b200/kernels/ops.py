@@ -125,6 +125,74 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int
                                   c_int(epilogue), _stream()), "gemm_simt")
 
 
+_status: dict = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The int32[4] status word of a device: kernels set [0] when a device-side check fails or a
+    bounded wait gives up (1: token id outside the table; 101-103: a wait of the tensor-core GEMM)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+_tc_scratch: dict = {}   # device index -> (workspace float32, counters int32, earlier tensors kept alive)
+
+
+def _tc_workspace(device: torch.device, floats: int, counters: int):
+    """Scratch of the split-K tensor-core GEMM: partial tiles and per-tile arrival counters.  One
+    pair per device, shared by all calls (they run in stream order); it only ever grows, and what it
+    replaced stays alive because captured graphs may still point at it."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws, cnt, old = _tc_scratch.get(key, (None, None, []))
+    if ws is None or ws.numel() < floats or cnt.numel() < counters:
+        if ws is not None:
+            old = old + [ws, cnt]
+        ws = torch.empty(max(floats, 8 << 20), dtype=torch.float32, device=device)
+        cnt = torch.zeros(max(counters, 1 << 14), dtype=torch.int32, device=device)
+        _tc_scratch[key] = (ws, cnt, old)
+    return ws, cnt
+
+
+def gemm_tc_supported(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int) -> bool:
+    """Whether the tcgen05 kernel takes these operands (types, alignment, the epilogue's output type)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    if a.dim() != 2 or w.dim() != 2 or out.dim() != 2 or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        return False
+    K = a.shape[1]
+    if K % 8 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    if epilogue == EPILOGUE_STORE:
+        return out.dtype in (torch.bfloat16, torch.float32)
+    if epilogue == EPILOGUE_ACCUMULATE:
+        return out.dtype == torch.float32
+    return out.dtype == torch.bfloat16
+
+
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor) -> None:
+    """out[T, N] = epilogue(a[T, K] @ w[N, K]^T) on the tcgen05 tensor cores (bfloat16 operands,
+    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows."""
+    T, N = out.shape
+    K = a.shape[1]
+    rows_w = 2 * N if epilogue == EPILOGUE_SWIGLU else N
+    if a.shape[0] != T or w.shape != (rows_w, K) or not gemm_tc_supported(out, a, w, epilogue):
+        raise KernelError(f"gemm_tc: operands out {tuple(out.shape)} {out.dtype} a {tuple(a.shape)} {a.dtype} "
+                          f"w {tuple(w.shape)} {w.dtype} epilogue {epilogue} are not taken")
+    floats, counters = ctypes.c_long(0), c_int(0)
+    _check(_lib().hymt2_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(epilogue), ctypes.byref(floats),
+                                     ctypes.byref(counters)), "gemm_tc_plan", 0)
+    ws = cnt = None
+    if floats.value:
+        ws, cnt = _tc_workspace(out.device, floats.value, counters.value)
+    _check(_lib().hymt2_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(T), c_int(N), c_int(K),
+                                c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)), c_int(epilogue),
+                                _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(cnt),
+                                c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream()), "gemm_tc")
+
+
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,
             block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor,
             slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int, q_gain: torch.Tensor | None,

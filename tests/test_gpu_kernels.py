@@ -301,3 +301,55 @@ def test_sampling_distribution_and_stream():
     top = np.argsort(-probs)[:5]
     assert np.allclose(counts[top] / 3000, probs[top], atol=0.03)
     assert states[0].tolist() != [0, 0, 0, 0] and [x & ((1 << 64) - 1) for x in states[1].tolist()] == ref.s
+
+
+# T <= 128 runs swapped (weights on the 128-row side, split K when there are few tiles),
+# larger T runs normal; sizes with tails in T, N and K (K only needs to be a multiple of 8)
+@pytest.mark.parametrize("T, N, K", [(1, 1000, 200), (8, 256, 128), (16, 2048, 2048), (33, 130, 72), (64, 384, 6144),
+                                     (100, 3072, 512), (128, 128, 64), (129, 1000, 200), (300, 384, 256),
+                                     (1000, 520, 1032)])
+def test_gemm_tcgen05_epilogues(T, N, K):
+    ops = _ops()
+    torch.manual_seed(T + N)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    a = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    for cdt in (torch.float32, torch.bfloat16):
+        out = torch.full((T, N), 7.0, dtype=cdt, device=DEV)
+        ops.gemm_tc(out, a, w[:N], ops.EPILOGUE_STORE, status)
+        assert torch.allclose(out.double(), ref[:, :N], **_tol(cdt)), f"store {cdt}"
+    base = torch.randn(T, N, device=DEV)
+    acc = base.clone()
+    ops.gemm_tc(acc, a, w[:N], ops.EPILOGUE_ACCUMULATE, status)
+    assert torch.allclose(acc.double(), base.double() + ref[:, :N], rtol=2e-5, atol=2e-5)
+    glu = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(glu, a, w, ops.EPILOGUE_SWIGLU, status)
+    g, u = ref[:, :N], ref[:, N:]
+    assert torch.allclose(glu.double(), g / (1 + torch.exp(-g)) * u, **_tol(torch.bfloat16))
+    # twice the same call gives the same bits (the split sum does not depend on arrival order)
+    acc2 = base.clone()
+    ops.gemm_tc(acc2, a, w[:N], ops.EPILOGUE_ACCUMULATE, status)
+    assert torch.equal(acc, acc2)
+    # a view with a larger row stride; an output with a larger row stride
+    wide = torch.zeros(T, K + 16, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = a
+    big = torch.zeros(T, N + 5, device=DEV)
+    ops.gemm_tc(big[:, :N], wide[:, :K], w[:N], ops.EPILOGUE_STORE, status)
+    assert torch.allclose(big[:, :N].double(), ref[:, :N], rtol=2e-5, atol=2e-5) and float(big[:, N:].abs().sum()) == 0
+    assert status.tolist() == [0, 0, 0, 0]
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_take():
+    ops = _ops()
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    a = torch.randn(4, 100, device=DEV).to(torch.bfloat16)   # K = 100 is no multiple of 8
+    w = torch.randn(16, 100, device=DEV).to(torch.bfloat16)
+    out = torch.empty(4, 16, device=DEV)
+    assert not ops.gemm_tc_supported(out, a, w, ops.EPILOGUE_STORE)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc(out, a, w, ops.EPILOGUE_STORE, status)
+    assert not ops.gemm_tc_supported(out, a.float(), w.float(), ops.EPILOGUE_STORE)   # the 32-bit path never goes here
+    from hymt2sharp_b200.parts.linear import matmul
+    matmul(out, a, w, ops.EPILOGUE_STORE)   # the general kernel takes it
+    assert torch.allclose(out.double(), a.double() @ w.double().T, rtol=2e-5, atol=2e-5)
