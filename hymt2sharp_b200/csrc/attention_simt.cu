@@ -207,6 +207,19 @@ __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
 
 }  // namespace
 
+// The merge alone, for other kernels that write partials in the same layout
+// (part_acc [token, head, split, d], part_ml [token, head, split, (max, sum)]).
+int hymt2_attention_merge_launch(void* out, int dtype, const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
+                                 float* part_acc, float* part_ml, int tokens, int nh, int d, int window, int split_keys,
+                                 int max_splits, cudaStream_t stream) {
+    AttnParams p{};
+    p.out = out; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
+    p.part_acc = part_acc; p.part_ml = part_ml; p.nh = nh; p.d = d; p.window = window;
+    p.split_keys = split_keys; p.max_splits = max_splits;
+    HYMT2_DISPATCH_DTYPE(dtype, T, (attention_merge_kernel<T><<<tokens * nh, 64, 0, stream>>>(p, tokens)));
+    return hymt2_check_launch("attention_merge");
+}
+
 // Sizes of the scratch that a split run needs, in floats: acc then ml.
 HYMT2_API int hymt2_attention_simt_scratch(int tokens, int nh, int d, int max_splits, long* acc_floats, long* ml_floats) {
     *acc_floats = (long)tokens * nh * max_splits * d;

@@ -15,5 +15,21 @@ def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: in
     return True
 
 
+DECODE_CHUNK_KEYS = 256  # keys per partial of the decode kernel, a constant of the kernel
+
+
 def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale, window) -> bool:
+    """bfloat16 decode steps with head_dim 64 or 128 go to the streaming decode kernel."""
+    from . import ops
+    bt = k_plane.shape[2]
+    if out.dtype != torch.bfloat16 or d not in (64, 128) or bt & (bt - 1):
+        return False
+    if ctx.decode:
+        splits = max(1, -(-ctx.max_kv_len // DECODE_CHUNK_KEYS))
+        na, nm = ops.attention_simt_scratch(ctx.num_tokens, nh, d, splits)
+        acc = torch.empty(na, dtype=torch.float32, device=out.device)
+        ml = torch.empty(nm, dtype=torch.float32, device=out.device)
+        ops.attention_decode(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens,
+                             nh, nkv, d, scale, window, splits, acc, ml)
+        return True
     return False

@@ -264,6 +264,32 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                                        _ptr(part_ml), _stream()), "attention_simt", 2 if split_keys > 0 else 1)
 
 
+def attention_decode(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                     block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor,
+                     nh: int, nkv: int, d: int, scale: float, window: int, max_splits: int,
+                     part_acc: torch.Tensor, part_ml: torch.Tensor) -> None:
+    """bfloat16 decode attention (one new token per row) that streams the cache once per kv head;
+    head_dim 64 or 128.  The partials go through part_acc / part_ml (sizes as attention_simt_scratch)."""
+    _need(out, "out", torch.bfloat16, 2); _need(q, "q", torch.bfloat16, 2)
+    _need(k_plane, "k_plane", torch.bfloat16, 4); _need(v_plane, "v_plane", torch.bfloat16, 4)
+    rows = out.shape[0]
+    if out.shape[1] != nh * d or q.shape[1] != nh * d or q.shape[0] < rows or k_plane.shape[1] != nkv \
+            or k_plane.shape[3] != d or v_plane.shape != k_plane.shape:
+        raise KernelError(f"attention_decode: shapes out {tuple(out.shape)} q {tuple(q.shape)} k {tuple(k_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    need_acc, need_ml = attention_simt_scratch(rows, nh, d, max_splits)
+    _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+        raise KernelError("attention_decode: the scratch for the partials is too small")
+    _check(_lib().hymt2_attention_decode(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
+                                         c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens),
+                                         _ptr(slot_ids), _ptr(kv_lens), c_int(rows), c_int(nh), c_int(nkv), c_int(d),
+                                         c_float(scale), c_int(window), c_int(max_splits), _ptr(part_acc),
+                                         _ptr(part_ml), _stream()), "attention_decode", 2)
+
+
 # ---------------------------------------------------------------------------
 def _logits_ok(logits: torch.Tensor, what: str) -> None:
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:

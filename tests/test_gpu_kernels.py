@@ -353,3 +353,34 @@ def test_gemm_tcgen05_refuses_what_it_cannot_take():
     from hymt2sharp_b200.parts.linear import matmul
     matmul(out, a, w, ops.EPILOGUE_STORE)   # the general kernel takes it
     assert torch.allclose(out.double(), a.double() @ w.double().T, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("nh, nkv, d, window", [(16, 4, 128, 0), (8, 2, 64, 0), (6, 2, 64, 300), (5, 5, 128, 0),
+                                                (12, 2, 128, 0), (8, 8, 64, 70)])
+def test_attention_decode_streaming(nh, nkv, d, window):
+    """The bfloat16 decode kernel against the float64 reference, lengths around its chunks of 256
+    keys and the cache's blocks of 64, a padding row, and a poisoned cache beyond the lengths."""
+    ops = _ops()
+    torch.manual_seed(nh + d)
+    dtype = torch.bfloat16
+    lens = [1, 64, 255, 256, 257, 700, 1025, 90]
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    qs = [torch.randn(1, nh, d, device=DEV).to(dtype) for _ in lens]
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=3)   # rows past a length hold 99 / -99
+    rows = len(lens)
+    q = torch.cat([x.reshape(1, nh * d) for x in qs])
+    cu = torch.arange(rows + 1, dtype=torch.int32, device=DEV)
+    slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+    slots[7] = -1
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    splits = -(-max(lens) // 256) + 2   # more chunks than any row needs, as in a captured graph
+    na, nm = ops.attention_simt_scratch(rows, nh, d, splits)
+    acc = torch.full((na,), float("nan"), device=DEV)
+    ml = torch.full((nm,), float("nan"), device=DEV)
+    out = torch.full((rows, nh * d), 5.0, dtype=dtype, device=DEV)
+    ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, window, splits, acc, ml)
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, window, scale) for i in range(rows)])
+    assert torch.allclose(out[:7].double(), ref[:7], **_tol(dtype))
+    assert (out[7] == 5.0).all()   # the padding row is left alone
