@@ -28,8 +28,10 @@ struct DecodeParams {
     const int* block_table;
     const int* slot_ids;
     const int* kv_lens;
+    __nv_bfloat16* out;            // [rows, nh * d]
     float* part_acc;               // [rows, nh, max_splits, d]
     float* part_ml;                // [rows, nh, max_splits, 2]
+    int* counters;                 // [rows, nkv * groups] arrivals of a row's chunks, zero between launches
     int table_stride, block_shift, nh, nkv, window, max_splits;   // block_tokens = 1 << block_shift
     float scale;
 };
@@ -59,6 +61,8 @@ template <int D, int G>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(DecodeParams p) {
     constexpr int E = D / LANES_PER_KEY;   // elements of a key that one lane holds
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, b = blockIdx.z;
     const int slot = p.slot_ids[b];
     if (slot < 0) return;
@@ -197,44 +201,67 @@ attention_decode_kernel(DecodeParams p) {
         p.part_acc[row * D + x] = a;
         if (x == 0) { p.part_ml[row * 2] = M; p.part_ml[row * 2 + 1] = L; }
     }
+
+    // the chunk that arrives last folds all chunks of its heads, in chunk order
+    const int s_begin = lo / CHUNK_KEYS, s_end = pos / CHUNK_KEYS + 1;
+    __shared__ int last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = p.counters + (size_t)b * gridDim.y + blockIdx.y;
+        const int arrived = atomicAdd(counter, 1);
+        last_s = arrived == s_end - s_begin - 1;
+        if (last_s) *counter = 0;
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+        const int h = i / D, x = i - h * D;
+        const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits;
+        float M = -INFINITY;
+        for (int s = s_begin; s < s_end; s++) M = fmaxf(M, __ldcg(p.part_ml + (row + s) * 2));
+        float L = 0.f, a = 0.f;
+        for (int s = s_begin; s < s_end; s++) {
+            const float c = expf(__ldcg(p.part_ml + (row + s) * 2) - M);
+            L += __ldcg(p.part_ml + (row + s) * 2 + 1) * c;
+            a = fmaf(__ldcg(p.part_acc + (row + s) * D + x), c, a);
+        }
+        p.out[((size_t)b * p.nh + head0 + h) * D + x] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
+    }
 }
 
 template <int D>
 int launch_d(const DecodeParams& p, int rows, int g, int splits, cudaStream_t stream) {
     const int G = g % 4 == 0 ? 4 : g % 2 == 0 ? 2 : 1;
     dim3 grid(splits, p.nkv * (g / G), rows);
-    if (G == 4) attention_decode_kernel<D, 4><<<grid, WARPS * 32, 0, stream>>>(p);
-    else if (G == 2) attention_decode_kernel<D, 2><<<grid, WARPS * 32, 0, stream>>>(p);
-    else attention_decode_kernel<D, 1><<<grid, WARPS * 32, 0, stream>>>(p);
+    if (G == 4) launch_pdl(attention_decode_kernel<D, 4>, grid, dim3(WARPS * 32), 0, stream, p);
+    else if (G == 2) launch_pdl(attention_decode_kernel<D, 2>, grid, dim3(WARPS * 32), 0, stream, p);
+    else launch_pdl(attention_decode_kernel<D, 1>, grid, dim3(WARPS * 32), 0, stream, p);
     return hymt2_check_launch("attention_decode");
 }
 
 }  // namespace
 
-// defined in attention_simt.cu: folds the partials of a decode step in chunk order
-int hymt2_attention_merge_launch(void* out, int dtype, const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
-                                 float* part_acc, float* part_ml, int tokens, int nh, int d, int window, int split_keys,
-                                 int max_splits, cudaStream_t stream);
-
 // out, q: [rows, nh * d] bfloat16; one new token per row.  max_splits >= ceil(longest kv_len / 256);
-// part_acc holds rows*nh*max_splits*d floats, part_ml rows*nh*max_splits*2.
+// part_acc holds rows*nh*max_splits*d floats, part_ml rows*nh*max_splits*2, counters rows*nh ints
+// that are zero before the first launch (the kernel leaves them zero).
 HYMT2_API int hymt2_attention_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* block_table, int table_stride, int block_tokens, const int* cu_seqlens,
                                      const int* slot_ids, const int* kv_lens, int rows, int nh, int nkv, int d, float scale,
-                                     int window, int max_splits, float* part_acc, float* part_ml, cudaStream_t stream) {
+                                     int window, int max_splits, float* part_acc, float* part_ml, int* counters,
+                                     cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad sizes");
     HYMT2_REQUIRE(d == 64 || d == 128, "attention_decode: head_dim %d is not taken (64 and 128 are)", d);
-    HYMT2_REQUIRE(max_splits > 0 && part_acc && part_ml, "attention_decode: scratch for the partials is needed");
+    HYMT2_REQUIRE(max_splits > 0 && part_acc && part_ml && counters, "attention_decode: scratch for the partials is needed");
     int block_shift = 0;
     while ((1 << block_shift) < block_tokens) block_shift++;
     HYMT2_REQUIRE((1 << block_shift) == block_tokens, "attention_decode: block_tokens %d must be a power of two", block_tokens);
     HYMT2_REQUIRE(rows <= 65535 && nkv * (nh / nkv) <= 65535, "attention_decode: grid too large");
     DecodeParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
-                   slot_ids, kv_lens, part_acc, part_ml, table_stride, block_shift, nh, nkv, window, max_splits, scale};
+                   slot_ids, kv_lens, (__nv_bfloat16*)out, part_acc, part_ml, counters, table_stride, block_shift, nh, nkv, window, max_splits, scale};
     const int g = nh / nkv;
-    int rc = d == 128 ? launch_d<128>(p, rows, g, max_splits, stream) : launch_d<64>(p, rows, g, max_splits, stream);
-    if (rc != HYMT2_OK) return rc;
-    return hymt2_attention_merge_launch(out, HYMT2_BF16, cu_seqlens, slot_ids, kv_lens, part_acc, part_ml, rows, nh, d,
-                                        window, CHUNK_KEYS, max_splits, stream);
+    (void)cu_seqlens;
+    return d == 128 ? launch_d<128>(p, rows, g, max_splits, stream) : launch_d<64>(p, rows, g, max_splits, stream);
 }

@@ -86,6 +86,33 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched through launch_pdl may start while the
+// kernel before it in the stream still runs.  It must call pdl_wait() before it touches
+// anything that an earlier kernel wrote (or will overwrite something an earlier kernel reads);
+// what it does before that (set-up, loads of weights) overlaps the earlier kernel's tail.
+// pdl_launch_dependents() lets the next kernel's blocks be scheduled early.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool hymt2_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = hymt2_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Dispatch on a runtime dtype code to a typed lambda-like macro body.
 #define HYMT2_DISPATCH_DTYPE(code, T, ...)                                   \
     do {                                                                     \

@@ -26,3 +26,9 @@ HYMT2_API const char* hymt2_last_error() { return g_last_error; }
 
 // Compiled for this architecture; the Python side checks it against the device.
 HYMT2_API int hymt2_compiled_arch() { return 100; }
+
+static int g_pdl_enabled = 1;
+bool hymt2_pdl_enabled() { return g_pdl_enabled != 0; }
+
+// Programmatic dependent launch of the decode kernels on (default) or off.
+HYMT2_API void hymt2_set_pdl(int on) { g_pdl_enabled = on; }

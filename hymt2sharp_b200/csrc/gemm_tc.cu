@@ -131,6 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
+    pdl_launch_dependents();
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
@@ -167,21 +168,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer -------------------------------------------------------------------
-        int issued = 0;
-        for (int i = 0; i < my_blocks; i++) {
+        // Weights do not depend on the kernel before this one: the first ring of weight tiles is
+        // requested at once, then the producer waits for that kernel and requests the activations.
+        const bool weights_are_a = SWAPPED;
+        auto load_weights = [&](int i) {
             const int s = i % stages;
-            if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, abort_flag, p.status, 101)) break;
             const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + NUM_ACC * A_TILE_BYTES;
             const int k = (kb_begin + i) * BLOCK_K;
-            mbar_expect_tx(bar, STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, bar, k, a_row0);
-            if (NUM_ACC == 2) tma_load_2d(a_dst + A_TILE_BYTES, &map_a, bar, k, p.N + a_row0);
-            if (SPLIT_B) {
+            if (weights_are_a) {
+                tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+                if (NUM_ACC == 2) tma_load_2d(a_dst + A_TILE_BYTES, &map_a, bar, k, p.N + a_row0);
+            } else if (SPLIT_B) {
                 tma_load_2d(b_dst, &map_b, bar, k, b_row0);
                 tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, bar, k, p.N + b_row0);
             } else {
                 tma_load_2d(b_dst, &map_b, bar, k, b_row0);
             }
+        };
+        auto load_activations = [&](int i) {
+            const int s = i % stages;
+            const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + NUM_ACC * A_TILE_BYTES;
+            const int k = (kb_begin + i) * BLOCK_K;
+            if (weights_are_a) tma_load_2d(b_dst, &map_b, bar, k, b_row0);
+            else tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+        };
+        const int ahead = min(stages, my_blocks);
+        for (int i = 0; i < ahead; i++) {   // fresh stages: nothing to wait for
+            mbar_expect_tx(full0 + 8 * (i % stages), STAGE_BYTES);
+            load_weights(i);
+        }
+        pdl_wait();
+        for (int i = 0; i < ahead; i++) load_activations(i);
+        int issued = ahead;
+        for (int i = ahead; i < my_blocks; i++) {
+            const int s = i % stages;
+            if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, abort_flag, p.status, 101)) break;
+            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            load_weights(i);
+            load_activations(i);
             issued = i + 1;
         }
         if (*abort_flag) {
@@ -212,6 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                   // row of the tile that this thread owns
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        pdl_wait();   // C, the workspace and the counters may still be in use by the kernel before
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         TC* C = (TC*)p.C;
@@ -380,7 +405,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, 
         if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
         configured = true;
     }
-    kernel<<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+    cudaError_t e = launch_pdl(kernel, grid, dim3(NUM_THREADS), smem, stream, ma, mb, p);
+    if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("gemm_tc");
 }
 
@@ -433,7 +459,7 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     pl.splits = (num_k_blocks + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
     pl.grid.z = pl.splits;
     const int stage_bytes = num_acc * A_TILE_BYTES + pl.bn * BLOCK_K * 2;
-    const int budget = pl.swapped ? 200 * 1024 : 100 * 1024;   // normal: two CTAs share an SM
+    const int budget = 100 * 1024;   // two CTAs share an SM: of one kernel, or of a kernel and the next one
     int stages = budget / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
     if (stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;

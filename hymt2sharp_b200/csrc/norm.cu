@@ -8,6 +8,8 @@ template <typename TX, typename TW, typename TY>
 __global__ void rmsnorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
                                const int* __restrict__ rows_index, int dim, float eps) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const TX* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim;
     float ss = 0.f;
@@ -28,8 +30,8 @@ HYMT2_API int hymt2_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, co
     HYMT2_REQUIRE(rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", rows, dim);
     const int threads = dim >= 1024 ? 256 : (dim >= 256 ? 128 : 32);
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(y_dtype, TY,
-        (rmsnorm_kernel<TX, TW, TY><<<rows, threads, 0, stream>>>((TY*)y, (const TX*)x, (const TW*)gain,
-                                                                    rows_index, dim, eps)))));
+        (launch_pdl(rmsnorm_kernel<TX, TW, TY>, dim3(rows), dim3(threads), 0, stream, (TY*)y, (const TX*)x,
+                    (const TW*)gain, rows_index, dim, eps)))));
     return hymt2_check_launch("rmsnorm");
 }
 

@@ -36,61 +36,60 @@ struct RopeKvParams {
 
 template <typename T, typename TG>
 __global__ void __launch_bounds__(128)
-rope_kv_kernel(RopeKvParams p) {
+rope_kv_kernel(RopeKvParams p, int tokens) {
     extern __shared__ float smem[];  // [4 warps][d]
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* row = smem + warp * p.d;
-    const int t = blockIdx.x;
+    const int total_heads = p.nh + 2 * p.nkv;
+    // one warp per (token, head)
+    const long item = (long)blockIdx.x * 4 + warp;
+    if (item >= (long)tokens * total_heads) return;
+    const int t = (int)(item / total_heads), head = (int)(item % total_heads);
     const int d = p.d, half = p.rope_dim / 2;
     const int pos = p.token_pos[t];
     const int slot = p.slot_ids[p.token_seq[t]];
-    const int total_heads = p.nh + 2 * p.nkv;
-    const T* src_tok = (const T*)p.qkv + (size_t)t * total_heads * d;
+    const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+    const bool write_kv = p.write_kv && slot >= 0;
+    if (!is_q && !write_kv) return;
+    const T* src = (const T*)p.qkv + ((size_t)t * total_heads + head) * d;
 
     size_t cache_row = 0;
-    const bool write_kv = p.write_kv && slot >= 0;
-    if (write_kv) {
+    if (!is_q) {
         const int block = p.block_table[(size_t)slot * p.table_stride + pos / p.block_tokens];
-        cache_row = ((size_t)block * p.nkv * p.block_tokens + (pos % p.block_tokens)) * d;  // + kvh * block_tokens * d
+        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+        cache_row = (((size_t)block * p.nkv + kvh) * p.block_tokens + (pos % p.block_tokens)) * d;
     }
-
-    for (int head = warp; head < total_heads; head += 4) {
-        const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
-        const T* src = src_tok + (size_t)head * d;
-        if (!is_q && !write_kv) continue;
-        if (!is_q && !is_k) {  // value head: a plain copy into the cache
-            const int kvh = head - p.nh - p.nkv;
-            T* dst = (T*)p.v_cache + cache_row + (size_t)kvh * p.block_tokens * d;
-            for (int c = lane; c < d; c += 32) dst[c] = src[c];
-            continue;
-        }
-        for (int c = lane; c < d; c += 32) row[c] = to_float(src[c]);
-        __syncwarp();
-        for (int i = lane; i < half; i += 32) {
-            const float angle = (float)pos * p.inv_freq[i];
-            float sn, cs;
-            sincosf(angle, &sn, &cs);
-            const float x0 = row[i], x1 = row[i + half];
-            row[i] = x0 * cs - x1 * sn;
-            row[i + half] = x0 * sn + x1 * cs;
-        }
-        __syncwarp();
-        const TG* gain = (const TG*)(is_q ? p.q_gain : p.k_gain);
-        float scale = 1.f;
-        if (gain) {
-            float ss = 0.f;
-            for (int c = lane; c < d; c += 32) ss = fmaf(row[c], row[c], ss);
-            ss = warp_sum(ss);
-            scale = 1.0f / sqrtf(ss / (float)d + p.eps);
-        }
-        T* dst = is_q ? (T*)p.q_out + ((size_t)t * p.nh + head) * d
-                      : (T*)p.k_cache + cache_row + (size_t)(head - p.nh) * p.block_tokens * d;
-        for (int c = lane; c < d; c += 32) {
-            float v = row[c];
-            if (gain) v = v * scale * to_float(gain[c]);
-            dst[c] = from_float<T>(v);
-        }
-        __syncwarp();
+    if (!is_q && !is_k) {  // value head: a plain copy into the cache
+        T* dst = (T*)p.v_cache + cache_row;
+        for (int c = lane; c < d; c += 32) dst[c] = src[c];
+        return;
+    }
+    for (int c = lane; c < d; c += 32) row[c] = to_float(src[c]);
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {
+        const float angle = (float)pos * p.inv_freq[i];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const float x0 = row[i], x1 = row[i + half];
+        row[i] = x0 * cs - x1 * sn;
+        row[i + half] = x0 * sn + x1 * cs;
+    }
+    __syncwarp();
+    const TG* gain = (const TG*)(is_q ? p.q_gain : p.k_gain);
+    float scale = 1.f;
+    if (gain) {
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) ss = fmaf(row[c], row[c], ss);
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)d + p.eps);
+    }
+    T* dst = is_q ? (T*)p.q_out + ((size_t)t * p.nh + head) * d : (T*)p.k_cache + cache_row;
+    for (int c = lane; c < d; c += 32) {
+        float v = row[c];
+        if (gain) v = v * scale * to_float(gain[c]);
+        dst[c] = from_float<T>(v);
     }
 }
 
@@ -112,7 +111,10 @@ HYMT2_API int hymt2_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v
                    q_gain, k_gain, table_stride, block_tokens, nh, nkv, d, rope_dim, write_kv, eps};
     const size_t smem = (size_t)4 * d * sizeof(float);
     HYMT2_REQUIRE(smem <= 48 * 1024, "rope_kv: head_dim %d is too large", d);
+    const long items = (long)tokens * (nh + 2 * nkv);
+    HYMT2_REQUIRE((items + 3) / 4 <= 2147483647L, "rope_kv: too many (token, head) pairs");
+    const unsigned blocks = (unsigned)((items + 3) / 4);
     HYMT2_DISPATCH_DTYPE(dtype, T, HYMT2_DISPATCH_DTYPE(gain_dtype, TG,
-        (rope_kv_kernel<T, TG><<<tokens, 128, smem, stream>>>(p))));
+        (launch_pdl(rope_kv_kernel<T, TG>, dim3(blocks), dim3(128), smem, stream, p, tokens))));
     return hymt2_check_launch("rope_kv");
 }

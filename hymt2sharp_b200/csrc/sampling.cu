@@ -55,6 +55,66 @@ argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     }
 }
 
+// Two-stage argmax for wide vocabularies: pieces of ARGMAX_PIECE logits each give their first
+// maximum, then one block per row picks the first maximum among the pieces.
+constexpr int ARGMAX_PIECE = 4096;
+
+__global__ void __launch_bounds__(256)
+argmax_pieces_kernel(float* __restrict__ piece_val, int* __restrict__ piece_idx, const float* __restrict__ logits,
+                     long row_stride, int vocab, const int* __restrict__ row_map) {
+    __shared__ float sval[8];
+    __shared__ int sidx[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y, piece = blockIdx.x;
+    if (row_map && row_map[row] < 0) return;
+    const float* x = logits + (size_t)row * row_stride;
+    const int begin = piece * ARGMAX_PIECE, end = min(vocab, begin + ARGMAX_PIECE);
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sval[warp] = best; sidx[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++)
+            if (sval[w] > best || (sval[w] == best && sidx[w] < best_i)) { best = sval[w]; best_i = sidx[w]; }
+        piece_val[(size_t)row * gridDim.x + piece] = best;
+        piece_idx[(size_t)row * gridDim.x + piece] = best_i;
+    }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ piece_val,
+                                    const int* __restrict__ piece_idx, int pieces, const int* __restrict__ row_map) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    if (row_map && row_map[row] < 0) return;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < pieces; i += 32) {
+        const float v = piece_val[(size_t)row * pieces + i];
+        const int vi = piece_idx[(size_t)row * pieces + i];
+        if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) out[row] = best_i == 0x7fffffff ? 0 : best_i;
+}
+
 __device__ __forceinline__ uint64_t rotl64(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
 
 __device__ __forceinline__ uint64_t xoshiro_next(uint64_t* s) {
@@ -394,10 +454,20 @@ HYMT2_API int hymt2_record_history(int* history, int* counts, int stride, const 
     return hymt2_check_launch("record_history");
 }
 
+// piece_val / piece_idx: scratch of rows * ceil(vocab / 4096) entries each, or null.  With scratch
+// and a vocabulary above 2 * 4096 the scan is spread over many blocks per row.
 HYMT2_API int hymt2_argmax(int* out, const float* logits, long row_stride, int rows, int vocab,
-                           const int* row_map, cudaStream_t stream) {
+                           const int* row_map, float* piece_val, int* piece_idx, cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
+    if (piece_val && piece_idx && vocab > 2 * ARGMAX_PIECE && rows <= 65535) {
+        const int pieces = (vocab + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
+        launch_pdl(argmax_pieces_kernel, dim3(pieces, rows), dim3(256), 0, stream, piece_val, piece_idx, logits, row_stride, vocab, row_map);
+        int rc = hymt2_check_launch("argmax (pieces)");
+        if (rc != HYMT2_OK) return rc;
+        launch_pdl(argmax_final_kernel, dim3(rows), dim3(32), 0, stream, out, (const float*)piece_val, (const int*)piece_idx, pieces, row_map);
+        return hymt2_check_launch("argmax (final)");
+    }
     argmax_kernel<<<rows, THREADS, 0, stream>>>(out, logits, row_stride, vocab, row_map);
     return hymt2_check_launch("argmax");
 }

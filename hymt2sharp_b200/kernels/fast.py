@@ -30,6 +30,6 @@ def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale,
         acc = torch.empty(na, dtype=torch.float32, device=out.device)
         ml = torch.empty(nm, dtype=torch.float32, device=out.device)
         ops.attention_decode(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens,
-                             nh, nkv, d, scale, window, splits, acc, ml)
+                             nh, nkv, d, scale, window, splits, acc, ml, ops.zeroed_counters(out.device, ctx.num_tokens * nh))
         return True
     return False

@@ -264,12 +264,27 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                                        _ptr(part_ml), _stream()), "attention_simt", 2 if split_keys > 0 else 1)
 
 
+_counters: dict = {}
+
+
+def zeroed_counters(device, n: int) -> torch.Tensor:
+    """A per-device int32 array that is zero between kernels: arrival counters of kernels whose
+    last-arriving block finishes the work (each such kernel leaves its counters at zero)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    old = _counters.get(key)
+    if old is None or old[-1].numel() < n:
+        _counters[key] = (old or []) + [torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)]
+    return _counters[key][-1]
+
+
 def attention_decode(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                      block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor,
                      nh: int, nkv: int, d: int, scale: float, window: int, max_splits: int,
-                     part_acc: torch.Tensor, part_ml: torch.Tensor) -> None:
+                     part_acc: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor) -> None:
     """bfloat16 decode attention (one new token per row) that streams the cache once per kv head;
-    head_dim 64 or 128.  The partials go through part_acc / part_ml (sizes as attention_simt_scratch)."""
+    head_dim 64 or 128.  The partials go through part_acc / part_ml (sizes as attention_simt_scratch);
+    `counters` holds rows*nh zeroed ints (the kernel leaves them zero)."""
     _need(out, "out", torch.bfloat16, 2); _need(q, "q", torch.bfloat16, 2)
     _need(k_plane, "k_plane", torch.bfloat16, 4); _need(v_plane, "v_plane", torch.bfloat16, 4)
     rows = out.shape[0]
@@ -281,13 +296,14 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, 
         _need(t, n, torch.int32, 1)
     need_acc, need_ml = attention_simt_scratch(rows, nh, d, max_splits)
     _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
-    if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+    _need(counters, "counters", torch.int32, 1)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml or counters.numel() < rows * nh:
         raise KernelError("attention_decode: the scratch for the partials is too small")
     _check(_lib().hymt2_attention_decode(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
                                          c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens),
                                          _ptr(slot_ids), _ptr(kv_lens), c_int(rows), c_int(nh), c_int(nkv), c_int(d),
                                          c_float(scale), c_int(window), c_int(max_splits), _ptr(part_acc),
-                                         _ptr(part_ml), _stream()), "attention_decode", 2)
+                                         _ptr(part_ml), _ptr(counters), _stream()), "attention_decode")
 
 
 # ---------------------------------------------------------------------------
@@ -296,13 +312,27 @@ def _logits_ok(logits: torch.Tensor, what: str) -> None:
         raise KernelError(f"{what}: logits must be a float32 CUDA matrix with contiguous rows")
 
 
-def argmax(out: torch.Tensor, logits: torch.Tensor, row_map: torch.Tensor | None = None) -> None:
-    """out[r] = first index of the maximum of logits[r]; rows with row_map[r] < 0 are skipped."""
+ARGMAX_PIECE = 4096
+
+
+def argmax(out: torch.Tensor, logits: torch.Tensor, row_map: torch.Tensor | None = None,
+           scratch: tuple | None = None) -> None:
+    """out[r] = first index of the maximum of logits[r]; rows with row_map[r] < 0 are skipped.
+    `scratch` = (float32, int32) tensors of rows * ceil(vocab / 4096) entries lets a wide
+    vocabulary be scanned by many blocks per row."""
     _need(out, "out", torch.int32, 1)
     _logits_ok(logits, "argmax")
     rows, vocab = logits.shape
+    val = idx = None
+    if scratch is not None:
+        val, idx = scratch
+        need = rows * (-(-vocab // ARGMAX_PIECE))
+        _need(val, "scratch values", torch.float32); _need(idx, "scratch indices", torch.int32)
+        if val.numel() < need or idx.numel() < need:
+            raise KernelError("argmax: the scratch is too small")
+    two_stage = scratch is not None and vocab > 2 * ARGMAX_PIECE
     _check(_lib().hymt2_argmax(_ptr(out), _ptr(logits), c_long(logits.stride(0)), c_int(rows), c_int(vocab),
-                               _ptr(row_map), _stream()), "argmax")
+                               _ptr(row_map), _ptr(val), _ptr(idx), _stream()), "argmax", 2 if two_stage else 1)
 
 
 def seed_rng(states: torch.Tensor, rows: torch.Tensor, seeds: torch.Tensor) -> None:

@@ -24,6 +24,7 @@ class BatchSampler:
         self.params = list(params)
         self.device = torch.device(device)
         n = len(params)
+        self._argmax_scratch = None
         self.all_greedy = all(p.greedy for p in params)
         self.any_filter = any(p.needs_filter for p in params)
         f32 = lambda vals: torch.tensor(vals, dtype=torch.float32, device=self.device)
@@ -69,7 +70,11 @@ class BatchSampler:
         if self.any_filter:
             ops.filter_logits(logits, self.inv_temperature, self.top_k, self.top_p, self.min_p, self.penalty,
                               self.history, row_map)
-        ops.argmax(out, logits, row_map)
+        need = rows * (-(-logits.shape[1] // ops.ARGMAX_PIECE))
+        if self._argmax_scratch is None or self._argmax_scratch[0].numel() < need:
+            self._argmax_scratch = (torch.empty(need, dtype=torch.float32, device=self.device),
+                                    torch.empty(need, dtype=torch.int32, device=self.device))
+        ops.argmax(out, logits, row_map, self._argmax_scratch)
         if not self.all_greedy:
             ops.sample(out, logits, self.inv_temperature, self.rng, row_map)
         if self.any_filter and self.history is not None:

@@ -267,6 +267,12 @@ def test_argmax_takes_the_first_maximum():
     want = x.argmax(dim=1).tolist()
     want[2], want[3], want[4], want[5] = 55, 0, -5, 120817
     assert out.tolist() == want
+    # the wide-vocabulary path: pieces of 4096 logits scanned by a block each, then one pick per row
+    pieces = 7 * (-(-120818 // ops.ARGMAX_PIECE))
+    scratch = (torch.full((pieces,), float("nan"), device=DEV), torch.full((pieces,), -3, dtype=torch.int32, device=DEV))
+    out2 = torch.full((7,), -5, dtype=torch.int32, device=DEV)
+    ops.argmax(out2, x, row_map, scratch)
+    assert out2.tolist() == want
     wide = torch.randn(3, 1000, device=DEV)
     view = wide[:, :509]  # rows with a stride larger than the vocabulary
     out = torch.empty(3, dtype=torch.int32, device=DEV)
@@ -380,7 +386,9 @@ def test_attention_decode_streaming(nh, nkv, d, window):
     acc = torch.full((na,), float("nan"), device=DEV)
     ml = torch.full((nm,), float("nan"), device=DEV)
     out = torch.full((rows, nh * d), 5.0, dtype=dtype, device=DEV)
-    ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, window, splits, acc, ml)
+    counters = torch.zeros(rows * nh, dtype=torch.int32, device=DEV)
+    ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, window, splits, acc, ml, counters)
+    assert int(counters.abs().sum()) == 0   # left at zero for the next launch
     ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, window, scale) for i in range(rows)])
     assert torch.allclose(out[:7].double(), ref[:7], **_tol(dtype))
     assert (out[7] == 5.0).all()   # the padding row is left alone
