@@ -61,6 +61,12 @@ template <int D, int G>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(DecodeParams p) {
     constexpr int E = D / LANES_PER_KEY;   // elements of a key that one lane holds
+    constexpr int KEYS_PER_WARP = CHUNK_KEYS / WARPS;
+    constexpr int ITERS = KEYS_PER_WARP / KEYS_PER_ITER;   // 16 keys per lane group
+    constexpr int PF = 4;                  // keys in flight per lane group
+    __shared__ float sm_p[WARPS][KEYS_PER_WARP][G];        // scores, then softmax numerators
+    __shared__ float sm_acc[WARPS][G][D];
+    __shared__ float sm_ml[WARPS][G][2];
     pdl_launch_dependents();
     pdl_wait();
     const int split = blockIdx.x, b = blockIdx.z;
@@ -75,107 +81,132 @@ attention_decode_kernel(DecodeParams p) {
     const int kvh = blockIdx.y / groups, head0 = kvh * g + (blockIdx.y % groups) * G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LANES_PER_KEY, keygrp = lane / LANES_PER_KEY;
-
-    float q[G][E];
-#pragma unroll
-    for (int h = 0; h < G; h++) {
-        uint4 raw[E / 8];
-        load_row<E>(p.q + ((size_t)b * p.nh + head0 + h) * D + sub * E, raw, true);
-        unpack<E>(raw, q[h]);
-#pragma unroll
-        for (int e = 0; e < E; e++) q[h][e] *= p.scale;
-    }
-    float acc[G][E], m[G], l[G];
-#pragma unroll
-    for (int h = 0; h < G; h++) {
-        m[h] = -INFINITY;
-        l[h] = 0.f;
-#pragma unroll
-        for (int e = 0; e < E; e++) acc[h][e] = 0.f;
-    }
-
     const int* table = p.block_table + (size_t)slot * p.table_stride;
-    const int warp_begin = chunk_begin + warp * (CHUNK_KEYS / WARPS);
-    constexpr int ITERS = CHUNK_KEYS / WARPS / KEYS_PER_ITER;   // 16 keys per lane group
+    const int warp_begin = chunk_begin + warp * KEYS_PER_WARP;
 
-    auto address = [&](int key, bool& ok) -> size_t {
+    auto address = [&](int it, bool& ok) -> size_t {   // the row of this lane group's key of iteration `it`
+        const int key = warp_begin + it * KEYS_PER_ITER + keygrp;
         ok = key >= lo && key <= pos;
         if (!ok) return 0;
         const int block = table[key >> p.block_shift];
         return ((((size_t)block * p.nkv + kvh) << p.block_shift) + (key & ((1 << p.block_shift) - 1))) * D + sub * E;
     };
 
-    uint4 kraw[2][E / 8], vraw[2][E / 8];
-    bool okv[2];
+    // ---- pass 1: scores of the warp's 64 keys; only q and the keys in flight are live --------
+    float m[G];
     {
-        const size_t a = address(warp_begin + keygrp, okv[0]);
-        load_row<E>(p.k_cache + a, kraw[0], okv[0]);
-        load_row<E>(p.v_cache + a, vraw[0], okv[0]);
-    }
-#pragma unroll 2
-    for (int it = 0; it < ITERS; it++) {
-        const int cur = it & 1, nxt = cur ^ 1;
-        if (it + 1 < ITERS) {   // the next key's bytes are on their way while this key is used
-            const size_t a = address(warp_begin + (it + 1) * KEYS_PER_ITER + keygrp, okv[nxt]);
-            load_row<E>(p.k_cache + a, kraw[nxt], okv[nxt]);
-            load_row<E>(p.v_cache + a, vraw[nxt], okv[nxt]);
-        }
-        float kf[E];
-        unpack<E>(kraw[cur], kf);
-        float s[G];
+        float q[G][E];
 #pragma unroll
         for (int h = 0; h < G; h++) {
-            float dot = 0.f;
+            uint4 raw[E / 8];
+            load_row<E>(p.q + ((size_t)b * p.nh + head0 + h) * D + sub * E, raw, true);
+            unpack<E>(raw, q[h]);
 #pragma unroll
-            for (int e = 0; e < E; e++) dot = fmaf(q[h][e], kf[e], dot);
-            s[h] = dot;
+            for (int e = 0; e < E; e++) q[h][e] *= p.scale;
+            m[h] = -INFINITY;
+        }
+        uint4 kraw[PF][E / 8];
+        bool okv[PF];
+#pragma unroll
+        for (int i = 0; i < PF; i++) {
+            const size_t a = address(i, okv[i]);
+            load_row<E>(p.k_cache + a, kraw[i], okv[i]);
         }
 #pragma unroll
-        for (int o = 1; o < LANES_PER_KEY; o <<= 1)
-#pragma unroll
-            for (int h = 0; h < G; h++) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
-        if (okv[cur]) {   // the same for the 8 lanes of a key
-            float vf[E];
-            unpack<E>(vraw[cur], vf);
+        for (int it = 0; it < ITERS; it++) {
+            const int st = it % PF;
+            float kf[E];
+            unpack<E>(kraw[st], kf);
+            const bool ok = okv[st];
+            if (it + PF < ITERS) {   // the freed registers take the key that is PF iterations ahead
+                const size_t a = address(it + PF, okv[st]);
+                load_row<E>(p.k_cache + a, kraw[st], okv[st]);
+            }
+            float s[G];
 #pragma unroll
             for (int h = 0; h < G; h++) {
-                const float m_new = fmaxf(m[h], s[h]);
-                const float pj = expf(s[h] - m_new);
-                if (m_new > m[h]) {
-                    const float corr = expf(m[h] - m_new);   // 0 for the first key
-                    l[h] *= corr;
+                float dot = 0.f;
 #pragma unroll
-                    for (int e = 0; e < E; e++) acc[h][e] *= corr;
-                    m[h] = m_new;
-                }
-                l[h] += pj;
+                for (int e = 0; e < E; e++) dot = fmaf(q[h][e], kf[e], dot);
+                s[h] = dot;
+            }
+#pragma unroll
+            for (int o = 1; o < LANES_PER_KEY; o <<= 1)
+#pragma unroll
+                for (int h = 0; h < G; h++) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
+#pragma unroll
+            for (int h = 0; h < G; h++) {
+                if (!ok) s[h] = -INFINITY;
+                m[h] = fmaxf(m[h], s[h]);
+            }
+            if (sub < G) sm_p[warp][it * KEYS_PER_ITER + keygrp][sub] = s[sub < G ? sub : 0];
+        }
+    }
+    // the warp's maximum per head, then numerators and their sum
+#pragma unroll
+    for (int o = LANES_PER_KEY; o < 32; o <<= 1)
+#pragma unroll
+        for (int h = 0; h < G; h++) m[h] = fmaxf(m[h], __shfl_xor_sync(0xffffffffu, m[h], o));
+    __syncwarp();
+    float l[G];
+#pragma unroll
+    for (int h = 0; h < G; h++) l[h] = 0.f;
+    for (int i = lane; i < KEYS_PER_WARP * G; i += 32) {
+        const int key = i / G, h = i - key * G;
+        float mh = m[0];
+#pragma unroll
+        for (int hh = 1; hh < G; hh++) mh = h == hh ? m[hh] : mh;
+        const float s = sm_p[warp][key][h];
+        const float pj = mh == -INFINITY ? 0.f : expf(s - mh);   // a masked key has s = -inf: 0
+        sm_p[warp][key][h] = pj;
+#pragma unroll
+        for (int hh = 0; hh < G; hh++) l[hh] += h == hh ? pj : 0.f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int h = 0; h < G; h++) l[h] += __shfl_xor_sync(0xffffffffu, l[h], o);
+    __syncwarp();
+
+    // ---- pass 2: weighted sum of the values; only the accumulators and the values in flight ----
+    float acc[G][E];
+#pragma unroll
+    for (int h = 0; h < G; h++)
+#pragma unroll
+        for (int e = 0; e < E; e++) acc[h][e] = 0.f;
+    {
+        uint4 vraw[PF][E / 8];
+        bool okv[PF];
+#pragma unroll
+        for (int i = 0; i < PF; i++) {
+            const size_t a = address(i, okv[i]);
+            load_row<E>(p.v_cache + a, vraw[i], okv[i]);
+        }
+#pragma unroll
+        for (int it = 0; it < ITERS; it++) {
+            const int st = it % PF;
+            float vf[E];
+            unpack<E>(vraw[st], vf);
+            if (it + PF < ITERS) {
+                const size_t a = address(it + PF, okv[st]);
+                load_row<E>(p.v_cache + a, vraw[st], okv[st]);
+            }
+            const float* pr = sm_p[warp][it * KEYS_PER_ITER + keygrp];   // 0 for keys that are not visible
+#pragma unroll
+            for (int h = 0; h < G; h++) {
+                const float pj = pr[h];
 #pragma unroll
                 for (int e = 0; e < E; e++) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
             }
         }
     }
-
-    // fold the 4 key groups of a warp, then the 4 warps, in a fixed order
-    __shared__ float sm_acc[WARPS][G][D];
-    __shared__ float sm_ml[WARPS][G][2];
+    // fold the 4 key groups of a warp (they share the warp's maximum), then the 4 warps, in a fixed order
 #pragma unroll
-    for (int o = LANES_PER_KEY; o < 32; o <<= 1) {
+    for (int o = LANES_PER_KEY; o < 32; o <<= 1)
 #pragma unroll
-        for (int h = 0; h < G; h++) {
-            const float m_o = __shfl_xor_sync(0xffffffffu, m[h], o);
-            const float l_o = __shfl_xor_sync(0xffffffffu, l[h], o);
-            const float m_new = fmaxf(m[h], m_o);
-            const float c_me = m_new == -INFINITY ? 0.f : expf(m[h] - m_new);
-            const float c_o = m_new == -INFINITY ? 0.f : expf(m_o - m_new);
-            l[h] = l[h] * c_me + l_o * c_o;
+        for (int h = 0; h < G; h++)
 #pragma unroll
-            for (int e = 0; e < E; e++) {
-                const float a_o = __shfl_xor_sync(0xffffffffu, acc[h][e], o);
-                acc[h][e] = acc[h][e] * c_me + a_o * c_o;
-            }
-            m[h] = m_new;
-        }
-    }
+            for (int e = 0; e < E; e++) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
     if (keygrp == 0) {
 #pragma unroll
         for (int h = 0; h < G; h++) {

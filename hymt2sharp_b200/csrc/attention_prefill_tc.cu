@@ -1,0 +1,396 @@
+// Causal grouped-query flash attention for prompts on the tcgen05 tensor cores (bfloat16).
+//
+// One CTA owns 128 query rows of one head of one sequence and walks the sequence's cache in
+// tiles of 64 keys (one cache block) up to the causal limit.  Per tile:
+//   S = Q·K^T        tcgen05.mma, M = 128, N = 64, K = d, accumulator in TMEM;
+//   softmax          four warps, one thread per query row: tcgen05.ld of the row's 64 scores,
+//                    scale, mask, running maximum and sum in float32 (exp2 of log2e-scaled
+//                    scores); P is written as bfloat16 into shared memory in the swizzled
+//                    K-major layout that the tensor core reads;
+//   O += P·V         tcgen05.mma, M = 128, N = d, K = 64 keys, accumulating in TMEM; V is used as
+//                    it lies in the cache ([key][d], i.e. MN-major for the B operand).
+// The running maximum of a row is only raised when the new maximum exceeds it by more than 2^8;
+// then the row's O in TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st).  Until then P is
+// taken relative to the older maximum, which gives the same quotient O / l.
+// Q, K and V tiles arrive by TMA (128-byte swizzle); K/V tiles are double-buffered; mbarriers
+// order producer, MMA issuer and softmax warps; every wait is bounded.
+// Formulas: src/HyMT2Sharp/Ops.cs:359-455 (scores, kv head = head / group), :198-325 (softmax
+// over the visible keys), :535-595 (combine).  A query at position p sees keys
+// [max(0, p - window + 1), p].
+// Takes head sizes 64 and 128 and cache blocks of 64 tokens; other shapes stay with the general kernel.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int Q_ROWS = 128, KEY_TILE = 64, NUM_THREADS = 192, KV_STAGES = 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 21;
+
+struct PrefillParams {
+    __nv_bfloat16* out;        // [T, nh * d]
+    const int* block_table;
+    const int* cu_seqlens;
+    const int* slot_ids;
+    const int* kv_lens;
+    int table_stride, nh, nkv, window;
+    float scale_log2;          // scale * log2(e)
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand tile, 128-byte swizzle: rows (K index) of 64 MN-elements = 128 bytes, 8-row groups
+// 1024 bytes apart (stride offset), the next 64 MN-elements `mn_group_bytes` further (leading offset)
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_group_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(mn_group_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, PrefillParams p) {
+    constexpr int D_BOXES = D / 64;                         // TMA boxes of 64 elements along d
+    constexpr int Q_BYTES = Q_ROWS * D * 2, KV_TILE_BYTES = KEY_TILE * D * 2, P_BYTES = Q_ROWS * KEY_TILE * 2;
+    // P of a tile (16 KB) takes the place of the tile's K (free once S is computed) when K is that large;
+    // else every stage has a P region of its own
+    constexpr bool P_IN_K = KV_TILE_BYTES >= P_BYTES;
+    constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES + (P_IN_K ? 0 : P_BYTES);
+    constexpr int TMEM_COLS = 256;                          // S: columns [0, 64), O tile: [64, 64 + D)
+    constexpr uint32_t S_COL = 0, O_COL = 64;
+    // D float32, A and B bfloat16; S: both K-major, N = 64; O: B is MN-major, N = D
+    constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KEY_TILE >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
+    constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * KV_STAGES + 4];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int b = blockIdx.z, head = blockIdx.y, qtile = blockIdx.x;
+    const int slot = p.slot_ids[b];
+    const int tok0 = p.cu_seqlens[b], T_b = p.cu_seqlens[b + 1] - tok0;
+    if (slot < 0 || qtile * Q_ROWS >= T_b) return;
+    const int kv_len = p.kv_lens[b], start = kv_len - T_b;
+    const int kvh = head / (p.nh / p.nkv);
+    const int rows_here = min(Q_ROWS, T_b - qtile * Q_ROWS);
+    const int first_pos = start + qtile * Q_ROWS, last_pos = first_pos + rows_here - 1;
+    const int tile_begin = p.window > 0 ? max(0, first_pos - p.window + 1) / KEY_TILE : 0;
+    const int tile_end = last_pos / KEY_TILE + 1;
+    const int num_tiles = tile_end - tile_begin;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = base, kv_smem = q_smem + Q_BYTES;
+    auto k_of = [&](int s) { return kv_smem + s * STAGE_BYTES; };
+    auto v_of = [&](int s) { return kv_smem + s * STAGE_BYTES + KV_TILE_BYTES; };
+    auto p_of = [&](int s) { return P_IN_K ? kv_smem + s * STAGE_BYTES : kv_smem + s * STAGE_BYTES + 2 * KV_TILE_BYTES; };
+    const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
+    const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), s_full = q_full + 8, p_full = q_full + 16, o_full = q_full + 24;
+    volatile int* abort_flag = &abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < KV_STAGES; s++) {
+            mbar_init(kv_full + 8 * s, 1);
+            mbar_init(kv_empty + 8 * s, 1);
+        }
+        mbar_init(q_full, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: Q once, then the K and V tiles ------------------------------------------
+        mbar_expect_tx(q_full, Q_BYTES);
+        for (int x = 0; x < D_BOXES; x++)
+            tma_load_2d(q_smem + x * (Q_ROWS * 128), &map_q, q_full, head * D + x * 64, tok0 + qtile * Q_ROWS);
+        const int* table = p.block_table + (size_t)slot * p.table_stride;
+        int issued = 0;
+        for (int i = 0; i < num_tiles; i++) {
+            const int s = i % KV_STAGES;
+            if (!mbar_wait(kv_empty + 8 * s, ((i / KV_STAGES) & 1) ^ 1, abort_flag, p.status, 111)) break;
+            const int block = table[tile_begin + i];
+            const int row = (block * p.nkv + kvh) * KEY_TILE;
+            const uint32_t k_dst = k_of(s), v_dst = v_of(s);
+            mbar_expect_tx(kv_full + 8 * s, 2 * KV_TILE_BYTES);
+            for (int x = 0; x < D_BOXES; x++) {
+                tma_load_2d(k_dst + x * (KEY_TILE * 128), &map_k, kv_full + 8 * s, x * 64, row);
+                tma_load_2d(v_dst + x * (KEY_TILE * 128), &map_v, kv_full + 8 * s, x * 64, row);
+            }
+            issued = i + 1;
+        }
+        if (*abort_flag)
+            for (int i = max(0, issued - KV_STAGES); i < issued; i++)
+                for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1); t++) {}
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ---------------------------------------------------------------------------
+        bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 112);
+        for (int i = 0; ok && i < num_tiles; i++) {
+            const int s = i % KV_STAGES;
+            const uint32_t k_src = k_of(s), v_src = v_of(s), p_src = p_of(s);
+            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // S = Q K^T over d in steps of 16
+#pragma unroll
+            for (int k = 0; k < D / 16; k++) {
+                const uint32_t box = (k / 4), in_box = (k % 4) * 32;
+                umma_bf16(tmem_base + S_COL, desc_k_major(q_smem + box * (Q_ROWS * 128) + in_box),
+                          desc_k_major(k_src + box * (KEY_TILE * 128) + in_box), IDESC_S, k > 0 ? 1u : 0u);
+            }
+            umma_commit(s_full);
+            // O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
+            if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 114)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int k = 0; k < KEY_TILE / 16; k++)
+                umma_bf16(tmem_base + O_COL, desc_k_major(p_src + k * 32),
+                          desc_mn_major(v_src + k * (16 * 128), KEY_TILE * 128), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(kv_empty + 8 * s);
+            umma_commit(o_full);
+        }
+    } else if (warp >= 2) {
+        // ---- softmax: one thread per query row; O stays in TMEM ------------------------------------
+        const int quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int pos = first_pos + r;                                  // position of this row's query
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const bool row_ok = r < rows_here;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < num_tiles; i++) {
+            if (!(ok = mbar_wait(s_full, i & 1, abort_flag, p.status, 115))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int key0 = (tile_begin + i) * KEY_TILE;
+            float s[KEY_TILE];
+            tmem_load32(lane_addr + S_COL, s);
+            tmem_load32(lane_addr + S_COL + 32, s + 32);
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < KEY_TILE; c++) {
+                const int key = key0 + c;
+                s[c] = (row_ok && key >= lo && key <= pos) ? s[c] * p.scale_log2 : -INFINITY;
+                tile_max = fmaxf(tile_max, s[c]);
+            }
+            // raise the row's maximum only when it grows by more than 2^8 (or at its first visible key)
+            const bool raise = tile_max > m + 8.0f || (m == -INFINITY && tile_max > -INFINITY);
+            const float corr = raise ? exp2f(m - tile_max) : 1.f;   // m = -inf: 0
+            if (raise) m = tile_max;
+            if (i > 0 && __any_sync(0xffffffffu, raise)) {
+                // the O of the tiles so far is complete, then every row of the warp scales its own O
+                if (!(ok = mbar_wait(o_full, (i - 1) & 1, abort_flag, p.status, 116))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    float o[32];
+                    tmem_load32(lane_addr + O_COL + c, o);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] *= corr;
+                    tmem_store32(lane_addr + O_COL + c, o);
+                }
+            }
+            l *= corr;
+            float psum = 0.f;
+            // P as bfloat16 into the swizzled K-major tile: row r, 16-byte chunk c8 at chunk (c8 ^ (r & 7))
+            const uint32_t p_dst = p_of(i % KV_STAGES);
+#pragma unroll
+            for (int c8 = 0; c8 < KEY_TILE / 8; c8++) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float p0 = m == -INFINITY ? 0.f : exp2f(s[c8 * 8 + 2 * j] - m);
+                    const float p1 = m == -INFINITY ? 0.f : exp2f(s[c8 * 8 + 2 * j + 1] - m);
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    // the sum uses the rounded values that the tensor core will multiply with
+                    psum += __low2float(h) + __high2float(h);
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                const uint32_t dst = p_dst + r * 128 + ((c8 ^ (r & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
+                             "r"(packed[2]), "r"(packed[3]) : "memory");
+            }
+            l += psum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_full);
+        }
+        if (ok) ok = mbar_wait(o_full, (num_tiles - 1) & 1, abort_flag, p.status, 117);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __nv_bfloat16* dst = p.out + ((size_t)(tok0 + qtile * Q_ROWS + r) * p.nh + head) * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 32) {
+                float o[32];
+                tmem_load32(lane_addr + O_COL + c, o);   // all lanes of the warp take part in the load
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        __nv_bfloat162 h[4];
+#pragma unroll
+                        for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(o[j + 2 * q] * inv, o[j + 2 * q + 1] * inv);
+                        *reinterpret_cast<uint4*>(dst + c + j) = *reinterpret_cast<uint4*>(h);
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+bool make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid,
+           cudaStream_t stream) {
+    constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
+    constexpr size_t smem = Q_ROWS * D * 2 + KV_STAGES * (2 * kv_tile + (kv_tile >= p_tile ? 0 : p_tile)) + 1024;
+    auto kernel = attention_prefill_tc_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { hymt2_set_error("attention_prefill_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+        configured = true;
+    }
+    kernel<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p);
+    return hymt2_check_launch("attention_prefill_tc");
+}
+
+}  // namespace
+
+// out, q: [tokens, nh * d] bfloat16; k_cache, v_cache: one layer's planes [blocks][nkv][64][d] bfloat16.
+HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                         long cache_blocks, const int* block_table, int table_stride, int block_tokens,
+                                         const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
+                                         int tokens, int max_new_tokens, int nh, int nkv, int d, float scale, int window,
+                                         int* status, cudaStream_t stream) {
+    if (tokens == 0 || batch == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim %d is not taken (64 and 128 are)", d);
+    HYMT2_REQUIRE(block_tokens == KEY_TILE, "attention_prefill_tc: cache blocks must hold %d tokens", KEY_TILE);
+    HYMT2_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && batch <= 65535 && nh <= 65535, "attention_prefill_tc: bad sizes");
+    HYMT2_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
+                  ((uintptr_t)out % 16 == 0), "attention_prefill_tc: tensors must be 16-byte aligned");
+    HYMT2_REQUIRE(status != nullptr, "attention_prefill_tc: a status word is needed");
+    CUtensorMap mq, mk, mv;
+    const long cache_rows = cache_blocks * nkv * KEY_TILE;
+    const bool ok = make_map(&mq, q, tokens, (long)nh * d, (long)nh * d, Q_ROWS) &&
+                    make_map(&mk, k_cache, cache_rows, d, d, KEY_TILE) && make_map(&mv, v_cache, cache_rows, d, d, KEY_TILE);
+    HYMT2_REQUIRE(ok, "attention_prefill_tc: cuTensorMapEncodeTiled refused the operands");
+    PrefillParams p{(__nv_bfloat16*)out, block_table, cu_seqlens, slot_ids, kv_lens, table_stride, nh, nkv, window,
+                    scale * 1.4426950408889634f, status};
+    dim3 grid((max_new_tokens + Q_ROWS - 1) / Q_ROWS, nh, batch);
+    return d == 128 ? launch<128>(mq, mk, mv, p, grid, stream) : launch<64>(mq, mk, mv, p, grid, stream);
+}

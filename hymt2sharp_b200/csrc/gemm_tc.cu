@@ -459,7 +459,9 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     pl.splits = (num_k_blocks + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
     pl.grid.z = pl.splits;
     const int stage_bytes = num_acc * A_TILE_BYTES + pl.bn * BLOCK_K * 2;
-    const int budget = 100 * 1024;   // two CTAs share an SM: of one kernel, or of a kernel and the next one
+    // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
+    const long ctas = (long)pl.grid.x * pl.grid.y * pl.splits;
+    const int budget = ctas <= sm_count ? 200 * 1024 : 100 * 1024;
     int stages = budget / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
     if (stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;

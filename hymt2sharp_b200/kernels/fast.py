@@ -19,7 +19,8 @@ DECODE_CHUNK_KEYS = 256  # keys per partial of the decode kernel, a constant of 
 
 
 def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale, window) -> bool:
-    """bfloat16 decode steps with head_dim 64 or 128 go to the streaming decode kernel."""
+    """bfloat16 with head_dim 64 or 128: decode steps go to the streaming decode kernel, steps with
+    longer pieces to the tcgen05 flash-attention kernel (cache blocks of 64 tokens)."""
     from . import ops
     bt = k_plane.shape[2]
     if out.dtype != torch.bfloat16 or d not in (64, 128) or bt & (bt - 1):
@@ -31,5 +32,10 @@ def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale,
         ml = torch.empty(nm, dtype=torch.float32, device=out.device)
         ops.attention_decode(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens,
                              nh, nkv, d, scale, window, splits, acc, ml, ops.zeroed_counters(out.device, ctx.num_tokens * nh))
+        return True
+    if bt == 64:
+        ops.attention_prefill_tc(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens,
+                                 ctx.num_seqs, ctx.max_new_tokens, nh, nkv, d, scale, window,
+                                 ops.device_status(out.device))
         return True
     return False

@@ -264,6 +264,28 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                                        _ptr(part_ml), _stream()), "attention_simt", 2 if split_keys > 0 else 1)
 
 
+def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                         block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor,
+                         kv_lens: torch.Tensor, batch: int, max_new_tokens: int, nh: int, nkv: int, d: int,
+                         scale: float, window: int, status: torch.Tensor) -> None:
+    """bfloat16 causal attention of the new tokens over the paged cache on the tcgen05 tensor cores
+    (flash attention with S and O in tensor memory); head_dim 64 or 128, cache blocks of 64 tokens."""
+    _need(out, "out", torch.bfloat16, 2); _need(q, "q", torch.bfloat16, 2)
+    _need(k_plane, "k_plane", torch.bfloat16, 4); _need(v_plane, "v_plane", torch.bfloat16, 4)
+    T = out.shape[0]
+    if out.shape[1] != nh * d or q.shape != out.shape or k_plane.shape[1] != nkv or k_plane.shape[3] != d \
+            or v_plane.shape != k_plane.shape:
+        raise KernelError(f"attention_prefill_tc: shapes out {tuple(out.shape)} q {tuple(q.shape)} k {tuple(k_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_attention_prefill_tc(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), c_long(k_plane.shape[0]),
+                                             _ptr(block_table), c_int(block_table.stride(0)), c_int(k_plane.shape[2]),
+                                             _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(T),
+                                             c_int(max_new_tokens), c_int(nh), c_int(nkv), c_int(d), c_float(scale),
+                                             c_int(window), _ptr(status), _stream()), "attention_prefill_tc")
+
+
 _counters: dict = {}
 
 

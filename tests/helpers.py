@@ -34,6 +34,13 @@ CONFIGS = {
                           rope_theta=5000.0, rope_dim=16, rms_norm_eps=1e-5, use_qk_norm=True,
                           tie_word_embeddings=True, sliding_window=40, max_position_embeddings=1024),
               seed=2, sigma=0.04, gain_dtype="bfloat16"),
+    # head_dim 64 with 4 heads per kv head: the bfloat16 engine runs its tensor-core attention kernels
+    # (prompt and decode) on this one; the sizes above stay with the general kernels
+    "M": dict(config=dict(architectures=[ARCH], num_hidden_layers=2, hidden_size=192, num_attention_heads=8,
+                          num_key_value_heads=2, head_dim=64, intermediate_size=328, vocab_size=1003,
+                          rope_theta=10000.0, rope_scaling={"type": "dynamic", "alpha": 1000.0}, rms_norm_eps=1e-5,
+                          use_qk_norm=True, tie_word_embeddings=True, max_position_embeddings=4096),
+              seed=3, sigma=0.03, gain_dtype="bfloat16"),
 }
 
 # Tolerances, fixed before the kernels were tuned.  32-bit: differences come from the order of

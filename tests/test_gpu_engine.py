@@ -24,7 +24,7 @@ def _poison(eng):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "M"])
 def test_long_decoding_from_the_first_token(name, dtype, model_dirs, plain_models):
     """A one-token prompt, then 420 tokens one by one (across block ends and past the length at
     which decode attention starts to split its keys), in a cache whose unwritten rows are NaN."""

@@ -392,3 +392,37 @@ def test_attention_decode_streaming(nh, nkv, d, window):
     ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, window, scale) for i in range(rows)])
     assert torch.allclose(out[:7].double(), ref[:7], **_tol(dtype))
     assert (out[7] == 5.0).all()   # the padding row is left alone
+
+
+@pytest.mark.parametrize("nh, nkv, d, window", [(4, 2, 128, 0), (8, 2, 64, 0), (3, 1, 128, 100), (6, 6, 64, 37)])
+def test_attention_prefill_tcgen05(nh, nkv, d, window):
+    """The tcgen05 flash-attention kernel against the float64 reference: whole prompts, a piece after
+    a long prefix, single rows, lengths around its tiles of 128 queries and 64 keys."""
+    ops = _ops()
+    torch.manual_seed(nh * 7 + d)
+    dtype = torch.bfloat16
+    lens, news = [70, 1, 600, 33, 129, 256], [70, 1, 300, 2, 129, 128]
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    qs = [torch.randn(n, nh, d, device=DEV).to(dtype) for n in news]
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=5)
+    scale = 1 / math.sqrt(d)
+    q = torch.cat([x.reshape(x.shape[0], nh * d) for x in qs])
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(news)]), dtype=torch.int32, device=DEV)
+    slots = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out = torch.full((sum(news), nh * d), 5.0, dtype=dtype, device=DEV)
+    ops.attention_prefill_tc(out, q, kp, vp, table, cu, slots, kv, len(lens), max(news), nh, nkv, d, scale, window, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), news[i], window, scale)
+                     for i in range(len(lens))])
+    assert torch.allclose(out.double(), ref, **_tol(dtype))
+    # scores far apart (a maximum that rises late by much more than 2^8): the rescale of O in tensor memory
+    big_q = [x * 6 for x in qs]
+    q2 = torch.cat([x.reshape(x.shape[0], nh * d) for x in big_q])
+    ops.attention_prefill_tc(out, q2, kp, vp, table, cu, slots, kv, len(lens), max(news), nh, nkv, d, scale, window, status)
+    ref2 = torch.cat([_ref_attention(big_q[i].float(), keys[i].float(), vals[i].float(), news[i], window, scale)
+                      for i in range(len(lens))])
+    assert torch.allclose(out.double(), ref2, **_tol(dtype))
