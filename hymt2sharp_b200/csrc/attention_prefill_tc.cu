@@ -291,6 +291,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                              "r"(packed[2]), "r"(packed[3]) : "memory");
             }
             l += psum;
+            // rows of V at and past the sequence's length were never written by this sequence: their
+            // weight is 0, but 0 x (whatever bits lie there) must stay 0 (K and V of the tile have
+            // landed: the scores came from them)
+            if (r < KEY_TILE && key0 + r >= kv_len) {
+#pragma unroll
+                for (int x = 0; x < D_BOXES; x++) {
+                    const uint32_t rowp = v_of(i % KV_STAGES) + x * (KEY_TILE * 128) + r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowp + c * 16), "r"(0) : "memory");
+                }
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full);

@@ -246,13 +246,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (SWAPPED) {
                 const int n = a_row0 + row;                    // output feature
                 if (n >= p.N) return;
+                float old[CH];
+                if (EPI == EPI_ACCUMULATE) {                   // all loads first: they do not wait for each other
+#pragma unroll
+                    for (int j = 0; j < CH; j++) {
+                        const int t = b_row0 + c + j;
+                        old[j] = t < p.T ? to_float(C[(size_t)t * p.ldc + n]) : 0.f;
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < CH; j++) {
                     const int t = b_row0 + c + j;              // token
                     if (t >= p.T) break;
                     TC* dst = C + (size_t)t * p.ldc + n;
                     if (EPI == EPI_STORE) *dst = from_float<TC>(g[j]);
-                    else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(to_float(*dst) + g[j]);
+                    else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[j] + g[j]);
                     else *dst = from_float<TC>(silu_mul(g[j], u[j]));
                 }
             } else {
@@ -444,7 +452,7 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         // the cut depends on N and K only, never on the number of tokens
         if (tiles < sm_count / 2) {
             int want = sm_count / tiles;
-            want = want > 8 ? 8 : want;
+            want = want > 16 ? 16 : want;
             while (want > 1 && num_k_blocks / want < 2) want--;
             pl.splits = want;
         }

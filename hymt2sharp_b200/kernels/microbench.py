@@ -1,0 +1,200 @@
+"""Runs ONE kernel of the library at a given shape a few times and prints its time: the small
+cases that profiles are taken on, and a quick way to see what a change did to a kernel.
+
+    python -m hymt2sharp_b200.kernels.microbench gemm --tokens 8 --out 6144 --inner 2048 --epilogue swiglu
+    python -m hymt2sharp_b200.kernels.microbench attention-decode --batch 8 --context 2100
+    python -m hymt2sharp_b200.kernels.microbench attention-prefill --tokens 2048
+    python -m hymt2sharp_b200.kernels.microbench rmsnorm | rope | argmax ...
+
+Weights rotate through `--copies` buffers so that a repeated call streams from memory, not from
+the L2 cache.  Times come from CUDA events around `--iters` calls after `--warmup` calls; with
+`--graph` the calls are captured into one CUDA graph first (what a decode step does), which
+takes the Python launch cost out of the number.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from . import ops
+
+DEV = "cuda:0"
+BF = torch.bfloat16
+
+
+def _time(fn, warmup: int, iters: int, graph: bool) -> float:
+    """Microseconds per call."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(iters):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        run = g.replay
+        calls = iters
+    else:
+        def run():
+            for _ in range(iters):
+                fn()
+        calls = iters
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / calls * 1000.0
+
+
+def gemm(a) -> None:
+    epi = {"store": ops.EPILOGUE_STORE, "accumulate": ops.EPILOGUE_ACCUMULATE, "swiglu": ops.EPILOGUE_SWIGLU}[a.epilogue]
+    rows = 2 * a.out if epi == ops.EPILOGUE_SWIGLU else a.out
+    ws = [(torch.randn(rows, a.inner, device=DEV) / math.sqrt(a.inner)).to(BF) for _ in range(a.copies)]
+    x = torch.randn(a.tokens, a.inner, device=DEV).to(BF)
+    cdt = torch.float32 if (epi == ops.EPILOGUE_ACCUMULATE or a.float_out) else BF
+    out = torch.zeros(a.tokens, a.out, device=DEV, dtype=cdt)
+    status = ops.device_status(DEV)
+    i = [0]
+
+    def fn():
+        ops.gemm_tc(out, x, ws[i[0] % a.copies], epi, status)
+        i[0] += 1
+    us = _time(fn, a.warmup, a.iters, a.graph)
+    flops = 2.0 * a.tokens * rows * a.inner
+    print(f"gemm_tc tokens={a.tokens} out={a.out} inner={a.inner} epilogue={a.epilogue}: {us:.1f} us  "
+          f"{flops / us / 1e6:.1f} TFLOP/s  weights {rows * a.inner * 2 / us / 1e3:.0f} GB/s")
+
+
+def _cache(batch: int, context: int, nkv: int, d: int):
+    nblk = -(-context // 64) + 1
+    kp = torch.randn(batch * nblk, nkv, 64, d, device=DEV).to(BF)
+    vp = torch.randn_like(kp)
+    table = torch.arange(batch * nblk, dtype=torch.int32, device=DEV).reshape(batch, nblk)
+    return kp, vp, table
+
+
+def attention_decode(a) -> None:
+    B, nh, nkv, d = a.batch, a.heads, a.kv_heads, a.head_dim
+    kp, vp, table = _cache(B, a.context, nkv, d)
+    q = torch.randn(B, nh * d, device=DEV).to(BF)
+    out = torch.empty_like(q)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    kv = torch.full((B,), a.context, dtype=torch.int32, device=DEV)
+    chunk = 128 if a.kernel == "tc" else 256
+    splits = -(-a.context // chunk)
+    na, nm = ops.attention_simt_scratch(B, nh, d, splits)
+    acc, ml = torch.empty(na, device=DEV), torch.empty(nm, device=DEV)
+    cnt = torch.zeros(B * nh, dtype=torch.int32, device=DEV)
+    status = ops.device_status(DEV)
+    scale = 1 / math.sqrt(d)
+    if a.kernel == "tc":
+        fn = lambda: ops.attention_decode_tc(out, q, kp, vp, table, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt, status)
+    else:
+        fn = lambda: ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt)
+    us = _time(fn, a.warmup, a.iters, a.graph)
+    nbytes = B * a.context * nkv * d * 2 * 2
+    print(f"attention_decode[{a.kernel}] batch={B} context={a.context} heads={nh}/{nkv} d={d}: {us:.1f} us  "
+          f"cache {nbytes / us / 1e3:.0f} GB/s ({nbytes / 1e6:.1f} MB)")
+
+
+def attention_prefill(a) -> None:
+    nh, nkv, d, T = a.heads, a.kv_heads, a.head_dim, a.tokens
+    kp, vp, table = _cache(a.batch, T, nkv, d)
+    q = torch.randn(a.batch * T, nh * d, device=DEV).to(BF)
+    out = torch.empty_like(q)
+    slots = torch.arange(a.batch, dtype=torch.int32, device=DEV)
+    cu = (torch.arange(a.batch + 1, dtype=torch.int32, device=DEV) * T).contiguous()
+    kv = torch.full((a.batch,), T, dtype=torch.int32, device=DEV)
+    status = ops.device_status(DEV)
+    fn = lambda: ops.attention_prefill_tc(out, q, kp, vp, table, cu, slots, kv, a.batch, T, nh, nkv, d, 1 / math.sqrt(d), 0, status)
+    us = _time(fn, a.warmup, a.iters, a.graph)
+    flops = 4.0 * nh * d * (T * (T + 1) / 2) * a.batch
+    print(f"attention_prefill_tc batch={a.batch} tokens={T} heads={nh}/{nkv} d={d}: {us:.1f} us  {flops / us / 1e6:.1f} TFLOP/s (causal)")
+
+
+def small(a) -> None:
+    B, H, nh, nkv, d, V = a.tokens, a.hidden, a.heads, a.kv_heads, a.head_dim, a.vocab
+    if a.op == "rmsnorm":
+        x = torch.randn(B, H, device=DEV)
+        gain = torch.ones(H, device=DEV, dtype=BF)
+        y = torch.empty(B, H, device=DEV, dtype=BF)
+        fn = lambda: ops.rmsnorm(y, x, gain, 1e-5)
+        nbytes = B * H * 6
+    elif a.op == "rope":
+        kp, vp, table = _cache(B, a.context, nkv, d)
+        qkv = torch.randn(B, (nh + 2 * nkv) * d, device=DEV).to(BF)
+        qo = torch.empty(B, nh * d, device=DEV, dtype=BF)
+        inv = torch.rand(d // 2, device=DEV)
+        seq = torch.arange(B, dtype=torch.int32, device=DEV)
+        pos = torch.full((B,), a.context - 1, dtype=torch.int32, device=DEV)
+        gain = torch.ones(d, device=DEV, dtype=BF)
+        fn = lambda: ops.rope_kv(qkv, qo, kp, vp, table, 64, seq, pos, seq, inv, d, gain, gain, 1e-5, nh, nkv, d)
+        nbytes = B * (nh + 2 * nkv) * d * 4
+    else:
+        lg = torch.randn(B, V, device=DEV)
+        o = torch.empty(B, dtype=torch.int32, device=DEV)
+        pieces = B * (-(-V // ops.ARGMAX_PIECE))
+        sc = (torch.empty(pieces, device=DEV), torch.empty(pieces, dtype=torch.int32, device=DEV))
+        fn = lambda: ops.argmax(o, lg, None, sc)
+        nbytes = B * V * 4
+    us = _time(fn, a.warmup, a.iters, a.graph)
+    print(f"{a.op} rows={B}: {us:.1f} us  {nbytes / us / 1e3:.0f} GB/s")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="op", required=True)
+
+    def common(p):
+        p.add_argument("--warmup", type=int, default=3)
+        p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--graph", action="store_true")
+        p.add_argument("--heads", type=int, default=16)
+        p.add_argument("--kv-heads", type=int, default=4)
+        p.add_argument("--head-dim", type=int, default=128)
+    g = sub.add_parser("gemm")
+    common(g)
+    g.add_argument("--tokens", type=int, default=8)
+    g.add_argument("--out", type=int, default=6144)
+    g.add_argument("--inner", type=int, default=2048)
+    g.add_argument("--epilogue", default="store", choices=["store", "accumulate", "swiglu"])
+    g.add_argument("--float-out", action="store_true")
+    g.add_argument("--copies", type=int, default=8)
+    d = sub.add_parser("attention-decode")
+    common(d)
+    d.add_argument("--batch", type=int, default=8)
+    d.add_argument("--context", type=int, default=2100)
+    d.add_argument("--kernel", default="tc", choices=["tc", "stream"])
+    pf = sub.add_parser("attention-prefill")
+    common(pf)
+    pf.add_argument("--batch", type=int, default=1)
+    pf.add_argument("--tokens", type=int, default=2048)
+    for name in ("rmsnorm", "rope", "argmax"):
+        s = sub.add_parser(name)
+        common(s)
+        s.add_argument("--tokens", type=int, default=8)
+        s.add_argument("--hidden", type=int, default=2048)
+        s.add_argument("--vocab", type=int, default=120818)
+        s.add_argument("--context", type=int, default=2100)
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a CUDA device", file=sys.stderr)
+        return 1
+    {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill}.get(a.op, small)(a)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -406,6 +406,8 @@ def test_attention_prefill_tcgen05(nh, nkv, d, window):
     vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
     qs = [torch.randn(n, nh, d, device=DEV).to(dtype) for n in news]
     kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=5)
+    kp[kp == 99.0] = float("nan")    # rows that no sequence wrote
+    vp[vp == -99.0] = float("nan")
     scale = 1 / math.sqrt(d)
     q = torch.cat([x.reshape(x.shape[0], nh * d) for x in qs])
     cu = torch.tensor(np.concatenate([[0], np.cumsum(news)]), dtype=torch.int32, device=DEV)
@@ -426,3 +428,41 @@ def test_attention_prefill_tcgen05(nh, nkv, d, window):
     ref2 = torch.cat([_ref_attention(big_q[i].float(), keys[i].float(), vals[i].float(), news[i], window, scale)
                       for i in range(len(lens))])
     assert torch.allclose(out.double(), ref2, **_tol(dtype))
+
+
+@pytest.mark.parametrize("nh, nkv, window", [(16, 4, 0), (4, 4, 0), (32, 2, 0), (6, 2, 300), (10, 2, 70)])
+def test_attention_decode_tcgen05(nh, nkv, window):
+    """The tensor-core decode kernel (keys on the 128-row side, head_dim 128) against the float64
+    reference: lengths around its chunks of 128 keys and the cache's blocks of 64, a padding row,
+    and NaN in every cache row that no sequence has written."""
+    ops = _ops()
+    torch.manual_seed(nh)
+    dtype, d = torch.bfloat16, 128
+    lens = [1, 64, 65, 127, 128, 129, 700, 1025, 90]
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    qs = [torch.randn(1, nh, d, device=DEV).to(dtype) for _ in lens]
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=4)
+    kp[kp == 99.0] = float("nan")    # rows that no sequence wrote
+    vp[vp == -99.0] = float("nan")
+    rows = len(lens)
+    q = torch.cat([x.reshape(1, nh * d) for x in qs])
+    slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+    slots[8] = -1
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    splits = -(-max(lens) // 128) + 2
+    na, nm = ops.attention_simt_scratch(rows, nh, d, splits)
+    acc = torch.full((na,), float("nan"), device=DEV)
+    ml = torch.full((nm,), float("nan"), device=DEV)
+    counters = torch.zeros(rows * nkv, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out = torch.full((rows, nh * d), 5.0, dtype=dtype, device=DEV)
+    for _ in range(2):   # twice: the counters are left at zero
+        ops.attention_decode_tc(out, q, kp, vp, table, slots, kv, nh, nkv, d, scale, window, splits, acc, ml, counters, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and int(counters.abs().sum()) == 0
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, window, scale) for i in range(rows)])
+    assert torch.isfinite(out[:8].float()).all()
+    assert torch.allclose(out[:8].double(), ref[:8], **_tol(dtype))
+    assert (out[8] == 5.0).all()
