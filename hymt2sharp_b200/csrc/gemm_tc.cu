@@ -268,44 +268,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (m >= p.T) return;
                 const int n0 = b_row0 + c;                     // first output feature of the chunk
                 TC* dst = C + (size_t)m * p.ldc + n0;
-                float o[CH];
-#pragma unroll
-                for (int j = 0; j < CH; j++) o[j] = EPI == EPI_SWIGLU ? silu_mul(g[j], u[j]) : g[j];
                 const bool vec = n0 + CH <= p.N && (((uintptr_t)dst) & 15) == 0;
-                if (vec) {
-                    if constexpr (sizeof(TC) == 4) {
-                        float4* d4 = reinterpret_cast<float4*>(dst);
+                // eight outputs at a time: few values are live at once, one 16-byte store each (bfloat16)
+#pragma unroll 1
+                for (int j8 = 0; j8 < CH; j8 += 8) {
+                    float o[8];
 #pragma unroll
-                        for (int j = 0; j < CH / 4; j++) {
-                            float4 v = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                            if (EPI == EPI_ACCUMULATE) {
-                                const float4 old = d4[j];
-                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                    for (int j = 0; j < 8; j++) o[j] = EPI == EPI_SWIGLU ? silu_mul(g[j8 + j], u[j8 + j]) : g[j8 + j];
+                    if (vec) {
+                        if constexpr (sizeof(TC) == 4) {
+                            float4* d4 = reinterpret_cast<float4*>(dst + j8);
+#pragma unroll
+                            for (int q = 0; q < 2; q++) {
+                                float4 v = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                                if (EPI == EPI_ACCUMULATE) {
+                                    const float4 old = d4[q];
+                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                                }
+                                d4[q] = v;
                             }
-                            d4[j] = v;
-                        }
-                    } else {
-                        uint4* d4 = reinterpret_cast<uint4*>(dst);
+                        } else {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst + j8);
+                            if (EPI == EPI_ACCUMULATE) {
+                                const uint4 oldv = *d4;
+                                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&oldv);
 #pragma unroll
-                        for (int j = 0; j < CH / 8; j++) {
+                                for (int q = 0; q < 4; q++) { o[2 * q] += __low2float(oh[q]); o[2 * q + 1] += __high2float(oh[q]); }
+                            }
                             __nv_bfloat162 h[4];
 #pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                float a = o[8 * j + 2 * q], b = o[8 * j + 2 * q + 1];
-                                if (EPI == EPI_ACCUMULATE) {
-                                    a += to_float(dst[8 * j + 2 * q]);
-                                    b += to_float(dst[8 * j + 2 * q + 1]);
-                                }
-                                h[q] = __floats2bfloat162_rn(a, b);
-                            }
-                            d4[j] = *reinterpret_cast<uint4*>(h);
+                            for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
+                            *d4 = *reinterpret_cast<uint4*>(h);
                         }
-                    }
-                } else {
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < CH; j++) {
-                        if (n0 + j >= p.N) break;
-                        dst[j] = from_float<TC>(EPI == EPI_ACCUMULATE ? to_float(dst[j]) + o[j] : o[j]);
+                        for (int j = 0; j < 8; j++) {
+                            if (n0 + j8 + j >= p.N) break;
+                            dst[j8 + j] = from_float<TC>(EPI == EPI_ACCUMULATE ? to_float(dst[j8 + j]) + o[j] : o[j]);
+                        }
                     }
                 }
             }
