@@ -70,16 +70,40 @@ class BatchSampler:
         if self.any_filter:
             ops.filter_logits(logits, self.inv_temperature, self.top_k, self.top_p, self.min_p, self.penalty,
                               self.history, row_map)
-        need = rows * (-(-logits.shape[1] // ops.ARGMAX_PIECE))
-        if self._argmax_scratch is None or self._argmax_scratch[0].numel() < need:
-            self._argmax_scratch = (torch.empty(need, dtype=torch.float32, device=self.device),
-                                    torch.empty(need, dtype=torch.int32, device=self.device))
-        ops.argmax(out, logits, row_map, self._argmax_scratch)
+        ops.argmax(out, logits, row_map, self.ensure_argmax_scratch(rows, logits.shape[1]))
         if not self.all_greedy:
             ops.sample(out, logits, self.inv_temperature, self.rng, row_map)
         if self.any_filter and self.history is not None:
             ops.record_history(self.history, self.counts, out, row_map, rows)
         return out
+
+    # -- fixed buffers for captured graphs -----------------------------------------------------------
+    _TENSORS = ("inv_temperature", "rng", "top_k", "top_p", "min_p", "penalty", "history", "counts")
+
+    def signature(self) -> tuple:
+        """Two samplers with the same signature launch the same kernels on tensors of the same shapes."""
+        width = self.history.shape[1] if self.any_filter and self.history is not None else 0
+        return (len(self.params), self.all_greedy, self.any_filter, width)
+
+    def tensors(self) -> dict:
+        """The device tensors that sampling reads and writes, by name."""
+        return {n: getattr(self, n) for n in self._TENSORS if isinstance(getattr(self, n, None), torch.Tensor)}
+
+    def adopt(self, tensors: dict, argmax_scratch=None) -> None:
+        """Moves this sampler's state into the given tensors (same names and shapes, e.g. the ones a
+        captured graph points to) and uses them from now on."""
+        for name, t in tensors.items():
+            t.copy_(getattr(self, name))
+            setattr(self, name, t)
+        if argmax_scratch is not None:
+            self._argmax_scratch = argmax_scratch
+
+    def ensure_argmax_scratch(self, rows: int, vocab: int):
+        need = rows * (-(-vocab // ops.ARGMAX_PIECE))
+        if self._argmax_scratch is None or self._argmax_scratch[0].numel() < need:
+            self._argmax_scratch = (torch.empty(need, dtype=torch.float32, device=self.device),
+                                    torch.empty(need, dtype=torch.int32, device=self.device))
+        return self._argmax_scratch
 
     def snapshot(self):
         """The state that sampling changes (random streams, penalty rings), to put back later."""
