@@ -138,7 +138,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
-    const int b = blockIdx.z, head = blockIdx.y, qtile = blockIdx.x;
+    // the last query tiles of a prompt walk the most keys: they are scheduled first
+    const int b = blockIdx.z, head = blockIdx.y, qtile = gridDim.x - 1 - blockIdx.x;
     const int slot = p.slot_ids[b];
     const int tok0 = p.cu_seqlens[b], T_b = p.cu_seqlens[b + 1] - tok0;
     if (slot < 0 || qtile * Q_ROWS >= T_b) return;

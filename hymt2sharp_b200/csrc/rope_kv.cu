@@ -16,6 +16,8 @@
 // are dropped.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace {
 
 struct RopeKvParams {
@@ -93,6 +95,70 @@ rope_kv_kernel(RopeKvParams p, int tokens) {
     }
 }
 
+// bfloat16 with the whole head rotated (rope_dim == d, d = 64, 128 or 256): one warp per (token, head),
+// every lane holds E = d / 32 neighbouring values (one 4-, 8- or 16-byte load), the partner of a value
+// sits 16 lanes away, the sum of squares is a warp sum, nothing goes through shared memory.
+template <int E, typename TG>
+__global__ void __launch_bounds__(128)
+rope_kv_vec_kernel(RopeKvParams p, int tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_heads = p.nh + 2 * p.nkv;
+    const long item = (long)blockIdx.x * 4 + warp;
+    if (item >= (long)tokens * total_heads) return;
+    const int t = (int)(item / total_heads), head = (int)(item % total_heads);
+    constexpr int D = 32 * E;
+    const int pos = p.token_pos[t];
+    const int slot = p.slot_ids[p.token_seq[t]];
+    const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+    const bool write_kv = p.write_kv && slot >= 0;
+    if (!is_q && !write_kv) return;
+    using Vec = typename std::conditional<E == 2, uint32_t, typename std::conditional<E == 4, uint2, uint4>::type>::type;
+    const __nv_bfloat16* src = (const __nv_bfloat16*)p.qkv + ((size_t)t * total_heads + head) * D + lane * E;
+    size_t cache_row = 0;
+    if (!is_q) {
+        const int block = p.block_table[(size_t)slot * p.table_stride + pos / p.block_tokens];
+        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+        cache_row = (((size_t)block * p.nkv + kvh) * p.block_tokens + (pos % p.block_tokens)) * D + lane * E;
+    }
+    Vec raw = *reinterpret_cast<const Vec*>(src);
+    if (!is_q && !is_k) {
+        *reinterpret_cast<Vec*>((__nv_bfloat16*)p.v_cache + cache_row) = raw;
+        return;
+    }
+    float x[E];
+    const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int i = 0; i < E; i++) x[i] = __bfloat162float(rb[i]);
+    const bool low = lane < 16;                      // holds x[i] of the pairs (i, i + d/2); else x[i + d/2]
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+        const float angle = (float)pos * p.inv_freq[(lane & 15) * E + i];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const float x0 = low ? x[i] : other, x1 = low ? other : x[i];
+        x[i] = low ? x0 * cs - x1 * sn : x0 * sn + x1 * cs;
+        ss = fmaf(x[i], x[i], ss);
+    }
+    const TG* gain = (const TG*)(is_q ? p.q_gain : p.k_gain);
+    if (gain) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)D + p.eps);
+#pragma unroll
+        for (int i = 0; i < E; i++) x[i] = x[i] * scale * to_float(gain[lane * E + i]);
+    }
+    Vec outv;
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&outv);
+#pragma unroll
+    for (int i = 0; i < E; i++) ob[i] = __float2bfloat16_rn(x[i]);
+    __nv_bfloat16* dst = is_q ? (__nv_bfloat16*)p.q_out + ((size_t)t * p.nh + head) * D + lane * E
+                              : (__nv_bfloat16*)p.k_cache + cache_row;
+    *reinterpret_cast<Vec*>(dst) = outv;
+}
+
 }  // namespace
 
 HYMT2_API int hymt2_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache, int dtype,
@@ -114,6 +180,15 @@ HYMT2_API int hymt2_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v
     const long items = (long)tokens * (nh + 2 * nkv);
     HYMT2_REQUIRE((items + 3) / 4 <= 2147483647L, "rope_kv: too many (token, head) pairs");
     const unsigned blocks = (unsigned)((items + 3) / 4);
+    if (dtype == HYMT2_BF16 && rope_dim == d && (d == 64 || d == 128 || d == 256) && (uintptr_t)qkv % 16 == 0 &&
+        (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0) {
+#define HYMT2_ROPE_VEC(E_)                                                                                          \
+        if (gain_dtype == HYMT2_BF16) launch_pdl(rope_kv_vec_kernel<E_, __nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, p, tokens); \
+        else launch_pdl(rope_kv_vec_kernel<E_, float>, dim3(blocks), dim3(128), 0, stream, p, tokens)
+        if (d == 64) { HYMT2_ROPE_VEC(2); } else if (d == 128) { HYMT2_ROPE_VEC(4); } else { HYMT2_ROPE_VEC(8); }
+#undef HYMT2_ROPE_VEC
+        return hymt2_check_launch("rope_kv");
+    }
     HYMT2_DISPATCH_DTYPE(dtype, T, HYMT2_DISPATCH_DTYPE(gain_dtype, TG,
         (launch_pdl(rope_kv_kernel<T, TG>, dim3(blocks), dim3(128), smem, stream, p, tokens))));
     return hymt2_check_launch("rope_kv");

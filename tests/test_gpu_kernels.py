@@ -39,7 +39,7 @@ def test_embed(dtype):
                                            (torch.float32, torch.bfloat16, torch.bfloat16),
                                            (torch.float32, torch.float32, torch.bfloat16),
                                            (torch.bfloat16, torch.bfloat16, torch.float32)])
-@pytest.mark.parametrize("dim", [70, 1000, 2052])
+@pytest.mark.parametrize("dim", [70, 1000, 2052, 768, 2048])
 def test_rmsnorm(xdt, gdt, ydt, dim):
     ops = _ops()
     x = (torch.randn(37, dim, device=DEV) * 3).to(xdt)
@@ -191,7 +191,8 @@ def test_attention_prefill_and_decode(dtype, nh, nkv, d, window):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh, nkv, d, rope_dim, norm", [(8, 2, 64, 64, True), (3, 3, 16, 16, False),
-                                                        (6, 1, 48, 16, True), (4, 2, 128, 0, True)])
+                                                        (6, 1, 48, 16, True), (4, 2, 128, 0, True),
+                                                        (4, 2, 128, 128, True), (2, 1, 256, 256, False)])
 def test_rope_qknorm_kv_append(dtype, nh, nkv, d, rope_dim, norm):
     ops = _ops()
     torch.manual_seed(d)
