@@ -11,10 +11,13 @@
 //   normal   the 128-row side holds tokens, the BN side holds output features (prefill);
 //   swapped  the 128-row side holds output features (weight rows), the BN side holds tokens
 //            (BN = 16..128): a decode step streams every weight tile once at full tile height
-//            whatever the batch is.  With `splits` > 1 the K range is cut over gridDim.z; every
-//            CTA writes its partial tile to a workspace, and the CTA that arrives last at the
-//            tile's counter adds the partials in split order (so the sum does not depend on
-//            arrival order) and runs the epilogue.
+//            whatever the batch is.  With `splits` > 1 the K range is cut over gridDim.z.  The
+//            split CTAs of a tile form a thread-block cluster: each leaves its partial tile in
+//            its own shared memory, and after the cluster's barrier the first CTA adds the
+//            partials of its peers through distributed shared memory, in rank order (so the sum
+//            is the same every time), and runs the epilogue.  (A partial tile too large for the
+//            stage ring goes through a global workspace instead, folded by the CTA that arrives
+//            last at the tile's counter, also in split order.)
 // Epilogues: store, accumulate into float32 C, SwiGLU (silu(gate) * up; W holds N gate rows,
 // then N up rows; src/HyMT2Sharp/Ops.cs:1053).  Rows and K beyond the matrices are zero-filled
 // by TMA and masked in the epilogue, so any T and N are taken; K, lda and ldw must be multiples
@@ -31,6 +34,7 @@ namespace {
 constexpr int BLOCK_K = 64, UMMA_K = 16, TILE_M = 128, NUM_THREADS = 192, MAX_STAGES = 8;
 constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
+constexpr int PERSISTENT_BN = 256;   // tile width of the persistent kernel for many tokens
 
 enum { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
 
@@ -40,6 +44,7 @@ struct GemmTcParams {
     int T, N, K;             // tokens, output features, reduction length
     int stages;
     int splits, k_blocks_per_split;
+    int cluster;             // splits > 1: the split CTAs of a tile form a cluster and reduce through shared memory
     float* workspace;        // [tile][split][acc][BN][128] partial tiles (splits > 1)
     int* counters;           // [tile] arrivals, zero between launches
     int* status;
@@ -52,6 +57,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_plain(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -111,6 +119,18 @@ template <>
 __device__ __forceinline__ void tmem_load<32>(uint32_t taddr, float* v) {
     tmem_load<16>(taddr, v);
     tmem_load<16>(taddr + 16, v + 16);
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
@@ -311,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         };
 
-        if (p.splits == 1) {
+        if (!SWAPPED || p.splits == 1) {   // K is only split in the swapped orientation
             if (ok) {
                 for (int c = 0; c < OUT_COLS; c += CH) {
                     float g[CH], u[CH];
@@ -320,7 +340,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     emit(c, g, u);
                 }
             }
-        } else {
+        } else if (SWAPPED && p.cluster) {
+            // partial tile -> this CTA's shared memory (the stage ring is free now), [column][row];
+            // after the cluster's barrier the first CTA adds the partials of all its peers in rank order
+            for (int c = 0; c < ACC_COLS; c += CH) {
+                float g[CH];
+                if (ok && my_blocks > 0) tmem_load<CH>(lane_addr + c, g);
+                else {
+#pragma unroll
+                    for (int j = 0; j < CH; j++) g[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < CH; j++)
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(tiles + ((c + j) * TILE_M + row) * 4), "f"(g[j]) : "memory");
+            }
+            __syncwarp();
+            cluster_sync_all();
+            if (blockIdx.z == 0) {
+                for (int c = 0; c < OUT_COLS; c += CH) {
+                    float g[CH], u[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; j++) { g[j] = 0.f; u[j] = 0.f; }
+                    for (int r = 0; r < p.splits; r++) {       // rank order: the sum is the same every time
+#pragma unroll
+                        for (int j = 0; j < CH; j++) {
+                            g[j] += ld_cluster_f32(tiles + ((c + j) * TILE_M + row) * 4, r);
+                            if (EPI == EPI_SWIGLU) u[j] += ld_cluster_f32(tiles + ((BN + c + j) * TILE_M + row) * 4, r);
+                        }
+                    }
+                    emit(c, g, u);
+                }
+            }
+            __syncwarp();
+            cluster_sync_all();   // peers keep their shared memory until the first CTA has read it
+        } else if (SWAPPED) {
             // partial tile -> workspace [tile][split][acc][column][row]; the last arrival reduces
             const int tile = blockIdx.y * gridDim.x + blockIdx.x;
             float* ws_tile = p.workspace + (size_t)tile * p.splits * (ACC_COLS * TILE_M);
@@ -360,6 +413,176 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     emit(c, g, u);
                 }
             }
+        }
+    }
+
+    if (p.cluster && p.splits > 1 && warp < 2) {   // the warps without an epilogue take part in both barriers
+        __syncwarp();
+        cluster_sync_all();
+        cluster_sync_all();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// Persistent kernel for many tokens (normal orientation): one CTA per SM walks the output tiles
+// (token tiles fastest, so that neighbours in time share a weight tile in L2).  The stage ring
+// runs on across tiles, and two accumulators in tensor memory alternate: while the epilogue
+// warps drain one, the MMA thread already fills the other with the next tile.
+// --------------------------------------------------------------------------------------------
+template <int BN, int EPI, typename TC>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
+    constexpr bool SPLIT_B = EPI == EPI_SWIGLU;
+    constexpr int B_TILE_BYTES = BN * BLOCK_K * 2;
+    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int TMEM_COLS = 2 * BN;                       // 256 or 512
+    constexpr int OUT_COLS = SPLIT_B ? BN / 2 : BN;
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    pdl_launch_dependents();
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = p.stages;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * MAX_STAGES]), acc_empty0 = acc_full0 + 16;
+    volatile int* abort_flag = &abort_s;
+    const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int tiles_m = (p.T + TILE_M - 1) / TILE_M, tiles_n = (p.N + OUT_COLS - 1) / OUT_COLS;
+    const int num_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 128);
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: weights (B) of the first ring before the wait, then everything in order ----
+        long it = 0;
+        bool waited = false;
+        for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+            const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
+            for (int kb = 0; kb < num_k_blocks; kb++, it++) {
+                const int s = (int)(it % stages);
+                if (it >= stages && !mbar_wait(empty0 + 8 * s, (uint32_t)(((it / stages) & 1) ^ 1), abort_flag, p.status, 101)) break;
+                const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
+                const int k = kb * BLOCK_K;
+                mbar_expect_tx(bar, STAGE_BYTES);
+                if (SPLIT_B) {
+                    tma_load_2d(b_dst, &map_b, bar, k, b_row0);
+                    tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, bar, k, p.N + b_row0);
+                } else {
+                    tma_load_2d(b_dst, &map_b, bar, k, b_row0);
+                }
+                if (!waited) { pdl_wait(); waited = true; }   // the activations come from the kernel before
+                tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+            }
+        }
+        if (!waited) pdl_wait();
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ---------------------------------------------------------------------------
+        long it = 0;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, j++) {
+            const int buf = j & 1;
+            if (j >= 2 && !mbar_wait(acc_empty0 + 8 * buf, (uint32_t)((((j >> 1) - 1) & 1)), abort_flag, p.status, 104)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            bool ok = true;
+            for (int kb = 0; kb < num_k_blocks; kb++, it++) {
+                const int s = (int)(it % stages);
+                if (!(ok = mbar_wait(full0 + 8 * s, (uint32_t)((it / stages) & 1), abort_flag, p.status, 102))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_src = tiles + s * STAGE_BYTES, b_src = a_src + A_TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                    umma_bf16(tmem_base + buf * BN, smem_desc_sw128(a_src + k * UMMA_K * 2), smem_desc_sw128(b_src + k * UMMA_K * 2),
+                              IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);
+            }
+            if (!ok) break;
+            umma_commit(acc_full0 + 8 * buf);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue ---------------------------------------------------------------------------------
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        pdl_wait();   // C may still be in use by the kernel before
+        TC* C = (TC*)p.C;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, j++) {
+            const int buf = j & 1;
+            const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
+            if (!mbar_wait(acc_full0 + 8 * buf, (uint32_t)((j >> 1) & 1), abort_flag, p.status, 103)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+            const int m = a_row0 + row;
+#pragma unroll 1
+            for (int c = 0; c < OUT_COLS; c += 16) {
+                float g[16], u[16];
+                tmem_load<16>(lane_addr + c, g);
+                if (EPI == EPI_SWIGLU) tmem_load<16>(lane_addr + BN / 2 + c, u);
+                if (m >= p.T) continue;
+                const int n0 = b_row0 + c;
+                TC* dst = C + (size_t)m * p.ldc + n0;
+                const bool vec = n0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0;
+#pragma unroll
+                for (int j8 = 0; j8 < 16; j8 += 8) {
+                    float o[8];
+#pragma unroll
+                    for (int q = 0; q < 8; q++) o[q] = EPI == EPI_SWIGLU ? silu_mul(g[j8 + q], u[j8 + q]) : g[j8 + q];
+                    if (vec) {
+                        if constexpr (sizeof(TC) == 4) {
+                            float4* d4 = reinterpret_cast<float4*>(dst + j8);
+#pragma unroll
+                            for (int q = 0; q < 2; q++) {
+                                float4 v = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                                if (EPI == EPI_ACCUMULATE) {
+                                    const float4 old = d4[q];
+                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                                }
+                                d4[q] = v;
+                            }
+                        } else {
+                            __nv_bfloat162 h[4];
+#pragma unroll
+                            for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
+                            *reinterpret_cast<uint4*>(dst + j8) = *reinterpret_cast<uint4*>(h);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            if (n0 + j8 + q >= p.N) break;
+                            dst[j8 + q] = from_float<TC>(EPI == EPI_ACCUMULATE ? to_float(dst[j8 + q]) + o[q] : o[q]);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive_plain(acc_empty0 + 8 * buf);   // this thread has taken its row out of the accumulator
         }
     }
 
@@ -413,7 +636,26 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, 
         if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
         configured = true;
     }
-    cudaError_t e = launch_pdl(kernel, grid, dim3(NUM_THREADS), smem, stream, ma, mb, p);
+    cudaError_t e;
+    if (p.cluster && p.splits > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = hymt2_pdl_enabled() ? 1 : 0;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = (unsigned)p.splits;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, p);
+    } else {
+        e = launch_pdl(kernel, grid, dim3(NUM_THREADS), smem, stream, ma, mb, p);
+    }
     if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("gemm_tc");
 }
@@ -432,6 +674,8 @@ int dispatch_epilogue(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTc
 struct Plan {
     bool swapped;
     int bn, splits, k_blocks_per_split, stages;
+    bool cluster, persistent;
+    int sm_count;
     dim3 grid;
     size_t smem, workspace_floats;
     int tiles;
@@ -440,6 +684,8 @@ struct Plan {
 bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     const int num_k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     Plan& pl = *plan;
+    pl.sm_count = sm_count;
+    pl.persistent = false;
     pl.swapped = T <= 128;
     pl.splits = 1;
     int num_acc = 1;
@@ -452,13 +698,18 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         // the cut depends on N and K only, never on the number of tokens
         if (tiles < sm_count / 2) {
             int want = sm_count / tiles;
-            want = want > 16 ? 16 : want;
+            want = want > 8 ? 8 : want;   // a portable cluster holds at most 8 CTAs
             while (want > 1 && num_k_blocks / want < 2) want--;
             pl.splits = want;
         }
         pl.tiles = tiles;
     } else {
-        pl.bn = 128;
+        // many tiles: the persistent kernel with 256-wide tiles (one CTA per SM, epilogue hidden behind the
+        // next tile); few tiles: 128-wide tiles, two CTAs per SM, so that all SMs get work
+        const int wide_cols = epilogue == EPI_SWIGLU ? PERSISTENT_BN / 2 : PERSISTENT_BN;
+        const long wide_tiles = (long)((T + TILE_M - 1) / TILE_M) * ((N + wide_cols - 1) / wide_cols);
+        pl.persistent = wide_tiles * 2 >= 5L * sm_count;
+        pl.bn = pl.persistent ? PERSISTENT_BN : 128;
         const int out_cols = epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn;
         pl.grid = dim3((T + TILE_M - 1) / TILE_M, (N + out_cols - 1) / out_cols, 1);
         pl.tiles = pl.grid.x * pl.grid.y;
@@ -467,16 +718,48 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     pl.splits = (num_k_blocks + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
     pl.grid.z = pl.splits;
     const int stage_bytes = num_acc * A_TILE_BYTES + pl.bn * BLOCK_K * 2;
-    // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
     const long ctas = (long)pl.grid.x * pl.grid.y * pl.splits;
-    const int budget = ctas <= sm_count ? 200 * 1024 : 100 * 1024;
+    // A split whose whole K slice is short goes the cluster way, with shared memory for two CTAs on an SM
+    // (clusters must be placed whole inside a GPC; with one CTA per SM they would not all fit at once).
+    // Long slices stream best with one CTA per SM and a deep ring, and fold through the global workspace.
+    pl.cluster = pl.splits > 1 && pl.splits <= 8 && (long)pl.k_blocks_per_split * stage_bytes <= 128 * 1024 &&
+                 (size_t)num_acc * pl.bn * TILE_M * 4 <= 96 * 1024;
+    // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
+    const int budget = ((ctas <= sm_count && !pl.cluster) || pl.persistent) ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM
     int stages = budget / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
-    if (stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
+    if (pl.swapped && stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
     pl.stages = stages;
     pl.smem = (size_t)stages * stage_bytes + 1024;
-    pl.workspace_floats = pl.splits > 1 ? (size_t)pl.tiles * pl.splits * num_acc * pl.bn * TILE_M : 0;
+    if ((size_t)num_acc * pl.bn * TILE_M * 4 > (size_t)stages * stage_bytes) pl.cluster = false;   // the partial must fit the ring
+    pl.workspace_floats = (pl.splits > 1 && !pl.cluster) ? (size_t)pl.tiles * pl.splits * num_acc * pl.bn * TILE_M : 0;
     return true;
+}
+
+template <int BN, int EPI, typename TC>
+int launch_persistent_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, int ctas, size_t smem,
+                          cudaStream_t stream) {
+    auto kernel = gemm_tc_persistent_kernel<BN, EPI, TC>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+        configured = true;
+    }
+    cudaError_t e = launch_pdl(kernel, dim3(ctas), dim3(NUM_THREADS), smem, stream, ma, mb, p);
+    if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+    return hymt2_check_launch("gemm_tc (persistent)");
+}
+
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, const Plan& pl, int epilogue,
+                      int c_dtype, cudaStream_t stream) {
+    const int ctas = pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count;
+    if (epilogue == EPI_STORE && c_dtype == HYMT2_BF16) return launch_persistent_one<PERSISTENT_BN, EPI_STORE, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);
+    if (epilogue == EPI_STORE && c_dtype == HYMT2_F32) return launch_persistent_one<PERSISTENT_BN, EPI_STORE, float>(ma, mb, p, ctas, pl.smem, stream);
+    if (epilogue == EPI_ACCUMULATE && c_dtype == HYMT2_F32) return launch_persistent_one<PERSISTENT_BN, EPI_ACCUMULATE, float>(ma, mb, p, ctas, pl.smem, stream);
+    if (epilogue == EPI_SWIGLU && c_dtype == HYMT2_BF16) return launch_persistent_one<PERSISTENT_BN, EPI_SWIGLU, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);
+    hymt2_set_error("gemm_tc: epilogue %d with output type %d is not built", epilogue, c_dtype);
+    return HYMT2_ERR_ARGUMENT;
 }
 
 int sm_count_of_current_device() {
@@ -496,7 +779,7 @@ HYMT2_API int hymt2_gemm_tc_plan(int T, int N, int K, int epilogue, long* worksp
     Plan pl;
     make_plan(T, N, K, epilogue, sm_count_of_current_device(), &pl);
     *workspace_floats = (long)pl.workspace_floats;
-    *counters = pl.splits > 1 ? pl.tiles : 0;
+    *counters = (pl.splits > 1 && !pl.cluster) ? pl.tiles : 0;
     return HYMT2_OK;
 }
 
@@ -513,7 +796,7 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     Plan pl;
     make_plan(T, N, K, epilogue, sm_count_of_current_device(), &pl);
     HYMT2_REQUIRE(pl.grid.y <= 65535 && pl.grid.x <= 2147483647u, "gemm_tc: grid too large");
-    if (pl.splits > 1)
+    if (pl.splits > 1 && !pl.cluster)
         HYMT2_REQUIRE(workspace && counters && workspace_floats >= (long)pl.workspace_floats && num_counters >= pl.tiles,
                       "gemm_tc: the split needs %zu floats of workspace and %d counters", pl.workspace_floats, pl.tiles);
     const long w_rows = epilogue == EPI_SWIGLU ? 2L * N : N;
@@ -525,7 +808,7 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
         ok = make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, w_rows, K, ldw, epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn);
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
-    GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, workspace, counters, status};
+    GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status};
     if (pl.swapped) {
         switch (pl.bn) {
             case 16: return dispatch_epilogue<16, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
@@ -534,5 +817,6 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
             default: return dispatch_epilogue<128, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
         }
     }
+    if (pl.persistent) return launch_persistent(ma, mb, p, pl, epilogue, c_dtype, stream);
     return dispatch_epilogue<128, false>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
 }

@@ -310,11 +310,12 @@ def test_sampling_distribution_and_stream():
     assert states[0].tolist() != [0, 0, 0, 0] and [x & ((1 << 64) - 1) for x in states[1].tolist()] == ref.s
 
 
-# T <= 128 runs swapped (weights on the 128-row side, split K when there are few tiles),
-# larger T runs normal; sizes with tails in T, N and K (K only needs to be a multiple of 8)
+# T <= 128 runs swapped (weights on the 128-row side, split K when there are few tiles), larger T runs
+# normal, and with many tiles (the last two cases) the persistent kernel with two accumulators;
+# sizes with tails in T, N and K (K only needs to be a multiple of 8)
 @pytest.mark.parametrize("T, N, K", [(1, 1000, 200), (8, 256, 128), (16, 2048, 2048), (33, 130, 72), (64, 384, 6144),
                                      (100, 3072, 512), (128, 128, 64), (129, 1000, 200), (300, 384, 256),
-                                     (1000, 520, 1032)])
+                                     (1000, 520, 1032), (3000, 4000, 136), (2100, 5000, 72)])
 def test_gemm_tcgen05_epilogues(T, N, K):
     ops = _ops()
     torch.manual_seed(T + N)
