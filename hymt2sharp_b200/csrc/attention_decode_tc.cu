@@ -286,28 +286,45 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (last_s) {
             __threadfence();
-            for (int h = 0; h < g; h++) {
-                const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits;
-                float M = -INFINITY;
-                for (int sp = s_begin; sp < s_end; sp++) M = fmaxf(M, __ldcg(p.part_ml + (row + sp) * 2));
-                float L = 0.f, a = 0.f;
-                for (int sp0 = s_begin; sp0 < s_end; sp0 += 8) {   // 8 chunks' loads in flight, folded in order
-                    float pm[8], pl[8], pa[8];
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const bool in = sp0 + j < s_end;
-                        pm[j] = in ? __ldcg(p.part_ml + (row + sp0 + j) * 2) : -INFINITY;
-                        pl[j] = in ? __ldcg(p.part_ml + (row + sp0 + j) * 2 + 1) : 0.f;
-                        pa[j] = in ? __ldcg(p.part_acc + (row + sp0 + j) * D + t) : 0.f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const float c = pm[j] == -INFINITY ? 0.f : exp2f(pm[j] - M);
-                        L += pl[j] * c;
-                        a = fmaf(pa[j], c, a);
-                    }
+            // weights of the chunks first: (maximum, sum) of every (head, chunk) pair is read by one thread
+            // each, all at once; then every thread folds its d over heads and chunks with the loads of
+            // 16 chunks in flight at a time
+            const int n_chunks = s_end - s_begin;
+            float* w_s = reinterpret_cast<float*>(smem_raw);           // [g][n_chunks] weights, then [g] 1/L
+            for (int base_i = 0; base_i < g * n_chunks; base_i += 128) {
+                const int i = base_i + t;
+                if (i < g * n_chunks) {
+                    const int h = i / n_chunks, sp = s_begin + i % n_chunks;
+                    const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits + sp;
+                    w_s[i] = __ldcg(p.part_ml + row * 2);                    // maxima for now
+                    w_s[g * n_chunks + NQ + i] = __ldcg(p.part_ml + row * 2 + 1);   // sums
                 }
-                p.out[((size_t)b * p.nh + head0 + h) * D + t] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (t < g) {
+                float M = -INFINITY;
+                for (int c = 0; c < n_chunks; c++) M = fmaxf(M, w_s[t * n_chunks + c]);
+                float L = 0.f;
+                for (int c = 0; c < n_chunks; c++) {
+                    const float m_c = w_s[t * n_chunks + c];
+                    const float wgt = m_c == -INFINITY ? 0.f : exp2f(m_c - M);
+                    L += w_s[g * n_chunks + NQ + t * n_chunks + c] * wgt;
+                    w_s[t * n_chunks + c] = wgt;
+                }
+                w_s[g * n_chunks + t] = L > 0.f ? 1.0f / L : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int h = 0; h < g; h++) {
+                const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits + s_begin;
+                float a = 0.f;
+                for (int c0 = 0; c0 < n_chunks; c0 += 16) {
+                    float pa[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) pa[j] = c0 + j < n_chunks ? __ldcg(p.part_acc + (row + c0 + j) * D + t) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) a = fmaf(pa[j], c0 + j < n_chunks ? w_s[h * n_chunks + c0 + j] : 0.f, a);
+                }
+                p.out[((size_t)b * p.nh + head0 + h) * D + t] = __float2bfloat16_rn(a * w_s[g * n_chunks + h]);
             }
         }
     }

@@ -402,13 +402,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float g[CH], u[CH];
 #pragma unroll
                     for (int j = 0; j < CH; j++) { g[j] = 0.f; u[j] = 0.f; }
-                    for (int s = 0; s < p.splits; s++) {       // split order: the sum is the same every time
-                        const float* part = ws_tile + (size_t)s * (ACC_COLS * TILE_M);
+                    constexpr int SB = CH == 16 ? 4 : 1;       // splits whose loads are in flight together
+                    for (int s0 = 0; s0 < p.splits; s0 += SB) {  // split order: the sum is the same every time
+                        float pg[SB][CH], pu[SB][CH];
 #pragma unroll
-                        for (int j = 0; j < CH; j++) {
-                            g[j] += __ldcg(part + (size_t)(c + j) * TILE_M + row);
-                            if (EPI == EPI_SWIGLU) u[j] += __ldcg(part + (size_t)(BN + c + j) * TILE_M + row);
+                        for (int q = 0; q < SB; q++) {
+                            const bool in = s0 + q < p.splits;
+                            const float* part = ws_tile + (size_t)(in ? s0 + q : 0) * (ACC_COLS * TILE_M);
+#pragma unroll
+                            for (int j = 0; j < CH; j++) {
+                                pg[q][j] = in ? __ldcg(part + (size_t)(c + j) * TILE_M + row) : 0.f;
+                                if (EPI == EPI_SWIGLU) pu[q][j] = in ? __ldcg(part + (size_t)(BN + c + j) * TILE_M + row) : 0.f;
+                            }
                         }
+#pragma unroll
+                        for (int q = 0; q < SB; q++)
+#pragma unroll
+                            for (int j = 0; j < CH; j++) {
+                                g[j] += pg[q][j];
+                                if (EPI == EPI_SWIGLU) u[j] += pu[q][j];
+                            }
                     }
                     emit(c, g, u);
                 }
