@@ -21,7 +21,8 @@
 
 namespace {
 
-constexpr int CHUNK = 128, BLOCK_KEYS = 64, D = 128, NQ = 16, NUM_THREADS = 192;
+constexpr int CHUNK = 128, BLOCK_KEYS = 64, D = 128, NQ = 16;
+constexpr int NUM_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 and 6-9: two softmax groups that take turns
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct DecodeTcParams {
@@ -32,7 +33,7 @@ struct DecodeTcParams {
     float* part_acc;           // [rows, nh, max_splits, d]
     float* part_ml;            // [rows, nh, max_splits, 2]  (maximum in log2 units, sum)
     int* counters;             // [rows, nkv]
-    int table_stride, nh, nkv, window, max_splits;
+    int table_stride, nh, nkv, window, max_splits, rows;
     float scale_log2;
     int* status;
 };
@@ -97,50 +98,57 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+constexpr int STAGES = 3;        // chunks whose keys and values are in shared memory or on their way
+constexpr int MAX_ITEMS = 64;    // chunks that one CTA can take in one launch
+
 template <int G>   // query heads per kv head that the softmax loops cover (the group size rounded up)
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, DecodeTcParams p) {
-    // shared memory: K [d half][128 keys x 128 B], V [key block][d half][64 keys x 128 B],
-    // Q [d half][16 x 128 B], P^T [key block][16 x 128 B]
-    constexpr int K_BYTES = CHUNK * D * 2, V_BYTES = CHUNK * D * 2, Q_BYTES = NQ * D * 2;
+    // Persistent: a CTA takes the work items (chunk, kv head, sequence) w = blockIdx.x, + gridDim.x, ...
+    // Per stage of shared memory: K [d half][128 keys x 128 B], V [key block][d half][64 keys x 128 B],
+    // Q [d half][16 x 128 B], P^T [key block][16 x 128 B].  Two (S^T, O^T) pairs alternate in tensor memory,
+    // so the tensor core computes the next chunk's scores while the softmax warps work on this one.
+    constexpr int K_BYTES = CHUNK * D * 2, V_BYTES = CHUNK * D * 2, Q_BYTES = NQ * D * 2, P_BYTES = 2 * NQ * 128;
+    constexpr int STAGE_BYTES = K_BYTES + V_BYTES + Q_BYTES + P_BYTES;
     constexpr int HALF_K = CHUNK * 128, BOX = BLOCK_KEYS * 128;
-    constexpr uint32_t S_COL = 0, O_COL = 16, TMEM_COLS = 32;
-    // D float32, A and B bfloat16, N = 16, M = 128; S^T: both K-major; O^T: A (V^T) is MN-major
+    constexpr uint32_t TMEM_COLS = 64;   // buffer t: S^T at 32 t, O^T at 32 t + 16
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NQ >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     constexpr uint32_t IDESC_O = IDESC_S | (1u << 15);
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[4];
+    __shared__ __align__(8) uint64_t bars[3 * STAGES + 8];
     __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s, last_s;
-    __shared__ float red_max[4][NQ], red_sum[4][NQ];
+    __shared__ int abort_s;
+    __shared__ float red_max[2][4][NQ], red_sum[2][4][NQ];
+    __shared__ int done_last[MAX_ITEMS];
 
     pdl_launch_dependents();
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t k_smem = base, v_smem = k_smem + K_BYTES, q_smem = v_smem + V_BYTES, p_smem = q_smem + Q_BYTES;
-    const uint32_t kq_full = smem_u32(&bars[0]), v_full = kq_full + 8, s_done = kq_full + 16, p_ready = kq_full + 24;
+    auto k_of = [&](int s) { return base + s * STAGE_BYTES; };
+    auto v_of = [&](int s) { return base + s * STAGE_BYTES + K_BYTES; };
+    auto q_of = [&](int s) { return base + s * STAGE_BYTES + K_BYTES + V_BYTES; };
+    auto p_of = [&](int s) { return base + s * STAGE_BYTES + K_BYTES + V_BYTES + Q_BYTES; };
+    const uint32_t kq_full = smem_u32(&bars[0]), v_full = kq_full + 8 * STAGES, stage_free = kq_full + 16 * STAGES;
+    const uint32_t s_done = smem_u32(&bars[3 * STAGES]), p_ready = s_done + 16, o_done = s_done + 32, tmem_free = s_done + 48;
     volatile int* abort_flag = &abort_s;
-    pdl_wait();   // q, the cache and the lengths come from the kernels before
-
-    const int slot = p.slot_ids[b];
-    if (slot < 0) return;
-    const int kv_len = p.kv_lens[b], pos = kv_len - 1;
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int chunk_begin = split * CHUNK;
-    if (chunk_begin > pos || chunk_begin + CHUNK <= lo) return;   // no visible key here: the merge skips it
-    const int g = p.nh / p.nkv, head0 = kvh * g;
-    const int blocks_here = min(2, (pos - chunk_begin) / BLOCK_KEYS + 1);   // cache blocks of the chunk that hold keys
+    const int g = p.nh / p.nkv;
+    const int total = p.rows * p.nkv * p.max_splits;
 
     if (threadIdx.x == 0) {
-        mbar_init(kq_full, 1);
-        mbar_init(v_full, 1);
-        mbar_init(s_done, 1);
-        mbar_init(p_ready, 128);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(kq_full + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(stage_free + 8 * s, 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(s_done + 8 * t, 1);
+            mbar_init(p_ready + 8 * t, 128);
+            mbar_init(o_done + 8 * t, 1);
+            mbar_init(tmem_free + 8 * t, 128);
+        }
         abort_s = 0;
-        last_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -151,180 +159,266 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
-    bool ok = true;
+    pdl_wait();   // q, the cache and the lengths come from the kernels before
+
+    // The items of this CTA, found once by 64 threads in parallel (their facts come from global memory:
+    // slot, length, block numbers) and kept in shared memory, valid ones first and in order of w.
+    struct Item { int w, b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, row0, row1; };
+    __shared__ Item items[MAX_ITEMS];
+    __shared__ int n_items_s, warp0_count;
+    if (threadIdx.x < 64) {
+        const int w = blockIdx.x + threadIdx.x * gridDim.x;
+        Item it;
+        it.w = w;
+        bool valid = w < total;
+        if (valid) {
+            it.split = w % p.max_splits;
+            it.kvh = (w / p.max_splits) % p.nkv;
+            it.b = w / (p.max_splits * p.nkv);
+            const int slot = p.slot_ids[it.b];
+            it.kv_len = p.kv_lens[it.b];
+            it.pos = it.kv_len - 1;
+            it.lo = p.window > 0 ? max(0, it.pos - p.window + 1) : 0;
+            it.chunk_begin = it.split * CHUNK;
+            valid = slot >= 0 && it.chunk_begin <= it.pos && it.chunk_begin + CHUNK > it.lo;
+            if (valid) {
+                it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
+                const int* table = p.block_table + (size_t)slot * p.table_stride + it.chunk_begin / BLOCK_KEYS;
+                it.row0 = (table[0] * p.nkv + it.kvh) * BLOCK_KEYS;
+                it.row1 = it.blocks_here > 1 ? (table[1] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
+            }
+        }
+        const unsigned ballot = __ballot_sync(0xffffffffu, valid);
+        if (warp == 0 && lane == 0) warp0_count = __popc(ballot);
+        asm volatile("bar.sync 3, 64;" ::: "memory");
+        const int index = (warp == 1 ? warp0_count : 0) + __popc(ballot & ((1u << lane) - 1));
+        if (valid) items[index] = it;
+        if (threadIdx.x == 63) n_items_s = warp0_count + __popc(ballot);
+    }
+    __syncthreads();
+    const int n_items = n_items_s;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: everything at once ------------------------------------------------------
-        const int* table = p.block_table + (size_t)slot * p.table_stride;
-        mbar_expect_tx(kq_full, Q_BYTES + blocks_here * BOX * 2);
-        mbar_expect_tx(v_full, blocks_here * BOX * 2);
-        for (int x = 0; x < 2; x++) tma_load_2d(q_smem + x * (NQ * 128), &map_q, kq_full, x * 64, b * p.nh + head0);
-        for (int kb = 0; kb < blocks_here; kb++) {
-            const int block = table[chunk_begin / BLOCK_KEYS + kb];
-            const int row = (block * p.nkv + kvh) * BLOCK_KEYS;
-            for (int x = 0; x < 2; x++) tma_load_2d(k_smem + x * HALF_K + kb * BOX, &map_k, kq_full, x * 64, row);
-            for (int x = 0; x < 2; x++) tma_load_2d(v_smem + (kb * 2 + x) * BOX, &map_v, v_full, x * 64, row);
+        // ---- producer -------------------------------------------------------------------------------
+        for (int n = 0; n < n_items; n++) {
+            const Item& it = items[n];
+            const int s = n % STAGES;
+            if (n >= STAGES && !mbar_wait(stage_free + 8 * s, (uint32_t)(((n / STAGES) - 1) & 1), abort_flag, p.status, 120)) break;
+            mbar_expect_tx(kq_full + 8 * s, Q_BYTES + it.blocks_here * BOX * 2);
+            mbar_expect_tx(v_full + 8 * s, it.blocks_here * BOX * 2);
+            for (int x = 0; x < 2; x++) tma_load_2d(q_of(s) + x * (NQ * 128), &map_q, kq_full + 8 * s, x * 64, it.b * p.nh + it.kvh * g);
+            for (int kb = 0; kb < it.blocks_here; kb++) {
+                const int row = kb == 0 ? it.row0 : it.row1;
+                for (int x = 0; x < 2; x++) tma_load_2d(k_of(s) + x * HALF_K + kb * BOX, &map_k, kq_full + 8 * s, x * 64, row);
+                for (int x = 0; x < 2; x++) tma_load_2d(v_of(s) + (kb * 2 + x) * BOX, &map_v, v_full + 8 * s, x * 64, row);
+            }
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ---------------------------------------------------------------------------
-        if (mbar_wait(kq_full, 0, abort_flag, p.status, 121)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // ---- MMA issuer: takes whatever is ready: the scores of the next item whose keys have landed (and
+        // whose accumulator pair is free), or the weighted sum of the oldest item whose P^T is written.
+        int next_s = 0, next_o = 0;       // next item that needs its scores / its weighted sum
+        uint32_t idle = 0;
+        while (next_o < n_items && !*abort_flag) {
+            bool progressed = false;
+            if (next_s < n_items && next_s <= next_o + 1) {
+                const int n = next_s, s = n % STAGES, t = n & 1;
+                if (mbar_try_wait(kq_full + 8 * s, (uint32_t)((n / STAGES) & 1)) &&
+                    (n < 2 || mbar_try_wait(tmem_free + 8 * t, (uint32_t)(((n >> 1) - 1) & 1)))) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < D / 16; k++) {
-                const uint32_t half = k / 4, in_box = (k % 4) * 32;
-                umma_bf16(tmem_base + S_COL, desc_k_major(k_smem + half * HALF_K + in_box),
-                          desc_k_major(q_smem + half * (NQ * 128) + in_box), IDESC_S, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < D / 16; k++) {
+                        const uint32_t half = k / 4, in_box = (k % 4) * 32;
+                        umma_bf16(tmem_base + 32 * t, desc_k_major(k_of(s) + half * HALF_K + in_box),
+                                  desc_k_major(q_of(s) + half * (NQ * 128) + in_box), IDESC_S, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(s_done + 8 * t);
+                    next_s++;
+                    progressed = true;
+                }
             }
-            umma_commit(s_done);
-            if (mbar_wait(p_ready, 0, abort_flag, p.status, 122) && mbar_wait(v_full, 0, abort_flag, p.status, 123)) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int kb = 0; kb < blocks_here; kb++)
+            if (next_o < next_s) {
+                const int n = next_o, s = n % STAGES, t = n & 1;
+                if (mbar_try_wait(p_ready + 8 * t, (uint32_t)((n >> 1) & 1)) &&
+                    mbar_try_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1))) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int kb = 0; kb < items[n].blocks_here; kb++)
 #pragma unroll
-                    for (int k = 0; k < BLOCK_KEYS / 16; k++)
-                        umma_bf16(tmem_base + O_COL, desc_mn_major(v_smem + kb * 2 * BOX + k * (16 * 128), BOX),
-                                  desc_k_major(p_smem + kb * (NQ * 128) + k * 32), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BLOCK_KEYS / 16; k++)
+                            umma_bf16(tmem_base + 32 * t + 16, desc_mn_major(v_of(s) + kb * 2 * BOX + k * (16 * 128), BOX),
+                                      desc_k_major(p_of(s) + kb * (NQ * 128) + k * 32), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(o_done + 8 * t);
+                    umma_commit(stage_free + 8 * s);
+                    next_o++;
+                    progressed = true;
+                }
             }
-            umma_commit(kq_full);   // second phase of this barrier: O^T is complete
+            if (progressed) idle = 0;
+            else if (++idle > WAIT_LIMIT) {   // nothing became ready for a long time: give up, flag it
+                *abort_flag = 1;
+                atomicExch(p.status, 121);
+            }
         }
     } else if (warp >= 2) {
-        // ---- softmax: thread = key -------------------------------------------------------------------
-        const int quarter = warp & 3, t = quarter * 32 + lane;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const int key = chunk_begin + t;
-        const bool visible = key >= lo && key <= pos;
-        float s[NQ];
-        ok = mbar_wait(s_done, 0, abort_flag, p.status, 124);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        tmem_load16(lane_addr + S_COL, s);
+        // ---- softmax (thread = key), then partial output (thread = d).  Two groups of four warps take turns:
+        // group 0 the even items of this CTA with accumulator pair 0, group 1 the odd ones with pair 1.
+        const int grp = (warp - 2) >> 2, quarter = warp & 3, t = quarter * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + 32 * grp;
+        auto group_sync = [&]() {
+            if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+            else asm volatile("bar.sync 2, 128;" ::: "memory");
+        };
+        bool ok = true;
+        for (int n = grp; ok && n < n_items; n += 2) {
+            const Item& it = items[n];
+            const int s = n % STAGES, use = n >> 1;   // `use`: how often this group's accumulators were used before
+            const int key = it.chunk_begin + t;
+            const bool visible = key >= it.lo && key <= it.pos;
+            const int head0 = it.kvh * g;
+            float sc[NQ];
+            if (!(ok = mbar_wait(s_done + 8 * grp, (uint32_t)(use & 1), abort_flag, p.status, 124))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            tmem_load16(lane_base, sc);
 #pragma unroll
-        for (int h = 0; h < G; h++) s[h] = (visible && h < g) ? s[h] * p.scale_log2 : -INFINITY;
-        // maximum per head over the 128 keys
-        float mx[G];
+            for (int h = 0; h < G; h++) sc[h] = (visible && h < g) ? sc[h] * p.scale_log2 : -INFINITY;
+            float mx[G];
 #pragma unroll
-        for (int h = 0; h < G; h++) {
-            mx[h] = s[h];
+            for (int h = 0; h < G; h++) {
+                mx[h] = sc[h];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
-        }
-        if (lane < G) {
-            float mine = mx[0];
-#pragma unroll
-            for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
-            red_max[quarter][lane] = mine;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        float psum[G];
-        const int kb = t / BLOCK_KEYS, kin = t % BLOCK_KEYS;
-        // the rows of P^T beyond the group stay zero: their columns of O^T are never read, but must be finite
-#pragma unroll
-        for (int h = G; h < NQ; h++) {
-            const uint32_t dst = p_smem + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"((unsigned short)0) : "memory");
-        }
-#pragma unroll
-        for (int h = 0; h < G; h++) {
-            const float M = fmaxf(fmaxf(red_max[0][h], red_max[1][h]), fmaxf(red_max[2][h], red_max[3][h]));
-            const float pj = (M == -INFINITY || s[h] == -INFINITY) ? 0.f : exp2f(s[h] - M);
-            const __nv_bfloat16 pb = __float2bfloat16_rn(pj);
-            psum[h] = __bfloat162float(pb);   // the sum uses what the tensor core multiplies with
-            mx[h] = M;
-            // P^T[h][key]: row h of the block's 16 x 128 B tile, 16-byte chunk (kin / 8) ^ (h & 7)
-            const uint32_t dst = p_smem + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&pb)) : "memory");
-        }
-        // rows of V at and past the sequence's length have never been written by this sequence:
-        // their weight is 0, but 0 x (whatever bits lie there) must stay 0
-        if (key >= kv_len && kb < blocks_here) {
-            for (int x = 0; x < 2; x++) {
-                const uint32_t rowp = v_smem + (kb * 2 + x) * BOX + kin * 128;
-                if (x == 0 && !mbar_wait(v_full, 0, abort_flag, p.status, 125)) break;
-#pragma unroll
-                for (int c = 0; c < 8; c++)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowp + c * 16), "r"(0) : "memory");
+                for (int o = 16; o > 0; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
             }
-        }
+            group_sync();   // red_max and red_sum of this group's item before are read
+            if (lane < G) {
+                float mine = mx[0];
 #pragma unroll
-        for (int h = 0; h < G; h++)
+                for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
+                red_max[grp][quarter][lane] = mine;
+            }
+            group_sync();
+            float psum[G];
+            const int kb = t / BLOCK_KEYS, kin = t % BLOCK_KEYS;
+            const uint32_t p_dst = p_of(s);
+            // the rows of P^T beyond the group stay zero: their columns of O^T are never read, but must be finite
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], o);
-        if (lane < G) {
-            float mine = psum[0];
+            for (int h = G; h < NQ; h++) {
+                const uint32_t dst = p_dst + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
+                asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"((unsigned short)0) : "memory");
+            }
 #pragma unroll
-            for (int h = 1; h < G; h++) mine = lane == h ? psum[h] : mine;
-            red_sum[quarter][lane] = mine;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(p_ready);
-        // ---- epilogue: thread = d ----------------------------------------------------------------------
-        ok = ok && mbar_wait(kq_full, 1, abort_flag, p.status, 126);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float o[NQ];
-        tmem_load16(lane_addr + O_COL, o);
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // red_sum of all four warps is written
+            for (int h = 0; h < G; h++) {
+                const float M = fmaxf(fmaxf(red_max[grp][0][h], red_max[grp][1][h]), fmaxf(red_max[grp][2][h], red_max[grp][3][h]));
+                const float pj = (M == -INFINITY || sc[h] == -INFINITY) ? 0.f : exp2f(sc[h] - M);
+                const __nv_bfloat16 pb = __float2bfloat16_rn(pj);
+                psum[h] = __bfloat162float(pb);   // the sum uses what the tensor core multiplies with
+                mx[h] = M;
+                // P^T[h][key]: row h of the block's 16 x 128 B tile, 16-byte chunk (kin / 8) ^ (h & 7)
+                const uint32_t dst = p_dst + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
+                asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&pb)) : "memory");
+            }
+            // rows of V at and past the sequence's length have never been written by this sequence:
+            // their weight is 0, but 0 x (whatever bits lie there) must stay 0
+            if (key >= it.kv_len && kb < it.blocks_here) {
+                for (int x = 0; x < 2; x++) {
+                    const uint32_t rowp = v_of(s) + (kb * 2 + x) * BOX + kin * 128;
+                    if (x == 0 && !mbar_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 125)) break;
 #pragma unroll
-        for (int h = 0; h < G; h++) {
-            if (h < g) {
-                const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits + split;
-                p.part_acc[row * D + t] = ok ? o[h] : 0.f;
-                if (t == h) {
-                    p.part_ml[row * 2] = mx[h];
-                    p.part_ml[row * 2 + 1] = red_sum[0][h] + red_sum[1][h] + red_sum[2][h] + red_sum[3][h];
+                    for (int c = 0; c < 8; c++)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowp + c * 16), "r"(0) : "memory");
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < G; h++)
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], o);
+            if (lane < G) {
+                float mine = psum[0];
+#pragma unroll
+                for (int h = 1; h < G; h++) mine = lane == h ? psum[h] : mine;
+                red_sum[grp][quarter][lane] = mine;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_ready + 8 * grp);
+            // partial output: thread = d
+            if (!(ok = mbar_wait(o_done + 8 * grp, (uint32_t)(use & 1), abort_flag, p.status, 126))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float o[NQ];
+            tmem_load16(lane_base + 16, o);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(tmem_free + 8 * grp);   // this pair of accumulators may be filled again
+            group_sync();                       // red_sum of all four warps is written
+#pragma unroll
+            for (int h = 0; h < G; h++) {
+                if (h < g) {
+                    const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + it.split;
+                    p.part_acc[row * D + t] = o[h];
+                    if (t == h) {
+                        p.part_ml[row * 2] = mx[h];
+                        p.part_ml[row * 2 + 1] = red_sum[grp][0][h] + red_sum[grp][1][h] + red_sum[grp][2][h] + red_sum[grp][3][h];
+                    }
                 }
             }
         }
-        // the chunk that arrives last folds all chunks of this kv head's heads, in chunk order
-        const int s_begin = lo / CHUNK, s_end = pos / CHUNK + 1;
+        const int n = n_items;
+        // All partials of this group are written.  One counter per (sequence, kv head) counts its finished chunks.
+        // The row is folded, in chunk order, by the group that computed the row's LAST chunk (so the folding is
+        // spread evenly over the CTAs): it waits, with a limit, until the counter shows that all chunks are in.
+        // One warp per (row, head), every lane four neighbouring d, the chunks' loads all in flight.
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (t == 0) {
-            int* counter = p.counters + (size_t)b * p.nkv + kvh;
-            const int arrived = atomicAdd(counter, 1);
-            last_s = arrived == s_end - s_begin - 1;
-            if (last_s) *counter = 0;
+        group_sync();
+        for (int i = grp + 2 * t; i < n; i += 256) {
+            const Item& it = items[i];
+            atomicAdd(p.counters + (size_t)it.b * p.nkv + it.kvh, 1);
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (last_s) {
-            __threadfence();
-            // weights of the chunks first: (maximum, sum) of every (head, chunk) pair is read by one thread
-            // each, all at once; then every thread folds its d over heads and chunks with the loads of
-            // 16 chunks in flight at a time
-            const int n_chunks = s_end - s_begin;
-            float* w_s = reinterpret_cast<float*>(smem_raw);           // [g][n_chunks] weights, then [g] 1/L
-            for (int base_i = 0; base_i < g * n_chunks; base_i += 128) {
-                const int i = base_i + t;
-                if (i < g * n_chunks) {
-                    const int h = i / n_chunks, sp = s_begin + i % n_chunks;
-                    const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits + sp;
-                    w_s[i] = __ldcg(p.part_ml + row * 2);                    // maxima for now
-                    w_s[g * n_chunks + NQ + i] = __ldcg(p.part_ml + row * 2 + 1);   // sums
-                }
+        group_sync();
+        int unit = 0;
+        for (int i = grp; i < n; i += 2) {
+            const Item& own = items[i];
+            if (own.split != own.pos / CHUNK) continue;      // not the row's last chunk
+            if (t == 0) {
+                volatile int* counter = p.counters + (size_t)own.b * p.nkv + own.kvh;
+                const int chunks = own.pos / CHUNK + 1 - own.lo / CHUNK;
+                uint32_t spins = 0;
+                while (*counter < chunks && ++spins < (1u << 22)) __nanosleep(64);
+                done_last[i] = *counter >= chunks;
+                if (done_last[i]) *counter = 0;              // ready for the next launch
+                else atomicExch(p.status, 128);              // a chunk never arrived: flag it, leave the row
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (t < g) {
-                float M = -INFINITY;
-                for (int c = 0; c < n_chunks; c++) M = fmaxf(M, w_s[t * n_chunks + c]);
-                float L = 0.f;
-                for (int c = 0; c < n_chunks; c++) {
-                    const float m_c = w_s[t * n_chunks + c];
-                    const float wgt = m_c == -INFINITY ? 0.f : exp2f(m_c - M);
-                    L += w_s[g * n_chunks + NQ + t * n_chunks + c] * wgt;
-                    w_s[t * n_chunks + c] = wgt;
-                }
-                w_s[g * n_chunks + t] = L > 0.f ? 1.0f / L : 0.f;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int h = 0; h < g; h++) {
-                const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits + s_begin;
-                float a = 0.f;
-                for (int c0 = 0; c0 < n_chunks; c0 += 16) {
-                    float pa[16];
+            group_sync();
+            if (!done_last[i]) continue;
+            const Item& it = items[i];
+            const int s_begin = it.lo / CHUNK, n_chunks = min(64, it.pos / CHUNK + 1 - s_begin);
+            for (int h = 0; h < g; h++, unit++) {
+                if ((unit & 3) != quarter) continue;
+                __threadfence();
+                const int head = it.kvh * g + h;
+                const size_t row = ((size_t)it.b * p.nh + head) * p.max_splits + s_begin;
+                const int c0 = lane, c1 = lane + 32;
+                const float m0 = c0 < n_chunks ? __ldcg(p.part_ml + (row + c0) * 2) : -INFINITY;
+                const float l0 = c0 < n_chunks ? __ldcg(p.part_ml + (row + c0) * 2 + 1) : 0.f;
+                const float m1 = c1 < n_chunks ? __ldcg(p.part_ml + (row + c1) * 2) : -INFINITY;
+                const float l1 = c1 < n_chunks ? __ldcg(p.part_ml + (row + c1) * 2 + 1) : 0.f;
+                const float M = warp_max(fmaxf(m0, m1));
+                const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+                const float L = warp_sum(l0 * w0 + l1 * w1);
+                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int cb = 0; cb < n_chunks; cb += 8) {
+                    float4 v[8];
 #pragma unroll
-                    for (int j = 0; j < 16; j++) pa[j] = c0 + j < n_chunks ? __ldcg(p.part_acc + (row + c0 + j) * D + t) : 0.f;
+                    for (int j = 0; j < 8; j++)
+                        v[j] = cb + j < n_chunks ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + (row + cb + j) * D) + lane)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) a = fmaf(pa[j], c0 + j < n_chunks ? w_s[h * n_chunks + c0 + j] : 0.f, a);
+                    for (int j = 0; j < 8; j++) {
+                        const int c = cb + j;
+                        const float wc = __shfl_sync(0xffffffffu, c < 32 ? w0 : w1, c & 31);
+                        a.x = fmaf(v[j].x, wc, a.x); a.y = fmaf(v[j].y, wc, a.y);
+                        a.z = fmaf(v[j].z, wc, a.z); a.w = fmaf(v[j].w, wc, a.w);
+                    }
                 }
-                p.out[((size_t)b * p.nh + head0 + h) * D + t] = __float2bfloat16_rn(a * w_s[g * n_chunks + h]);
+                __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(a.x * inv, a.y * inv), __floats2bfloat162_rn(a.z * inv, a.w * inv)};
+                *reinterpret_cast<uint2*>(p.out + ((size_t)it.b * p.nh + head) * D + lane * 4) = *reinterpret_cast<uint2*>(o2);
             }
         }
     }
@@ -379,7 +473,7 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
     HYMT2_REQUIRE(d == D, "attention_decode_tc: head_dim %d is not taken (128 is)", d);
     HYMT2_REQUIRE(block_tokens == BLOCK_KEYS, "attention_decode_tc: cache blocks must hold %d tokens", BLOCK_KEYS);
     HYMT2_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= NQ, "attention_decode_tc: at most %d heads per kv head", NQ);
-    HYMT2_REQUIRE(rows <= 65535 && nkv <= 65535 && max_splits > 0, "attention_decode_tc: grid too large");
+    HYMT2_REQUIRE(max_splits > 0 && max_splits <= 64, "attention_decode_tc: at most 64 chunks of 128 keys (8,192 positions) are taken, got %d", max_splits);
     HYMT2_REQUIRE(part_acc && part_ml && counters && status, "attention_decode_tc: scratch is needed");
     CUtensorMap mq, mk, mv;
     const long cache_rows = cache_blocks * nkv * BLOCK_KEYS;
@@ -387,8 +481,8 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
                     make_map(&mv, v_cache, cache_rows, d, d, BLOCK_KEYS);
     HYMT2_REQUIRE(ok, "attention_decode_tc: cuTensorMapEncodeTiled refused the operands");
     DecodeTcParams p{(__nv_bfloat16*)out, block_table, slot_ids, kv_lens, part_acc, part_ml, counters, table_stride, nh, nkv,
-                     window, max_splits, scale * 1.4426950408889634f, status};
-    constexpr size_t smem = 2 * CHUNK * D * 2 + NQ * D * 2 + 2 * NQ * 128 + 1024;
+                     window, max_splits, rows, scale * 1.4426950408889634f, status};
+    constexpr size_t smem = (size_t)STAGES * (2 * CHUNK * D * 2 + NQ * D * 2 + 2 * NQ * 128) + 1024;
     const int g = nh / nkv;
     auto kernel = g <= 1 ? attention_decode_tc_kernel<1> : g <= 2 ? attention_decode_tc_kernel<2>
                 : g <= 4 ? attention_decode_tc_kernel<4> : g <= 8 ? attention_decode_tc_kernel<8>
@@ -400,7 +494,17 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
         if (e != cudaSuccess) { hymt2_set_error("attention_decode_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
         configured[which] = true;
     }
-    cudaError_t e = launch_pdl(kernel, dim3(max_splits, nkv, rows), dim3(NUM_THREADS), smem, stream, mq, mk, mv, p);
+    // one CTA per SM walks the (chunk, kv head, sequence) items; a CTA takes at most MAX_ITEMS of them
+    const long total = (long)rows * nkv * max_splits;
+    int sms = 148;
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    long ctas = total < sms ? total : sms;
+    if ((total + ctas - 1) / ctas > MAX_ITEMS) ctas = (total + MAX_ITEMS - 1) / MAX_ITEMS;
+    cudaError_t e = launch_pdl(kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), smem, stream, mq, mk, mv, p);
     if (e != cudaSuccess) { hymt2_set_error("attention_decode_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("attention_decode_tc");
 }

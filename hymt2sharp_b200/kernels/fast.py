@@ -26,7 +26,7 @@ def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale,
     bt = k_plane.shape[2]
     if out.dtype != torch.bfloat16 or d not in (64, 128) or bt & (bt - 1):
         return False
-    if ctx.decode and d == 128 and bt == 64 and nh // nkv <= 16:
+    if ctx.decode and d == 128 and bt == 64 and nh // nkv <= 16 and ctx.max_kv_len <= 64 * DECODE_TC_CHUNK_KEYS:
         splits = max(1, -(-ctx.max_kv_len // DECODE_TC_CHUNK_KEYS))
         na, nm = ops.attention_simt_scratch(ctx.num_tokens, nh, d, splits)
         acc = torch.empty(na, dtype=torch.float32, device=out.device)
