@@ -12,8 +12,8 @@
 //   one thread per d writes the unnormalised partial (O^T, max, sum) of the chunk.
 // The K and V blocks of the chunk arrive by TMA, all in flight at once, so a step's cache
 // traffic is streamed at full tile size whatever the batch is; the tensor core sees the
-// cache once per kv head (all heads of the group share it).  The chunk that arrives last
-// at a row's counter folds all chunks of its heads in chunk order.
+// cache once per kv head (all heads of the group share it).  The warps that computed a
+// row's last chunk fold all chunks of the row in chunk order, each for its quarter of d.
 // Formulas: src/HyMT2Sharp/Ops.cs:462-532 (the reference's fused decode attention).
 #include "common.cuh"
 
@@ -31,8 +31,8 @@ struct DecodeTcParams {
     const int* slot_ids;
     const int* kv_lens;
     float* part_acc;           // [rows, nh, max_splits, d]
-    float* part_ml;            // [rows, nh, max_splits, 2]  (maximum in log2 units, sum)
-    int* counters;             // [rows, nkv]
+    float* part_ml;            // [rows, nh, max_splits, 4 quarters of d, 2]  (maximum in log2 units, sum)
+    int* counters;             // [rows, nkv, 4 quarters of d]
     int table_stride, nh, nkv, window, max_splits, rows;
     float scale_log2;
     int* status;
@@ -100,12 +100,14 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
 
 constexpr int STAGES = 3;        // chunks whose keys and values are in shared memory or on their way
 constexpr int MAX_ITEMS = 64;    // chunks that one CTA can take in one launch
+constexpr int MAX_ROWS = 512;    // sequences in one launch
+constexpr int FOLD_BATCH = 20;   // chunks whose partials are loaded together when a row is folded
 
 template <int G>   // query heads per kv head that the softmax loops cover (the group size rounded up)
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, DecodeTcParams p) {
-    // Persistent: a CTA takes the work items (chunk, kv head, sequence) w = blockIdx.x, + gridDim.x, ...
+    // Persistent: a CTA takes the work items (sequence, kv head, chunk) w = blockIdx.x, + gridDim.x, ...
     // Per stage of shared memory: K [d half][128 keys x 128 B], V [key block][d half][64 keys x 128 B],
     // Q [d half][16 x 128 B], P^T [key block][16 x 128 B].  Two (S^T, O^T) pairs alternate in tensor memory,
     // so the tensor core computes the next chunk's scores while the softmax warps work on this one.
@@ -121,7 +123,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     __shared__ float red_max[2][4][NQ], red_sum[2][4][NQ];
-    __shared__ int done_last[MAX_ITEMS];
+    __shared__ int n_items_s;
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,8 +136,19 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const uint32_t s_done = smem_u32(&bars[3 * STAGES]), p_ready = s_done + 16, o_done = s_done + 32, tmem_free = s_done + 48;
     volatile int* abort_flag = &abort_s;
     const int g = p.nh / p.nkv;
-    const int total = p.rows * p.nkv * p.max_splits;
 
+    // Three things at the same time: thread 0 sets up the barriers, warp 1 allocates tensor memory, and
+    // warps 2 and 3 find the items of this CTA.  The items' facts come from global memory (slots, lengths,
+    // block numbers) and are read BEFORE the wait for the kernel in front (see the producer): lengths,
+    // tables and every cache block but the one of the newest position were written by kernels that are
+    // long complete.
+    //
+    // Only chunks that hold visible keys are items: warp 2 counts them row by row (a running sum in shared
+    // memory), so w = blockIdx.x, + gridDim.x, ... below the total is always a real chunk and every CTA
+    // gets the same number of them, give or take one.
+    struct Item { int b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, row0, row1; };
+    __shared__ Item items[MAX_ITEMS];
+    __shared__ int row_first[MAX_ROWS + 1], row_slot[MAX_ROWS], row_len[MAX_ROWS];
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(kq_full + 8 * s, 1);
@@ -150,68 +163,111 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_v) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_q) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (warp == 2 || warp == 3) {
+        if (warp == 2) {
+            int running = 0;
+            for (int r0 = 0; r0 < p.rows; r0 += 32) {
+                const int r = r0 + lane;
+                int mine = 0;
+                if (r < p.rows) {
+                    const int slot = p.slot_ids[r], len = p.kv_lens[r];
+                    const int pos = len - 1, lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+                    row_slot[r] = slot;
+                    row_len[r] = len;
+                    if (slot >= 0 && len > 0) mine = (pos / CHUNK + 1 - lo / CHUNK) * p.nkv;
+                }
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                if (r < p.rows) row_first[r + 1] = running + incl;
+                running += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) row_first[0] = 0;
+        }
+        asm volatile("bar.sync 3, 64;" ::: "memory");
+        const int total = row_first[p.rows];
+        const int w = blockIdx.x + (threadIdx.x - 64) * gridDim.x;
+        if (w < total) {
+            int b = 0;                                        // the last row whose first item is <= w
+            for (int step = MAX_ROWS / 2; step > 0; step >>= 1)
+                if (b + step < p.rows && row_first[b + step] <= w) b += step;
+            Item it;
+            it.b = b;
+            it.kv_len = row_len[b];
+            it.pos = it.kv_len - 1;
+            it.lo = p.window > 0 ? max(0, it.pos - p.window + 1) : 0;
+            const int chunks = it.pos / CHUNK + 1 - it.lo / CHUNK, rem = w - row_first[b];
+            it.kvh = rem / chunks;
+            it.split = it.lo / CHUNK + rem % chunks;
+            it.chunk_begin = it.split * CHUNK;
+            it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
+            const int* table = p.block_table + (size_t)row_slot[b] * p.table_stride + it.chunk_begin / BLOCK_KEYS;
+            it.row0 = (table[0] * p.nkv + it.kvh) * BLOCK_KEYS;
+            it.row1 = it.blocks_here > 1 ? (table[1] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
+            items[threadIdx.x - 64] = it;
+        }
+        if (threadIdx.x == 64) n_items_s = total > (int)blockIdx.x ? min(MAX_ITEMS, (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1) : 0;
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
-    pdl_wait();   // q, the cache and the lengths come from the kernels before
-
-    // The items of this CTA, found once by 64 threads in parallel (their facts come from global memory:
-    // slot, length, block numbers) and kept in shared memory, valid ones first and in order of w.
-    struct Item { int w, b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, row0, row1; };
-    __shared__ Item items[MAX_ITEMS];
-    __shared__ int n_items_s, warp0_count;
-    if (threadIdx.x < 64) {
-        const int w = blockIdx.x + threadIdx.x * gridDim.x;
-        Item it;
-        it.w = w;
-        bool valid = w < total;
-        if (valid) {
-            it.split = w % p.max_splits;
-            it.kvh = (w / p.max_splits) % p.nkv;
-            it.b = w / (p.max_splits * p.nkv);
-            const int slot = p.slot_ids[it.b];
-            it.kv_len = p.kv_lens[it.b];
-            it.pos = it.kv_len - 1;
-            it.lo = p.window > 0 ? max(0, it.pos - p.window + 1) : 0;
-            it.chunk_begin = it.split * CHUNK;
-            valid = slot >= 0 && it.chunk_begin <= it.pos && it.chunk_begin + CHUNK > it.lo;
-            if (valid) {
-                it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
-                const int* table = p.block_table + (size_t)slot * p.table_stride + it.chunk_begin / BLOCK_KEYS;
-                it.row0 = (table[0] * p.nkv + it.kvh) * BLOCK_KEYS;
-                it.row1 = it.blocks_here > 1 ? (table[1] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
-            }
-        }
-        const unsigned ballot = __ballot_sync(0xffffffffu, valid);
-        if (warp == 0 && lane == 0) warp0_count = __popc(ballot);
-        asm volatile("bar.sync 3, 64;" ::: "memory");
-        const int index = (warp == 1 ? warp0_count : 0) + __popc(ballot & ((1u << lane) - 1));
-        if (valid) items[index] = it;
-        if (threadIdx.x == 63) n_items_s = warp0_count + __popc(ballot);
-    }
-    __syncthreads();
     const int n_items = n_items_s;
 
-    if (warp == 0 && lane == 0) {
-        // ---- producer -------------------------------------------------------------------------------
-        for (int n = 0; n < n_items; n++) {
+    if (warp == 0) {
+        // ---- producer: lane 0 announces the bytes, then every lane requests one box ---------------------
+        // The kernel in front of this one (rotation and cache append) writes q and the cache rows of the
+        // newest position, and lets this kernel start only once everything before ITSELF is complete.  So the
+        // keys and values of the first chunks, all but a sequence's last, are requested at once; q and the last
+        // chunks follow after the wait.
+        // box j of an item: 0, 1 q halves; 2 + 4 kb + {0, 1} the K halves of block kb, + {2, 3} its V halves
+        auto load_box = [&](const Item& it, int s, int j) {
+            if (j < 2) {
+                tma_load_2d(q_of(s) + j * (NQ * 128), &map_q, kq_full + 8 * s, j * 64, it.b * p.nh + it.kvh * g);
+            } else {
+                const int kb = (j - 2) >> 2, x = j & 1;
+                if (kb >= it.blocks_here) return;
+                const int row = kb == 0 ? it.row0 : it.row1;
+                if (((j - 2) & 2) == 0) tma_load_2d(k_of(s) + x * HALF_K + kb * BOX, &map_k, kq_full + 8 * s, x * 64, row);
+                else tma_load_2d(v_of(s) + (kb * 2 + x) * BOX, &map_v, v_full + 8 * s, x * 64, row);
+            }
+        };
+        const int ahead = min(STAGES, n_items);
+        if (lane < ahead) {
+            const Item& it = items[lane];
+            mbar_expect_tx(kq_full + 8 * lane, Q_BYTES + it.blocks_here * BOX * 2);
+            mbar_expect_tx(v_full + 8 * lane, it.blocks_here * BOX * 2);
+        }
+        __syncwarp();
+        const int my_n = lane / 10, my_j = lane % 10;     // three items of ten boxes each
+        const bool mine = my_n < ahead;
+        const bool early = mine && my_j >= 2 && items[my_n].split != items[my_n].pos / CHUNK;
+        if (early) load_box(items[my_n], my_n, my_j);
+        pdl_wait();
+        if (mine && !early) load_box(items[my_n], my_n, my_j);
+        for (int n = ahead; n < n_items; n++) {
             const Item& it = items[n];
             const int s = n % STAGES;
-            if (n >= STAGES && !mbar_wait(stage_free + 8 * s, (uint32_t)(((n / STAGES) - 1) & 1), abort_flag, p.status, 120)) break;
-            mbar_expect_tx(kq_full + 8 * s, Q_BYTES + it.blocks_here * BOX * 2);
-            mbar_expect_tx(v_full + 8 * s, it.blocks_here * BOX * 2);
-            for (int x = 0; x < 2; x++) tma_load_2d(q_of(s) + x * (NQ * 128), &map_q, kq_full + 8 * s, x * 64, it.b * p.nh + it.kvh * g);
-            for (int kb = 0; kb < it.blocks_here; kb++) {
-                const int row = kb == 0 ? it.row0 : it.row1;
-                for (int x = 0; x < 2; x++) tma_load_2d(k_of(s) + x * HALF_K + kb * BOX, &map_k, kq_full + 8 * s, x * 64, row);
-                for (int x = 0; x < 2; x++) tma_load_2d(v_of(s) + (kb * 2 + x) * BOX, &map_v, v_full + 8 * s, x * 64, row);
+            int freed = lane == 0 ? (int)mbar_wait(stage_free + 8 * s, (uint32_t)(((n / STAGES) - 1) & 1), abort_flag, p.status, 120) : 1;
+            freed = __shfl_sync(0xffffffffu, freed, 0);
+            if (!freed) break;
+            if (lane == 0) {
+                mbar_expect_tx(kq_full + 8 * s, Q_BYTES + it.blocks_here * BOX * 2);
+                mbar_expect_tx(v_full + 8 * s, it.blocks_here * BOX * 2);
             }
+            __syncwarp();
+            if (lane < 10) load_box(it, s, lane);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: takes whatever is ready: the scores of the next item whose keys have landed (and
@@ -268,6 +324,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             else asm volatile("bar.sync 2, 128;" ::: "memory");
         };
         bool ok = true;
+        pdl_wait();   // the partials, the counters and the output may still be in use by the kernels before
         for (int n = grp; ok && n < n_items; n += 2) {
             const Item& it = items[n];
             const int s = n % STAGES, use = n >> 1;   // `use`: how often this group's accumulators were used before
@@ -352,73 +409,78 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 if (h < g) {
                     const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + it.split;
                     p.part_acc[row * D + t] = o[h];
-                    if (t == h) {
-                        p.part_ml[row * 2] = mx[h];
-                        p.part_ml[row * 2 + 1] = red_sum[grp][0][h] + red_sum[grp][1][h] + red_sum[grp][2][h] + red_sum[grp][3][h];
-                    }
                 }
             }
+            if (lane < g) {   // every warp keeps its own copy of (maximum, sum): a warp folds what warps of its quarter wrote
+                float mine = mx[0];
+#pragma unroll
+                for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
+                const size_t row = ((size_t)it.b * p.nh + head0 + lane) * p.max_splits + it.split;
+                *reinterpret_cast<float2*>(p.part_ml + (row * 4 + quarter) * 2) =
+                    make_float2(mine, red_sum[grp][0][lane] + red_sum[grp][1][lane] + red_sum[grp][2][lane] + red_sum[grp][3][lane]);
+            }
         }
-        const int n = n_items;
-        // All partials of this group are written.  One counter per (sequence, kv head) counts its finished chunks.
-        // The row is folded, in chunk order, by the group that computed the row's LAST chunk (so the folding is
-        // spread evenly over the CTAs): it waits, with a limit, until the counter shows that all chunks are in.
-        // One warp per (row, head), every lane four neighbouring d, the chunks' loads all in flight.
+        // All partials of this warp are written.  One counter per (sequence, kv head, quarter of d) counts the
+        // chunks whose partials are in memory; a warp raises the counters of all its items at once (lane l the
+        // l-th item of the group).  A row is folded, in chunk order, by the warps that computed the row's LAST
+        // chunk, each for its quarter of d (so the folding is spread evenly over the CTAs): the warp waits, with
+        // a limit, until its counter shows that all chunks are in.
         __threadfence();
-        group_sync();
-        for (int i = grp + 2 * t; i < n; i += 256) {
-            const Item& it = items[i];
-            atomicAdd(p.counters + (size_t)it.b * p.nkv + it.kvh, 1);
+        __syncwarp();
+        if (ok && grp + 2 * lane < n_items) {
+            const Item& it = items[grp + 2 * lane];
+            atomicAdd(p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter, 1);
         }
-        group_sync();
-        int unit = 0;
-        for (int i = grp; i < n; i += 2) {
-            const Item& own = items[i];
-            if (own.split != own.pos / CHUNK) continue;      // not the row's last chunk
-            if (t == 0) {
-                volatile int* counter = p.counters + (size_t)own.b * p.nkv + own.kvh;
-                const int chunks = own.pos / CHUNK + 1 - own.lo / CHUNK;
+        for (int i = grp; ok && i < n_items; i += 2) {
+            const Item& it = items[i];
+            if (it.split != it.pos / CHUNK) continue;        // not the row's last chunk
+            const int s_begin = it.lo / CHUNK, n_chunks = it.pos / CHUNK + 1 - s_begin;
+            int* counter = p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter;
+            int seen = 0;
+            if (lane == 0) {
                 uint32_t spins = 0;
-                while (*counter < chunks && ++spins < (1u << 22)) __nanosleep(64);
-                done_last[i] = *counter >= chunks;
-                if (done_last[i]) *counter = 0;              // ready for the next launch
+                while ((seen = *reinterpret_cast<volatile int*>(counter)) < n_chunks && ++spins < (1u << 22)) __nanosleep(20);
+                if (seen >= n_chunks) *counter = 0;          // ready for the next launch
                 else atomicExch(p.status, 128);              // a chunk never arrived: flag it, leave the row
             }
-            group_sync();
-            if (!done_last[i]) continue;
-            const Item& it = items[i];
-            const int s_begin = it.lo / CHUNK, n_chunks = min(64, it.pos / CHUNK + 1 - s_begin);
-            for (int h = 0; h < g; h++, unit++) {
-                if ((unit & 3) != quarter) continue;
-                __threadfence();
-                const int head = it.kvh * g + h;
-                const size_t row = ((size_t)it.b * p.nh + head) * p.max_splits + s_begin;
-                const int c0 = lane, c1 = lane + 32;
-                const float m0 = c0 < n_chunks ? __ldcg(p.part_ml + (row + c0) * 2) : -INFINITY;
-                const float l0 = c0 < n_chunks ? __ldcg(p.part_ml + (row + c0) * 2 + 1) : 0.f;
-                const float m1 = c1 < n_chunks ? __ldcg(p.part_ml + (row + c1) * 2) : -INFINITY;
-                const float l1 = c1 < n_chunks ? __ldcg(p.part_ml + (row + c1) * 2 + 1) : 0.f;
-                const float M = warp_max(fmaxf(m0, m1));
-                const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
-                const float L = warp_sum(l0 * w0 + l1 * w1);
-                const float inv = L > 0.f ? 1.0f / L : 0.f;
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (seen < n_chunks) continue;
+            __threadfence();
+            // a lane takes four neighbouring d of one head: 8 lanes per head, 4 heads per round
+            const int head0 = it.kvh * g;
+            for (int unit = lane; unit < g * 8; unit += 32) {
+                const int h = unit >> 3, dd = quarter * 32 + (unit & 7) * 4;
+                const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + s_begin;
+                float M = -INFINITY, L = 0.f;
                 float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int cb = 0; cb < n_chunks; cb += 8) {
-                    float4 v[8];
+                for (int cb = 0; cb < n_chunks; cb += FOLD_BATCH) {
+                    float2 ml[FOLD_BATCH];
+                    float4 v[FOLD_BATCH];
 #pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        v[j] = cb + j < n_chunks ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + (row + cb + j) * D) + lane)
-                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j = 0; j < FOLD_BATCH; j++) {   // all loads of the batch are in flight together
+                        const bool in = cb + j < n_chunks;
+                        ml[j] = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((row + cb + j) * 4 + quarter) * 2))
+                                   : make_float2(-INFINITY, 0.f);
+                        v[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + (row + cb + j) * D + dd))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    float Mb = M;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int c = cb + j;
-                        const float wc = __shfl_sync(0xffffffffu, c < 32 ? w0 : w1, c & 31);
+                    for (int j = 0; j < FOLD_BATCH; j++) Mb = fmaxf(Mb, ml[j].x);
+                    const float keep = M == -INFINITY ? 0.f : exp2f(M - Mb);
+                    L *= keep; a.x *= keep; a.y *= keep; a.z *= keep; a.w *= keep;
+#pragma unroll
+                    for (int j = 0; j < FOLD_BATCH; j++) {
+                        const float wc = ml[j].x == -INFINITY ? 0.f : exp2f(ml[j].x - Mb);
+                        L = fmaf(ml[j].y, wc, L);
                         a.x = fmaf(v[j].x, wc, a.x); a.y = fmaf(v[j].y, wc, a.y);
                         a.z = fmaf(v[j].z, wc, a.z); a.w = fmaf(v[j].w, wc, a.w);
                     }
+                    M = Mb;
                 }
+                const float inv = L > 0.f ? 1.0f / L : 0.f;
                 __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(a.x * inv, a.y * inv), __floats2bfloat162_rn(a.z * inv, a.w * inv)};
-                *reinterpret_cast<uint2*>(p.out + ((size_t)it.b * p.nh + head) * D + lane * 4) = *reinterpret_cast<uint2*>(o2);
+                *reinterpret_cast<uint2*>(p.out + ((size_t)it.b * p.nh + head0 + h) * D + dd) = *reinterpret_cast<uint2*>(o2);
             }
         }
     }
@@ -463,7 +525,7 @@ bool make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld,
 
 // out, q: [rows, nh * 128] bfloat16, one new token per row; k_cache, v_cache: one layer's planes
 // [blocks][nkv][64][128].  max_splits >= ceil(longest kv_len / 128); part_acc holds
-// rows*nh*max_splits*128 floats, part_ml rows*nh*max_splits*2, counters rows*nkv zeroed ints.
+// rows*nh*max_splits*128 floats, part_ml rows*nh*max_splits*8, counters rows*nkv*4 zeroed ints.
 HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_cache, const void* v_cache,
                                         long cache_blocks, const int* block_table, int table_stride, int block_tokens,
                                         const int* slot_ids, const int* kv_lens, int rows, int nh, int nkv, int d,
@@ -475,6 +537,7 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
     HYMT2_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= NQ, "attention_decode_tc: at most %d heads per kv head", NQ);
     HYMT2_REQUIRE(max_splits > 0 && max_splits <= 64, "attention_decode_tc: at most 64 chunks of 128 keys (8,192 positions) are taken, got %d", max_splits);
     HYMT2_REQUIRE(part_acc && part_ml && counters && status, "attention_decode_tc: scratch is needed");
+    HYMT2_REQUIRE(rows <= MAX_ROWS, "attention_decode_tc: at most %d sequences in one launch, got %d", MAX_ROWS, rows);
     CUtensorMap mq, mk, mv;
     const long cache_rows = cache_blocks * nkv * BLOCK_KEYS;
     const bool ok = make_map(&mq, q, (long)rows * nh, d, d, NQ) && make_map(&mk, k_cache, cache_rows, d, d, BLOCK_KEYS) &&

@@ -40,8 +40,10 @@ template <typename T, typename TG>
 __global__ void __launch_bounds__(128)
 rope_kv_kernel(RopeKvParams p, int tokens) {
     extern __shared__ float smem[];  // [4 warps][d]
-    pdl_launch_dependents();
+    // Wait first, release after: the attention kernel that follows reads lengths, tables and old cache
+    // blocks before its own wait, which is only safe once everything in front of THIS kernel is complete.
     pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* row = smem + warp * p.d;
     const int total_heads = p.nh + 2 * p.nkv;
@@ -101,8 +103,10 @@ rope_kv_kernel(RopeKvParams p, int tokens) {
 template <int E, typename TG>
 __global__ void __launch_bounds__(128)
 rope_kv_vec_kernel(RopeKvParams p, int tokens) {
-    pdl_launch_dependents();
+    // Wait first, release after: the attention kernel that follows reads lengths, tables and old cache
+    // blocks before its own wait, which is only safe once everything in front of THIS kernel is complete.
     pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_heads = p.nh + 2 * p.nkv;
     const long item = (long)blockIdx.x * 4 + warp;

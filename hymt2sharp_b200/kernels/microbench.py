@@ -86,23 +86,29 @@ def _cache(batch: int, context: int, nkv: int, d: int):
 
 def attention_decode(a) -> None:
     B, nh, nkv, d = a.batch, a.heads, a.kv_heads, a.head_dim
-    kp, vp, table = _cache(B, a.context, nkv, d)
+    caches = [_cache(B, a.context, nkv, d) for _ in range(a.copies)]
+    table = caches[0][2]
     q = torch.randn(B, nh * d, device=DEV).to(BF)
     out = torch.empty_like(q)
     slots = torch.arange(B, dtype=torch.int32, device=DEV)
     cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
     kv = torch.full((B,), a.context, dtype=torch.int32, device=DEV)
+    i = [0]
     chunk = 128 if a.kernel == "tc" else 256
     splits = -(-a.context // chunk)
-    na, nm = ops.attention_simt_scratch(B, nh, d, splits)
+    na, nm, nc = ops.attention_decode_tc_scratch(B, nh, nkv, d, splits)
     acc, ml = torch.empty(na, device=DEV), torch.empty(nm, device=DEV)
-    cnt = torch.zeros(B * nh, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(max(nc, B * nh), dtype=torch.int32, device=DEV)
     status = ops.device_status(DEV)
     scale = 1 / math.sqrt(d)
-    if a.kernel == "tc":
-        fn = lambda: ops.attention_decode_tc(out, q, kp, vp, table, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt, status)
-    else:
-        fn = lambda: ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt)
+
+    def fn():
+        kp, vp, _ = caches[i[0] % a.copies]
+        i[0] += 1
+        if a.kernel == "tc":
+            ops.attention_decode_tc(out, q, kp, vp, table, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt, status)
+        else:
+            ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt)
     us = _time(fn, a.warmup, a.iters, a.graph)
     nbytes = B * a.context * nkv * d * 2 * 2
     print(f"attention_decode[{a.kernel}] batch={B} context={a.context} heads={nh}/{nkv} d={d}: {us:.1f} us  "
@@ -177,6 +183,7 @@ def main(argv=None) -> int:
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=2100)
     d.add_argument("--kernel", default="tc", choices=["tc", "stream"])
+    d.add_argument("--copies", type=int, default=8, help="caches that the calls rotate through, so that keys come from memory")
     pf = sub.add_parser("attention-prefill")
     common(pf)
     pf.add_argument("--batch", type=int, default=1)

@@ -264,14 +264,20 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                                        _ptr(part_ml), _stream()), "attention_simt", 2 if split_keys > 0 else 1)
 
 
+def attention_decode_tc_scratch(rows: int, nh: int, nkv: int, d: int, max_splits: int) -> tuple[int, int, int]:
+    """What attention_decode_tc needs: floats of partial outputs, floats of partial (maximum, sum), one
+    copy for each quarter of d, and zeroed int32 counters."""
+    return rows * nh * max_splits * d, rows * nh * max_splits * 8, rows * nkv * 4
+
+
 def attention_decode_tc(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                         block_table: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, nh: int, nkv: int,
                         d: int, scale: float, window: int, max_splits: int, part_acc: torch.Tensor,
                         part_ml: torch.Tensor, counters: torch.Tensor, status: torch.Tensor) -> None:
     """bfloat16 decode attention on the tcgen05 tensor cores with the keys on the 128-row side;
     head_dim 128, cache blocks of 64 tokens, at most 16 heads per kv head.  Chunks of 128 keys:
-    max_splits >= ceil(longest length / 128); scratch sizes as attention_simt_scratch, counters
-    rows*nkv zeroed ints."""
+    max_splits >= ceil(longest length / 128); scratch and counters as attention_decode_tc_scratch
+    says, the counters zeroed (the kernel leaves them zeroed)."""
     _need(out, "out", torch.bfloat16, 2); _need(q, "q", torch.bfloat16, 2)
     _need(k_plane, "k_plane", torch.bfloat16, 4); _need(v_plane, "v_plane", torch.bfloat16, 4)
     rows = out.shape[0]
@@ -280,8 +286,8 @@ def attention_decode_tc(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tenso
         raise KernelError(f"attention_decode_tc: shapes out {tuple(out.shape)} q {tuple(q.shape)} k {tuple(k_plane.shape)}")
     _need(block_table, "block_table", torch.int32, 2)
     _need(slot_ids, "slot_ids", torch.int32, 1); _need(kv_lens, "kv_lens", torch.int32, 1)
-    need_acc, need_ml = attention_simt_scratch(rows, nh, d, max_splits)
-    if part_acc.numel() < need_acc or part_ml.numel() < need_ml or counters.numel() < rows * nkv:
+    need_acc, need_ml, need_counters = attention_decode_tc_scratch(rows, nh, nkv, d, max_splits)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml or counters.numel() < need_counters:
         raise KernelError("attention_decode_tc: the scratch for the partials is too small")
     _check(_lib().hymt2_attention_decode_tc(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), c_long(k_plane.shape[0]),
                                             _ptr(block_table), c_int(block_table.stride(0)), c_int(k_plane.shape[2]),

@@ -454,10 +454,10 @@ def test_attention_decode_tcgen05(nh, nkv, window):
     kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(d)
     splits = -(-max(lens) // 128) + 2
-    na, nm = ops.attention_simt_scratch(rows, nh, d, splits)
+    na, nm, nc = ops.attention_decode_tc_scratch(rows, nh, nkv, d, splits)
     acc = torch.full((na,), float("nan"), device=DEV)
     ml = torch.full((nm,), float("nan"), device=DEV)
-    counters = torch.zeros(rows * nkv, dtype=torch.int32, device=DEV)
+    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
     out = torch.full((rows, nh * d), 5.0, dtype=dtype, device=DEV)
     for _ in range(2):   # twice: the counters are left at zero
