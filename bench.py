@@ -19,6 +19,7 @@ import os
 import statistics
 import subprocess
 import sys
+import shutil
 import tempfile
 import time
 
@@ -159,8 +160,11 @@ def main() -> int:
     point_batches = [] if args.no_points else [1, 64]
     biggest = max([args.batch] + point_batches)
     per_seq = -(-(PROMPT + warmup + steps + 8) // 64) * 64
-    engine = hymt2sharp_b200.load(folder, dtype="bfloat16", max_tokens=biggest * per_seq + 4096, max_batch=biggest,
-                                  max_sequence_tokens=CONTEXT)
+    try:
+        engine = hymt2sharp_b200.load(folder, dtype="bfloat16", max_tokens=biggest * per_seq + 4096, max_batch=biggest,
+                                      max_sequence_tokens=CONTEXT)
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)   # the weights are on the device now; leave nothing in the temporary folder
     cfg = engine.config
     gen = torch.Generator().manual_seed(1234)
     rand_prompt = lambda: torch.randint(0, cfg.vocab_size, (PROMPT,), generator=gen).tolist()

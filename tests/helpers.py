@@ -6,6 +6,7 @@ import json
 import os
 import subprocess
 import sys
+import shutil
 import tempfile
 
 import numpy as np
@@ -85,19 +86,22 @@ def run_trace(model_dir: str, dtype: str, steps: list, max_tokens: int, vocab: i
     text = "".join(json.dumps(s) + "\n" for s in steps)
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens)]
-    r = subprocess.run(cmd, input=text, capture_output=True, text=True, cwd=tempfile.gettempdir(), timeout=timeout)
-    assert r.returncode == 0, f"trace_run failed ({r.returncode}):\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
-    done = [l for l in r.stdout.splitlines() if l.startswith("done ")]
-    assert [l.split()[1] for l in done] == [str(s["step"]) for s in steps], "a 'done <step>' line is missing"
-    result = {}
-    for s in steps:
-        wanted = sum(len(e.get("want", [])) for e in s["entries"])
-        path = os.path.join(out_dir, f"{s['step']}.f32")
-        if wanted:
-            result[s["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
-        else:
-            assert not os.path.exists(path)
-    return result
+    try:
+        r = subprocess.run(cmd, input=text, capture_output=True, text=True, cwd=tempfile.gettempdir(), timeout=timeout)
+        assert r.returncode == 0, f"trace_run failed ({r.returncode}):\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
+        done = [l for l in r.stdout.splitlines() if l.startswith("done ")]
+        assert [l.split()[1] for l in done] == [str(s["step"]) for s in steps], "a 'done <step>' line is missing"
+        result = {}
+        for s in steps:
+            wanted = sum(len(e.get("want", [])) for e in s["entries"])
+            path = os.path.join(out_dir, f"{s['step']}.f32")
+            if wanted:
+                result[s["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
+            else:
+                assert not os.path.exists(path)
+        return result
+    finally:
+        shutil.rmtree(out_dir, ignore_errors=True)
 
 
 class TraceBuilder:
