@@ -99,6 +99,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with "add to what the accumulator holds" fixed, so that no predicate has to be computed
+__device__ __forceinline__ void umma_bf16_add(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -235,20 +243,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ---------------------------------------------------------------------
+        // One thread issues every MMA, and with few columns an MMA is over sooner than a chain of address
+        // arithmetic in that thread: so the loop carries the stage's descriptor along (the address sits in the
+        // low bits, in units of 16 bytes, and the ring is far too small to carry out of them) and adds constants.
+        constexpr uint64_t K_STEP = (UMMA_K * 2) >> 4, A2_STEP = A_TILE_BYTES >> 4, B_STEP = (NUM_ACC * A_TILE_BYTES) >> 4;
+        const uint64_t desc0 = smem_desc_sw128(tiles);
+        uint64_t adesc = desc0;
+        uint32_t s = 0, phase = 0;
         for (int i = 0; i < my_blocks; i++) {
-            const int s = i % stages;
-            if (!mbar_wait(full0 + 8 * s, (i / stages) & 1, abort_flag, p.status, 102)) break;
+            if (!mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_src = tiles + s * STAGE_BYTES, b_src = a_src + NUM_ACC * A_TILE_BYTES;
+            const uint64_t bdesc = adesc + B_STEP;
+            umma_bf16(tmem_base, adesc, bdesc, IDESC, i > 0 ? 1u : 0u);
+            if (NUM_ACC == 2) umma_bf16(tmem_base + BN, adesc + A2_STEP, bdesc, IDESC, i > 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                const uint64_t bdesc = smem_desc_sw128(b_src + k * UMMA_K * 2);
-                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                umma_bf16(tmem_base, smem_desc_sw128(a_src + k * UMMA_K * 2), bdesc, IDESC, acc);
-                if (NUM_ACC == 2)
-                    umma_bf16(tmem_base + BN, smem_desc_sw128(a_src + A_TILE_BYTES + k * UMMA_K * 2), bdesc, IDESC, acc);
+            for (int k = 1; k < BLOCK_K / UMMA_K; k++) {
+                umma_bf16_add(tmem_base, adesc + k * K_STEP, bdesc + k * K_STEP, IDESC);
+                if (NUM_ACC == 2) umma_bf16_add(tmem_base + BN, adesc + A2_STEP + k * K_STEP, bdesc + k * K_STEP, IDESC);
             }
             umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs have read it
+            if (++s == (uint32_t)stages) { s = 0; phase ^= 1; adesc = desc0; }
+            else adesc += (uint64_t)(STAGE_BYTES >> 4);
         }
         umma_commit(done_bar);             // the accumulator is complete once all MMAs are done
     } else if (warp >= 2) {
@@ -518,24 +533,28 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         }
         if (!waited) pdl_wait();
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ---------------------------------------------------------------------------
-        long it = 0;
+        // ---- MMA issuer: the stage's descriptor is carried along, see gemm_tc_kernel --------------
+        const uint64_t desc0 = smem_desc_sw128(tiles);
+        uint64_t adesc = desc0;
+        uint32_t s = 0, phase = 0;
         int j = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, j++) {
             const int buf = j & 1;
             if (j >= 2 && !mbar_wait(acc_empty0 + 8 * buf, (uint32_t)((((j >> 1) - 1) & 1)), abort_flag, p.status, 104)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             bool ok = true;
-            for (int kb = 0; kb < num_k_blocks; kb++, it++) {
-                const int s = (int)(it % stages);
-                if (!(ok = mbar_wait(full0 + 8 * s, (uint32_t)((it / stages) & 1), abort_flag, p.status, 102))) break;
+            const uint32_t acc_at = tmem_base + buf * BN;
+            for (int kb = 0; kb < num_k_blocks; kb++) {
+                if (!(ok = mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_src = tiles + s * STAGE_BYTES, b_src = a_src + A_TILE_BYTES;
+                const uint64_t bdesc = adesc + (A_TILE_BYTES >> 4);
+                umma_bf16(acc_at, adesc, bdesc, IDESC, kb > 0 ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < BLOCK_K / UMMA_K; k++)
-                    umma_bf16(tmem_base + buf * BN, smem_desc_sw128(a_src + k * UMMA_K * 2), smem_desc_sw128(b_src + k * UMMA_K * 2),
-                              IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                for (int k = 1; k < BLOCK_K / UMMA_K; k++)
+                    umma_bf16_add(acc_at, adesc + k * ((UMMA_K * 2) >> 4), bdesc + k * ((UMMA_K * 2) >> 4), IDESC);
                 umma_commit(empty0 + 8 * s);
+                if (++s == (uint32_t)stages) { s = 0; phase ^= 1; adesc = desc0; }
+                else adesc += (uint64_t)(STAGE_BYTES >> 4);
             }
             if (!ok) break;
             umma_commit(acc_full0 + 8 * buf);
