@@ -272,6 +272,11 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: takes whatever is ready: the scores of the next item whose keys have landed (and
         // whose accumulator pair is free), or the weighted sum of the oldest item whose P^T is written.
+        // The descriptors of stage 0 once; per instruction only constants are added (the address sits in the low
+        // bits in units of 16 bytes, and shared memory is too small to carry out of them).
+        const uint64_t k_desc0 = desc_k_major(k_of(0)), q_desc0 = desc_k_major(q_of(0)), p_desc0 = desc_k_major(p_of(0));
+        const uint64_t v_desc0 = desc_mn_major(v_of(0), BOX);
+        constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
         int next_s = 0, next_o = 0;       // next item that needs its scores / its weighted sum
         uint32_t idle = 0;
         while (next_o < n_items && !*abort_flag) {
@@ -281,11 +286,12 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 if (mbar_try_wait(kq_full + 8 * s, (uint32_t)((n / STAGES) & 1)) &&
                     (n < 2 || mbar_try_wait(tmem_free + 8 * t, (uint32_t)(((n >> 1) - 1) & 1)))) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t kd = k_desc0 + s * STAGE_STEP, qd = q_desc0 + s * STAGE_STEP;
 #pragma unroll
                     for (int k = 0; k < D / 16; k++) {
-                        const uint32_t half = k / 4, in_box = (k % 4) * 32;
-                        umma_bf16(tmem_base + 32 * t, desc_k_major(k_of(s) + half * HALF_K + in_box),
-                                  desc_k_major(q_of(s) + half * (NQ * 128) + in_box), IDESC_S, k > 0 ? 1u : 0u);
+                        constexpr int HALF_Q = NQ * 128;
+                        const uint64_t k_off = ((k / 4) * HALF_K + (k % 4) * 32) >> 4, q_off = ((k / 4) * HALF_Q + (k % 4) * 32) >> 4;
+                        umma_bf16(tmem_base + 32 * t, kd + k_off, qd + q_off, IDESC_S, k > 0 ? 1u : 0u);
                     }
                     umma_commit(s_done + 8 * t);
                     next_s++;
@@ -297,11 +303,17 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 if (mbar_try_wait(p_ready + 8 * t, (uint32_t)((n >> 1) & 1)) &&
                     mbar_try_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1))) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    for (int kb = 0; kb < items[n].blocks_here; kb++)
+                    const uint64_t vd = v_desc0 + s * STAGE_STEP, pd = p_desc0 + s * STAGE_STEP;
+                    const int blocks_here = items[n].blocks_here;
 #pragma unroll
-                        for (int k = 0; k < BLOCK_KEYS / 16; k++)
-                            umma_bf16(tmem_base + 32 * t + 16, desc_mn_major(v_of(s) + kb * 2 * BOX + k * (16 * 128), BOX),
-                                      desc_k_major(p_of(s) + kb * (NQ * 128) + k * 32), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int kb = 0; kb < 2; kb++) {
+                        if (kb < blocks_here) {
+#pragma unroll
+                            for (int k = 0; k < BLOCK_KEYS / 16; k++)
+                                umma_bf16(tmem_base + 32 * t + 16, vd + ((kb * 2 * BOX + k * (16 * 128)) >> 4),
+                                          pd + ((kb * (NQ * 128) + k * 32) >> 4), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
                     umma_commit(o_done + 8 * t);
                     umma_commit(stage_free + 8 * s);
                     next_o++;
