@@ -12,8 +12,10 @@
 // The running maximum of a row is only raised when the new maximum exceeds it by more than 2^8;
 // then the row's O in TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st).  Until then P is
 // taken relative to the older maximum, which gives the same quotient O / l.
-// Q, K and V tiles arrive by TMA (128-byte swizzle); K/V tiles are double-buffered; mbarriers
-// order producer, MMA issuer and softmax warps; every wait is bounded.
+// Q, K and V tiles arrive by TMA (128-byte swizzle); K/V tiles are double-buffered, and so is S in tensor
+// memory: the scores of tile i + 1 are computed while the softmax warps work on tile i, and P·V of tile i
+// runs while they work on tile i + 1.  mbarriers order producer, MMA issuer and softmax warps; every wait
+// is bounded.
 // Formulas: src/HyMT2Sharp/Ops.cs:359-455 (scores, kv head = head / group), :198-325 (softmax
 // over the visible keys), :535-595 (combine).  A query at position p sees keys
 // [max(0, p - window + 1), p].
@@ -127,14 +129,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // else every stage has a P region of its own
     constexpr bool P_IN_K = KV_TILE_BYTES >= P_BYTES;
     constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES + (P_IN_K ? 0 : P_BYTES);
-    constexpr int TMEM_COLS = 256;                          // S: columns [0, 64), O tile: [64, 64 + D)
-    constexpr uint32_t S_COL = 0, O_COL = 64;
+    constexpr int TMEM_COLS = 256;                          // S of even tiles: columns [0, 64), of odd tiles [64, 128); O: [128, 128 + D)
+    constexpr uint32_t S_COL = 0, O_COL = 128;
     // D float32, A and B bfloat16; S: both K-major, N = 64; O: B is MN-major, N = D
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KEY_TILE >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
     constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * KV_STAGES + 4];
+    __shared__ __align__(8) uint64_t bars[2 * KV_STAGES + 8];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -157,7 +159,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto v_of = [&](int s) { return kv_smem + s * STAGE_BYTES + KV_TILE_BYTES; };
     auto p_of = [&](int s) { return P_IN_K ? kv_smem + s * STAGE_BYTES : kv_smem + s * STAGE_BYTES + 2 * KV_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
-    const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), s_full = q_full + 8, p_full = q_full + 16, o_full = q_full + 24;
+    const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
+    const uint32_t s_full = q_full + 16, s_free = q_full + 32, p_full = q_full + 48;   // two of each: even and odd tiles
     volatile int* abort_flag = &abort_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -167,9 +170,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(kv_empty + 8 * s, 1);
         }
         mbar_init(q_full, 1);
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
         mbar_init(o_full, 1);
+        for (int t = 0; t < 2; t++) {
+            mbar_init(s_full + 8 * t, 1);
+            mbar_init(s_free + 8 * t, 128);
+            mbar_init(p_full + 8 * t, 128);
+        }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -206,28 +212,38 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int i = max(0, issued - KV_STAGES); i < issued; i++)
                 for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1); t++) {}
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ---------------------------------------------------------------------------
-        bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 112);
-        for (int i = 0; ok && i < num_tiles; i++) {
+        // ---- MMA issuer: S of the next tile goes out before P·V of this one -------------------------
+        // The descriptors of stage 0 once; per instruction only constants are added (the address sits in the
+        // low bits in units of 16 bytes, and shared memory is too small to carry out of them).
+        const uint64_t q_desc = desc_k_major(q_smem), k_desc0 = desc_k_major(k_of(0)), p_desc0 = desc_k_major(p_of(0));
+        const uint64_t v_desc0 = desc_mn_major(v_of(0), KEY_TILE * 128);
+        constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
+        auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T over d in steps of 16, into the S buffer of i's parity
             const int s = i % KV_STAGES;
-            const uint32_t k_src = k_of(s), v_src = v_of(s), p_src = p_of(s);
-            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
+            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) return false;
+            if (i >= 2 && !mbar_wait(s_free + 8 * (i & 1), ((i >> 1) - 1) & 1, abort_flag, p.status, 118)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // S = Q K^T over d in steps of 16
+            const uint64_t kd = k_desc0 + s * STAGE_STEP;
 #pragma unroll
             for (int k = 0; k < D / 16; k++) {
-                const uint32_t box = (k / 4), in_box = (k % 4) * 32;
-                umma_bf16(tmem_base + S_COL, desc_k_major(q_smem + box * (Q_ROWS * 128) + in_box),
-                          desc_k_major(k_src + box * (KEY_TILE * 128) + in_box), IDESC_S, k > 0 ? 1u : 0u);
+                const uint64_t q_off = ((k / 4) * (Q_ROWS * 128) + (k % 4) * 32) >> 4, k_off = ((k / 4) * (KEY_TILE * 128) + (k % 4) * 32) >> 4;
+                umma_bf16(tmem_base + S_COL + 64 * (i & 1), q_desc + q_off, kd + k_off, IDESC_S, k > 0 ? 1u : 0u);
             }
-            umma_commit(s_full);
+            umma_commit(s_full + 8 * (i & 1));
+            return true;
+        };
+        bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 112);
+        if (ok && num_tiles > 0) ok = issue_scores(0);
+        for (int i = 0; ok && i < num_tiles; i++) {
+            const int s = i % KV_STAGES;
+            if (i + 1 < num_tiles && !(ok = issue_scores(i + 1))) break;
             // O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
-            if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 114)) break;
+            if (!mbar_wait(p_full + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 114)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t pd = p_desc0 + s * STAGE_STEP, vd = v_desc0 + s * STAGE_STEP;
 #pragma unroll
             for (int k = 0; k < KEY_TILE / 16; k++)
-                umma_bf16(tmem_base + O_COL, desc_k_major(p_src + k * 32),
-                          desc_mn_major(v_src + k * (16 * 128), KEY_TILE * 128), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
+                umma_bf16(tmem_base + O_COL, pd + ((k * 32) >> 4), vd + ((k * (16 * 128)) >> 4), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
             umma_commit(kv_empty + 8 * s);
             umma_commit(o_full);
         }
@@ -241,19 +257,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < num_tiles; i++) {
-            if (!(ok = mbar_wait(s_full, i & 1, abort_flag, p.status, 115))) break;
+            if (!(ok = mbar_wait(s_full + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 115))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int key0 = (tile_begin + i) * KEY_TILE;
             float s[KEY_TILE];
-            tmem_load32(lane_addr + S_COL, s);
-            tmem_load32(lane_addr + S_COL + 32, s + 32);
+            tmem_load32(lane_addr + S_COL + 64 * (i & 1), s);
+            tmem_load32(lane_addr + S_COL + 64 * (i & 1) + 32, s + 32);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(s_free + 8 * (i & 1));   // the scores are in registers: this buffer may take the tile after next
+            // s stays unscaled: the scale (> 0) goes into the exponent's multiply-add; most tiles lie wholly
+            // inside the row's visible range and need no mask
             float tile_max = -INFINITY;
+            if (row_ok && key0 >= lo && key0 + KEY_TILE - 1 <= pos) {
 #pragma unroll
-            for (int c = 0; c < KEY_TILE; c++) {
-                const int key = key0 + c;
-                s[c] = (row_ok && key >= lo && key <= pos) ? s[c] * p.scale_log2 : -INFINITY;
-                tile_max = fmaxf(tile_max, s[c]);
+                for (int c = 0; c < KEY_TILE; c++) tile_max = fmaxf(tile_max, s[c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < KEY_TILE; c++) {
+                    const int key = key0 + c;
+                    s[c] = (row_ok && key >= lo && key <= pos) ? s[c] : -INFINITY;
+                    tile_max = fmaxf(tile_max, s[c]);
+                }
             }
+            tile_max *= p.scale_log2;
             // raise the row's maximum only when it grows by more than 2^8 (or at its first visible key)
             const bool raise = tile_max > m + 8.0f || (m == -INFINITY && tile_max > -INFINITY);
             const float corr = raise ? exp2f(m - tile_max) : 1.f;   // m = -inf: 0
@@ -273,6 +299,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             l *= corr;
             float psum = 0.f;
+            // a row that has seen no key yet (m = -inf) has only masked scores: -inf * scale + 0 = -inf, exp2 gives 0
+            const float neg_m = m == -INFINITY ? 0.f : -m;
             // P as bfloat16 into the swizzled K-major tile: row r, 16-byte chunk c8 at chunk (c8 ^ (r & 7))
             const uint32_t p_dst = p_of(i % KV_STAGES);
 #pragma unroll
@@ -280,8 +308,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 uint32_t packed[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const float p0 = m == -INFINITY ? 0.f : exp2f(s[c8 * 8 + 2 * j] - m);
-                    const float p1 = m == -INFINITY ? 0.f : exp2f(s[c8 * 8 + 2 * j + 1] - m);
+                    const float p0 = exp2f(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, neg_m));
+                    const float p1 = exp2f(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, neg_m));
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     // the sum uses the rounded values that the tensor core will multiply with
                     psum += __low2float(h) + __high2float(h);
@@ -306,7 +334,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full);
+            mbar_arrive(p_full + 8 * (i & 1));
         }
         if (ok) ok = mbar_wait(o_full, (num_tiles - 1) & 1, abort_flag, p.status, 117);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
