@@ -36,6 +36,7 @@ struct PrefillParams {
     const int* slot_ids;
     const int* kv_lens;
     int table_stride, nh, nkv, window;
+    int batch, qtiles, sm_count;
     float scale_log2;          // scale * log2(e)
     int* status;
 };
@@ -140,8 +141,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
-    // the last query tiles of a prompt walk the most keys: they are scheduled first
-    const int b = blockIdx.z, head = blockIdx.y, qtile = gridDim.x - 1 - blockIdx.x;
+    // The last query tiles of a prompt walk the most keys: CTAs are numbered by falling query tile, so the long
+    // ones start first and the short ones fill the gaps.  When all CTAs fit on the SMs at once (two each), the
+    // ones beyond the first per SM are numbered by RISING length instead: the SM that got the longest tile also
+    // gets the shortest.
+    int n = blockIdx.x;
+    const int total = gridDim.x, per_qtile = p.nh * p.batch;
+    if (total <= 2 * p.sm_count && n >= p.sm_count) n = p.sm_count + (total - 1 - n);
+    const int qtile = p.qtiles - 1 - n / per_qtile, head = (n % per_qtile) % p.nh, b = (n % per_qtile) / p.nh;
     const int slot = p.slot_ids[b];
     const int tok0 = p.cu_seqlens[b], T_b = p.cu_seqlens[b + 1] - tok0;
     if (slot < 0 || qtile * Q_ROWS >= T_b) return;
@@ -430,8 +437,13 @@ HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k
     const bool ok = make_map(&mq, q, tokens, (long)nh * d, (long)nh * d, Q_ROWS) &&
                     make_map(&mk, k_cache, cache_rows, d, d, KEY_TILE) && make_map(&mv, v_cache, cache_rows, d, d, KEY_TILE);
     HYMT2_REQUIRE(ok, "attention_prefill_tc: cuTensorMapEncodeTiled refused the operands");
+    const int qtiles = (max_new_tokens + Q_ROWS - 1) / Q_ROWS;
+    HYMT2_REQUIRE((long)qtiles * nh * batch <= 2147483647L, "attention_prefill_tc: too many tiles");
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     PrefillParams p{(__nv_bfloat16*)out, block_table, cu_seqlens, slot_ids, kv_lens, table_stride, nh, nkv, window,
-                    scale * 1.4426950408889634f, status};
-    dim3 grid((max_new_tokens + Q_ROWS - 1) / Q_ROWS, nh, batch);
+                    batch, qtiles, sms, scale * 1.4426950408889634f, status};
+    dim3 grid((unsigned)(qtiles * nh * batch), 1, 1);
     return d == 128 ? launch<128>(mq, mk, mv, p, grid, stream) : launch<64>(mq, mk, mv, p, grid, stream);
 }
