@@ -336,6 +336,11 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             else asm volatile("bar.sync 2, 128;" ::: "memory");
         };
         bool ok = true;
+        // The rows of P^T beyond the group are zero for good: their columns of O^T are never read, but must be
+        // finite.  Nothing else writes there, so they are cleared once, before the first P^T of this CTA.
+        for (int i = threadIdx.x - 64; i < STAGES * P_BYTES / 16; i += 256)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(p_of(i / (P_BYTES / 16)) + (i % (P_BYTES / 16)) * 16), "r"(0) : "memory");
+        asm volatile("bar.sync 4, 256;" ::: "memory");
         pdl_wait();   // the partials, the counters and the output may still be in use by the kernels before
         for (int n = grp; ok && n < n_items; n += 2) {
             const Item& it = items[n];
@@ -367,12 +372,6 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             float psum[G];
             const int kb = t / BLOCK_KEYS, kin = t % BLOCK_KEYS;
             const uint32_t p_dst = p_of(s);
-            // the rows of P^T beyond the group stay zero: their columns of O^T are never read, but must be finite
-#pragma unroll
-            for (int h = G; h < NQ; h++) {
-                const uint32_t dst = p_dst + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
-                asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"((unsigned short)0) : "memory");
-            }
 #pragma unroll
             for (int h = 0; h < G; h++) {
                 const float M = fmaxf(fmaxf(red_max[grp][0][h], red_max[grp][1][h]), fmaxf(red_max[grp][2][h], red_max[grp][3][h]));
