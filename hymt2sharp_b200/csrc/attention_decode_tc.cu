@@ -99,8 +99,9 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
 }
 
 constexpr int STAGES = 3;        // chunks whose keys and values are in shared memory or on their way
-constexpr int MAX_ITEMS = 64;    // chunks that one CTA can take in one launch
+constexpr int MAX_ITEMS = 64;    // chunks that one CTA holds in shared memory at a time (one round)
 constexpr int MAX_ROWS = 512;    // sequences in one launch
+constexpr int MAX_CHUNKS = 2048; // chunks of one sequence (262,144 positions)
 constexpr int FOLD_BATCH = 20;   // chunks whose partials are loaded together when a row is folded
 
 template <int G>   // query heads per kv head that the softmax loops cover (the group size rounded up)
@@ -149,358 +150,377 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     struct Item { int b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, row0, row1; };
     __shared__ Item items[MAX_ITEMS];
     __shared__ int row_first[MAX_ROWS + 1], row_slot[MAX_ROWS], row_len[MAX_ROWS];
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(kq_full + 8 * s, 1);
-            mbar_init(v_full + 8 * s, 1);
-            mbar_init(stage_free + 8 * s, 1);
-        }
-        for (int t = 0; t < 2; t++) {
-            mbar_init(s_done + 8 * t, 1);
-            mbar_init(p_ready + 8 * t, 128);
-            mbar_init(o_done + 8 * t, 1);
-            mbar_init(tmem_free + 8 * t, 128);
-        }
-        abort_s = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_k) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_v) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_q) : "memory");
-    }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp == 2 || warp == 3) {
-        if (warp == 2) {
-            int running = 0;
-            for (int r0 = 0; r0 < p.rows; r0 += 32) {
-                const int r = r0 + lane;
-                int mine = 0;
-                if (r < p.rows) {
-                    const int slot = p.slot_ids[r], len = p.kv_lens[r];
-                    const int pos = len - 1, lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-                    row_slot[r] = slot;
-                    row_len[r] = len;
-                    if (slot >= 0 && len > 0) mine = (pos / CHUNK + 1 - lo / CHUNK) * p.nkv;
-                }
-                int incl = mine;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += up;
-                }
-                if (r < p.rows) row_first[r + 1] = running + incl;
-                running += __shfl_sync(0xffffffffu, incl, 31);
+    // A CTA keeps MAX_ITEMS items in shared memory at a time; if it has more (many long sequences), it goes
+    // through them in rounds: the barriers are set up again, the next items are found, the pipeline refills.
+    for (int round = 0;; round++) {
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < STAGES; s++) {
+                mbar_init(kq_full + 8 * s, 1);
+                mbar_init(v_full + 8 * s, 1);
+                mbar_init(stage_free + 8 * s, 1);
             }
-            if (lane == 0) row_first[0] = 0;
+            for (int t = 0; t < 2; t++) {
+                mbar_init(s_done + 8 * t, 1);
+                mbar_init(p_ready + 8 * t, 128);
+                mbar_init(o_done + 8 * t, 1);
+                mbar_init(tmem_free + 8 * t, 128);
+            }
+            abort_s = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            if (round == 0) {
+                asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_k) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_v) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_q) : "memory");
+            }
         }
-        asm volatile("bar.sync 3, 64;" ::: "memory");
-        const int total = row_first[p.rows];
-        const int w = blockIdx.x + (threadIdx.x - 64) * gridDim.x;
-        if (w < total) {
-            int b = 0;                                        // the last row whose first item is <= w
-            for (int step = MAX_ROWS / 2; step > 0; step >>= 1)
-                if (b + step < p.rows && row_first[b + step] <= w) b += step;
-            Item it;
-            it.b = b;
-            it.kv_len = row_len[b];
-            it.pos = it.kv_len - 1;
-            it.lo = p.window > 0 ? max(0, it.pos - p.window + 1) : 0;
-            const int chunks = it.pos / CHUNK + 1 - it.lo / CHUNK, rem = w - row_first[b];
-            it.kvh = rem / chunks;
-            it.split = it.lo / CHUNK + rem % chunks;
-            it.chunk_begin = it.split * CHUNK;
-            it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
-            const int* table = p.block_table + (size_t)row_slot[b] * p.table_stride + it.chunk_begin / BLOCK_KEYS;
-            it.row0 = (table[0] * p.nkv + it.kvh) * BLOCK_KEYS;
-            it.row1 = it.blocks_here > 1 ? (table[1] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
-            items[threadIdx.x - 64] = it;
+        if (warp == 2 || warp == 3) {
+            if (warp == 2 && round == 0) {
+                int running = 0;
+                for (int r0 = 0; r0 < p.rows; r0 += 32) {
+                    const int r = r0 + lane;
+                    int mine = 0;
+                    if (r < p.rows) {
+                        const int slot = p.slot_ids[r], len = p.kv_lens[r];
+                        const int pos = len - 1, lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+                        row_slot[r] = slot;
+                        row_len[r] = len;
+                        if (slot >= 0 && len > 0) mine = (pos / CHUNK + 1 - lo / CHUNK) * p.nkv;
+                    }
+                    int incl = mine;
+    #pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += up;
+                    }
+                    if (r < p.rows) row_first[r + 1] = running + incl;
+                    running += __shfl_sync(0xffffffffu, incl, 31);
+                }
+                if (lane == 0) row_first[0] = 0;
+            }
+            asm volatile("bar.sync 3, 64;" ::: "memory");
+            const int total = row_first[p.rows];
+            const int w = blockIdx.x + (round * MAX_ITEMS + (int)threadIdx.x - 64) * gridDim.x;
+            if (w < total) {
+                int b = 0;                                        // the last row whose first item is <= w
+                for (int step = MAX_ROWS / 2; step > 0; step >>= 1)
+                    if (b + step < p.rows && row_first[b + step] <= w) b += step;
+                Item it;
+                it.b = b;
+                it.kv_len = row_len[b];
+                it.pos = it.kv_len - 1;
+                it.lo = p.window > 0 ? max(0, it.pos - p.window + 1) : 0;
+                const int chunks = it.pos / CHUNK + 1 - it.lo / CHUNK, rem = w - row_first[b];
+                it.kvh = rem / chunks;
+                it.split = it.lo / CHUNK + rem % chunks;
+                it.chunk_begin = it.split * CHUNK;
+                it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
+                const int* table = p.block_table + (size_t)row_slot[b] * p.table_stride + it.chunk_begin / BLOCK_KEYS;
+                it.row0 = (table[0] * p.nkv + it.kvh) * BLOCK_KEYS;
+                it.row1 = it.blocks_here > 1 ? (table[1] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
+                items[threadIdx.x - 64] = it;
+            }
+            if (threadIdx.x == 64) {
+                const int mine = total > (int)blockIdx.x ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;   // of all rounds
+                n_items_s = max(0, min(MAX_ITEMS, mine - round * MAX_ITEMS));
+            }
         }
-        if (threadIdx.x == 64) n_items_s = total > (int)blockIdx.x ? min(MAX_ITEMS, (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1) : 0;
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = tmem_base_s;
-    const int n_items = n_items_s;
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_base = tmem_base_s;
+        const int n_items = n_items_s;
+        if (n_items == 0) break;
 
-    if (warp == 0) {
-        // ---- producer: lane 0 announces the bytes, then every lane requests one box ---------------------
-        // The kernel in front of this one (rotation and cache append) writes q and the cache rows of the
-        // newest position, and lets this kernel start only once everything before ITSELF is complete.  So the
-        // keys and values of the first chunks, all but a sequence's last, are requested at once; q and the last
-        // chunks follow after the wait.
-        // box j of an item: 0, 1 q halves; 2 + 4 kb + {0, 1} the K halves of block kb, + {2, 3} its V halves
-        auto load_box = [&](const Item& it, int s, int j) {
-            if (j < 2) {
-                tma_load_2d(q_of(s) + j * (NQ * 128), &map_q, kq_full + 8 * s, j * 64, it.b * p.nh + it.kvh * g);
-            } else {
-                const int kb = (j - 2) >> 2, x = j & 1;
-                if (kb >= it.blocks_here) return;
-                const int row = kb == 0 ? it.row0 : it.row1;
-                if (((j - 2) & 2) == 0) tma_load_2d(k_of(s) + x * HALF_K + kb * BOX, &map_k, kq_full + 8 * s, x * 64, row);
-                else tma_load_2d(v_of(s) + (kb * 2 + x) * BOX, &map_v, v_full + 8 * s, x * 64, row);
-            }
-        };
-        const int ahead = min(STAGES, n_items);
-        if (lane < ahead) {
-            const Item& it = items[lane];
-            mbar_expect_tx(kq_full + 8 * lane, Q_BYTES + it.blocks_here * BOX * 2);
-            mbar_expect_tx(v_full + 8 * lane, it.blocks_here * BOX * 2);
-        }
-        __syncwarp();
-        const int my_n = lane / 10, my_j = lane % 10;     // three items of ten boxes each
-        const bool mine = my_n < ahead;
-        const bool early = mine && my_j >= 2 && items[my_n].split != items[my_n].pos / CHUNK;
-        if (early) load_box(items[my_n], my_n, my_j);
-        pdl_wait();
-        if (mine && !early) load_box(items[my_n], my_n, my_j);
-        for (int n = ahead; n < n_items; n++) {
-            const Item& it = items[n];
-            const int s = n % STAGES;
-            int freed = lane == 0 ? (int)mbar_wait(stage_free + 8 * s, (uint32_t)(((n / STAGES) - 1) & 1), abort_flag, p.status, 120) : 1;
-            freed = __shfl_sync(0xffffffffu, freed, 0);
-            if (!freed) break;
-            if (lane == 0) {
-                mbar_expect_tx(kq_full + 8 * s, Q_BYTES + it.blocks_here * BOX * 2);
-                mbar_expect_tx(v_full + 8 * s, it.blocks_here * BOX * 2);
+        if (warp == 0) {
+            // ---- producer: lane 0 announces the bytes, then every lane requests one box ---------------------
+            // The kernel in front of this one (rotation and cache append) writes q and the cache rows of the
+            // newest position, and lets this kernel start only once everything before ITSELF is complete.  So the
+            // keys and values of the first chunks, all but a sequence's last, are requested at once; q and the last
+            // chunks follow after the wait.
+            // box j of an item: 0, 1 q halves; 2 + 4 kb + {0, 1} the K halves of block kb, + {2, 3} its V halves
+            auto load_box = [&](const Item& it, int s, int j) {
+                if (j < 2) {
+                    tma_load_2d(q_of(s) + j * (NQ * 128), &map_q, kq_full + 8 * s, j * 64, it.b * p.nh + it.kvh * g);
+                } else {
+                    const int kb = (j - 2) >> 2, x = j & 1;
+                    if (kb >= it.blocks_here) return;
+                    const int row = kb == 0 ? it.row0 : it.row1;
+                    if (((j - 2) & 2) == 0) tma_load_2d(k_of(s) + x * HALF_K + kb * BOX, &map_k, kq_full + 8 * s, x * 64, row);
+                    else tma_load_2d(v_of(s) + (kb * 2 + x) * BOX, &map_v, v_full + 8 * s, x * 64, row);
+                }
+            };
+            const int ahead = min(STAGES, n_items);
+            if (lane < ahead) {
+                const Item& it = items[lane];
+                mbar_expect_tx(kq_full + 8 * lane, Q_BYTES + it.blocks_here * BOX * 2);
+                mbar_expect_tx(v_full + 8 * lane, it.blocks_here * BOX * 2);
             }
             __syncwarp();
-            if (lane < 10) load_box(it, s, lane);
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer: takes whatever is ready: the scores of the next item whose keys have landed (and
-        // whose accumulator pair is free), or the weighted sum of the oldest item whose P^T is written.
-        // The descriptors of stage 0 once; per instruction only constants are added (the address sits in the low
-        // bits in units of 16 bytes, and shared memory is too small to carry out of them).
-        const uint64_t k_desc0 = desc_k_major(k_of(0)), q_desc0 = desc_k_major(q_of(0)), p_desc0 = desc_k_major(p_of(0));
-        const uint64_t v_desc0 = desc_mn_major(v_of(0), BOX);
-        constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
-        int next_s = 0, next_o = 0;       // next item that needs its scores / its weighted sum
-        uint32_t idle = 0;
-        while (next_o < n_items && !*abort_flag) {
-            bool progressed = false;
-            if (next_s < n_items && next_s <= next_o + 1) {
-                const int n = next_s, s = n % STAGES, t = n & 1;
-                if (mbar_try_wait(kq_full + 8 * s, (uint32_t)((n / STAGES) & 1)) &&
-                    (n < 2 || mbar_try_wait(tmem_free + 8 * t, (uint32_t)(((n >> 1) - 1) & 1)))) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t kd = k_desc0 + s * STAGE_STEP, qd = q_desc0 + s * STAGE_STEP;
-#pragma unroll
-                    for (int k = 0; k < D / 16; k++) {
-                        constexpr int HALF_Q = NQ * 128;
-                        const uint64_t k_off = ((k / 4) * HALF_K + (k % 4) * 32) >> 4, q_off = ((k / 4) * HALF_Q + (k % 4) * 32) >> 4;
-                        umma_bf16(tmem_base + 32 * t, kd + k_off, qd + q_off, IDESC_S, k > 0 ? 1u : 0u);
-                    }
-                    umma_commit(s_done + 8 * t);
-                    next_s++;
-                    progressed = true;
+            const int my_n = lane / 10, my_j = lane % 10;     // three items of ten boxes each
+            const bool mine = my_n < ahead;
+            const bool early = mine && my_j >= 2 && items[my_n].split != items[my_n].pos / CHUNK;
+            if (early) load_box(items[my_n], my_n, my_j);
+            pdl_wait();
+            if (mine && !early) load_box(items[my_n], my_n, my_j);
+            for (int n = ahead; n < n_items; n++) {
+                const Item& it = items[n];
+                const int s = n % STAGES;
+                int freed = lane == 0 ? (int)mbar_wait(stage_free + 8 * s, (uint32_t)(((n / STAGES) - 1) & 1), abort_flag, p.status, 120) : 1;
+                freed = __shfl_sync(0xffffffffu, freed, 0);
+                if (!freed) break;
+                if (lane == 0) {
+                    mbar_expect_tx(kq_full + 8 * s, Q_BYTES + it.blocks_here * BOX * 2);
+                    mbar_expect_tx(v_full + 8 * s, it.blocks_here * BOX * 2);
                 }
+                __syncwarp();
+                if (lane < 10) load_box(it, s, lane);
             }
-            if (next_o < next_s) {
-                const int n = next_o, s = n % STAGES, t = n & 1;
-                if (mbar_try_wait(p_ready + 8 * t, (uint32_t)((n >> 1) & 1)) &&
-                    mbar_try_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1))) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t vd = v_desc0 + s * STAGE_STEP, pd = p_desc0 + s * STAGE_STEP;
-                    const int blocks_here = items[n].blocks_here;
-#pragma unroll
-                    for (int kb = 0; kb < 2; kb++) {
-                        if (kb < blocks_here) {
-#pragma unroll
-                            for (int k = 0; k < BLOCK_KEYS / 16; k++)
-                                umma_bf16(tmem_base + 32 * t + 16, vd + ((kb * 2 * BOX + k * (16 * 128)) >> 4),
-                                          pd + ((kb * (NQ * 128) + k * 32) >> 4), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
+        } else if (warp == 1 && lane == 0) {
+            // ---- MMA issuer: takes whatever is ready: the scores of the next item whose keys have landed (and
+            // whose accumulator pair is free), or the weighted sum of the oldest item whose P^T is written.
+            // The descriptors of stage 0 once; per instruction only constants are added (the address sits in the low
+            // bits in units of 16 bytes, and shared memory is too small to carry out of them).
+            const uint64_t k_desc0 = desc_k_major(k_of(0)), q_desc0 = desc_k_major(q_of(0)), p_desc0 = desc_k_major(p_of(0));
+            const uint64_t v_desc0 = desc_mn_major(v_of(0), BOX);
+            constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
+            int next_s = 0, next_o = 0;       // next item that needs its scores / its weighted sum
+            uint32_t idle = 0;
+            while (next_o < n_items && !*abort_flag) {
+                bool progressed = false;
+                if (next_s < n_items && next_s <= next_o + 1) {
+                    const int n = next_s, s = n % STAGES, t = n & 1;
+                    if (mbar_try_wait(kq_full + 8 * s, (uint32_t)((n / STAGES) & 1)) &&
+                        (n < 2 || mbar_try_wait(tmem_free + 8 * t, (uint32_t)(((n >> 1) - 1) & 1)))) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t kd = k_desc0 + s * STAGE_STEP, qd = q_desc0 + s * STAGE_STEP;
+    #pragma unroll
+                        for (int k = 0; k < D / 16; k++) {
+                            constexpr int HALF_Q = NQ * 128;
+                            const uint64_t k_off = ((k / 4) * HALF_K + (k % 4) * 32) >> 4, q_off = ((k / 4) * HALF_Q + (k % 4) * 32) >> 4;
+                            umma_bf16(tmem_base + 32 * t, kd + k_off, qd + q_off, IDESC_S, k > 0 ? 1u : 0u);
                         }
+                        umma_commit(s_done + 8 * t);
+                        next_s++;
+                        progressed = true;
                     }
-                    umma_commit(o_done + 8 * t);
-                    umma_commit(stage_free + 8 * s);
-                    next_o++;
-                    progressed = true;
+                }
+                if (next_o < next_s) {
+                    const int n = next_o, s = n % STAGES, t = n & 1;
+                    if (mbar_try_wait(p_ready + 8 * t, (uint32_t)((n >> 1) & 1)) &&
+                        mbar_try_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1))) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t vd = v_desc0 + s * STAGE_STEP, pd = p_desc0 + s * STAGE_STEP;
+                        const int blocks_here = items[n].blocks_here;
+    #pragma unroll
+                        for (int kb = 0; kb < 2; kb++) {
+                            if (kb < blocks_here) {
+    #pragma unroll
+                                for (int k = 0; k < BLOCK_KEYS / 16; k++)
+                                    umma_bf16(tmem_base + 32 * t + 16, vd + ((kb * 2 * BOX + k * (16 * 128)) >> 4),
+                                              pd + ((kb * (NQ * 128) + k * 32) >> 4), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
+                            }
+                        }
+                        umma_commit(o_done + 8 * t);
+                        umma_commit(stage_free + 8 * s);
+                        next_o++;
+                        progressed = true;
+                    }
+                }
+                if (progressed) idle = 0;
+                else if (++idle > WAIT_LIMIT) {   // nothing became ready for a long time: give up, flag it
+                    *abort_flag = 1;
+                    atomicExch(p.status, 121);
                 }
             }
-            if (progressed) idle = 0;
-            else if (++idle > WAIT_LIMIT) {   // nothing became ready for a long time: give up, flag it
-                *abort_flag = 1;
-                atomicExch(p.status, 121);
+            // the last commits have arrived before the barriers are set up again for another round
+            for (int n = max(0, n_items - STAGES); n < n_items && !*abort_flag; n++)
+                mbar_wait(stage_free + 8 * (n % STAGES), (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 122);
+        } else if (warp >= 2) {
+            // ---- softmax (thread = key), then partial output (thread = d).  Two groups of four warps take turns:
+            // group 0 the even items of this CTA with accumulator pair 0, group 1 the odd ones with pair 1.
+            const int grp = (warp - 2) >> 2, quarter = warp & 3, t = quarter * 32 + lane;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + 32 * grp;
+            auto group_sync = [&]() {
+                if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                else asm volatile("bar.sync 2, 128;" ::: "memory");
+            };
+            bool ok = true;
+            // The rows of P^T beyond the group are zero for good: their columns of O^T are never read, but must be
+            // finite.  Nothing else writes there, so they are cleared once, before the first P^T of this CTA.
+            if (round == 0) {
+                for (int i = threadIdx.x - 64; i < STAGES * P_BYTES / 16; i += 256)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(p_of(i / (P_BYTES / 16)) + (i % (P_BYTES / 16)) * 16), "r"(0) : "memory");
+                asm volatile("bar.sync 4, 256;" ::: "memory");
             }
-        }
-    } else if (warp >= 2) {
-        // ---- softmax (thread = key), then partial output (thread = d).  Two groups of four warps take turns:
-        // group 0 the even items of this CTA with accumulator pair 0, group 1 the odd ones with pair 1.
-        const int grp = (warp - 2) >> 2, quarter = warp & 3, t = quarter * 32 + lane;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + 32 * grp;
-        auto group_sync = [&]() {
-            if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-            else asm volatile("bar.sync 2, 128;" ::: "memory");
-        };
-        bool ok = true;
-        // The rows of P^T beyond the group are zero for good: their columns of O^T are never read, but must be
-        // finite.  Nothing else writes there, so they are cleared once, before the first P^T of this CTA.
-        for (int i = threadIdx.x - 64; i < STAGES * P_BYTES / 16; i += 256)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(p_of(i / (P_BYTES / 16)) + (i % (P_BYTES / 16)) * 16), "r"(0) : "memory");
-        asm volatile("bar.sync 4, 256;" ::: "memory");
-        pdl_wait();   // the partials, the counters and the output may still be in use by the kernels before
-        for (int n = grp; ok && n < n_items; n += 2) {
-            const Item& it = items[n];
-            const int s = n % STAGES, use = n >> 1;   // `use`: how often this group's accumulators were used before
-            const int key = it.chunk_begin + t;
-            const bool visible = key >= it.lo && key <= it.pos;
-            const int head0 = it.kvh * g;
-            float sc[NQ];
-            if (!(ok = mbar_wait(s_done + 8 * grp, (uint32_t)(use & 1), abort_flag, p.status, 124))) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            tmem_load16(lane_base, sc);
-#pragma unroll
-            for (int h = 0; h < G; h++) sc[h] = (visible && h < g) ? sc[h] * p.scale_log2 : -INFINITY;
-            float mx[G];
-#pragma unroll
-            for (int h = 0; h < G; h++) {
-                mx[h] = sc[h];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
-            }
-            group_sync();   // red_max and red_sum of this group's item before are read
-            if (lane < G) {
-                float mine = mx[0];
-#pragma unroll
-                for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
-                red_max[grp][quarter][lane] = mine;
-            }
-            group_sync();
-            float psum[G];
-            const int kb = t / BLOCK_KEYS, kin = t % BLOCK_KEYS;
-            const uint32_t p_dst = p_of(s);
-#pragma unroll
-            for (int h = 0; h < G; h++) {
-                const float M = fmaxf(fmaxf(red_max[grp][0][h], red_max[grp][1][h]), fmaxf(red_max[grp][2][h], red_max[grp][3][h]));
-                const float pj = (M == -INFINITY || sc[h] == -INFINITY) ? 0.f : exp2f(sc[h] - M);
-                const __nv_bfloat16 pb = __float2bfloat16_rn(pj);
-                psum[h] = __bfloat162float(pb);   // the sum uses what the tensor core multiplies with
-                mx[h] = M;
-                // P^T[h][key]: row h of the block's 16 x 128 B tile, 16-byte chunk (kin / 8) ^ (h & 7)
-                const uint32_t dst = p_dst + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
-                asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&pb)) : "memory");
-            }
-            // rows of V at and past the sequence's length have never been written by this sequence:
-            // their weight is 0, but 0 x (whatever bits lie there) must stay 0
-            if (key >= it.kv_len && kb < it.blocks_here) {
-                for (int x = 0; x < 2; x++) {
-                    const uint32_t rowp = v_of(s) + (kb * 2 + x) * BOX + kin * 128;
-                    if (x == 0 && !mbar_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 125)) break;
-#pragma unroll
-                    for (int c = 0; c < 8; c++)
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowp + c * 16), "r"(0) : "memory");
+            pdl_wait();   // the partials, the counters and the output may still be in use by the kernels before
+            for (int n = grp; ok && n < n_items; n += 2) {
+                const Item& it = items[n];
+                const int s = n % STAGES, use = n >> 1;   // `use`: how often this group's accumulators were used before
+                const int key = it.chunk_begin + t;
+                const bool visible = key >= it.lo && key <= it.pos;
+                const int head0 = it.kvh * g;
+                float sc[NQ];
+                if (!(ok = mbar_wait(s_done + 8 * grp, (uint32_t)(use & 1), abort_flag, p.status, 124))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tmem_load16(lane_base, sc);
+    #pragma unroll
+                for (int h = 0; h < G; h++) sc[h] = (visible && h < g) ? sc[h] * p.scale_log2 : -INFINITY;
+                float mx[G];
+    #pragma unroll
+                for (int h = 0; h < G; h++) {
+                    mx[h] = sc[h];
+    #pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
+                }
+                group_sync();   // red_max and red_sum of this group's item before are read
+                if (lane < G) {
+                    float mine = mx[0];
+    #pragma unroll
+                    for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
+                    red_max[grp][quarter][lane] = mine;
+                }
+                group_sync();
+                float psum[G];
+                const int kb = t / BLOCK_KEYS, kin = t % BLOCK_KEYS;
+                const uint32_t p_dst = p_of(s);
+    #pragma unroll
+                for (int h = 0; h < G; h++) {
+                    const float M = fmaxf(fmaxf(red_max[grp][0][h], red_max[grp][1][h]), fmaxf(red_max[grp][2][h], red_max[grp][3][h]));
+                    const float pj = (M == -INFINITY || sc[h] == -INFINITY) ? 0.f : exp2f(sc[h] - M);
+                    const __nv_bfloat16 pb = __float2bfloat16_rn(pj);
+                    psum[h] = __bfloat162float(pb);   // the sum uses what the tensor core multiplies with
+                    mx[h] = M;
+                    // P^T[h][key]: row h of the block's 16 x 128 B tile, 16-byte chunk (kin / 8) ^ (h & 7)
+                    const uint32_t dst = p_dst + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&pb)) : "memory");
+                }
+                // rows of V at and past the sequence's length have never been written by this sequence:
+                // their weight is 0, but 0 x (whatever bits lie there) must stay 0
+                if (key >= it.kv_len && kb < it.blocks_here) {
+                    for (int x = 0; x < 2; x++) {
+                        const uint32_t rowp = v_of(s) + (kb * 2 + x) * BOX + kin * 128;
+                        if (x == 0 && !mbar_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 125)) break;
+    #pragma unroll
+                        for (int c = 0; c < 8; c++)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowp + c * 16), "r"(0) : "memory");
+                    }
+                }
+    #pragma unroll
+                for (int h = 0; h < G; h++)
+    #pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], o);
+                if (lane < G) {
+                    float mine = psum[0];
+    #pragma unroll
+                    for (int h = 1; h < G; h++) mine = lane == h ? psum[h] : mine;
+                    red_sum[grp][quarter][lane] = mine;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(p_ready + 8 * grp);
+                // partial output: thread = d
+                if (!(ok = mbar_wait(o_done + 8 * grp, (uint32_t)(use & 1), abort_flag, p.status, 126))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float o[NQ];
+                tmem_load16(lane_base + 16, o);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(tmem_free + 8 * grp);   // this pair of accumulators may be filled again
+                group_sync();                       // red_sum of all four warps is written
+    #pragma unroll
+                for (int h = 0; h < G; h++) {
+                    if (h < g) {
+                        const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + it.split;
+                        p.part_acc[row * D + t] = o[h];
+                    }
+                }
+                if (lane < g) {   // every warp keeps its own copy of (maximum, sum): a warp folds what warps of its quarter wrote
+                    float mine = mx[0];
+    #pragma unroll
+                    for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
+                    const size_t row = ((size_t)it.b * p.nh + head0 + lane) * p.max_splits + it.split;
+                    *reinterpret_cast<float2*>(p.part_ml + (row * 4 + quarter) * 2) =
+                        make_float2(mine, red_sum[grp][0][lane] + red_sum[grp][1][lane] + red_sum[grp][2][lane] + red_sum[grp][3][lane]);
                 }
             }
-#pragma unroll
-            for (int h = 0; h < G; h++)
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], o);
-            if (lane < G) {
-                float mine = psum[0];
-#pragma unroll
-                for (int h = 1; h < G; h++) mine = lane == h ? psum[h] : mine;
-                red_sum[grp][quarter][lane] = mine;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_ready + 8 * grp);
-            // partial output: thread = d
-            if (!(ok = mbar_wait(o_done + 8 * grp, (uint32_t)(use & 1), abort_flag, p.status, 126))) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float o[NQ];
-            tmem_load16(lane_base + 16, o);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(tmem_free + 8 * grp);   // this pair of accumulators may be filled again
-            group_sync();                       // red_sum of all four warps is written
-#pragma unroll
-            for (int h = 0; h < G; h++) {
-                if (h < g) {
-                    const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + it.split;
-                    p.part_acc[row * D + t] = o[h];
-                }
-            }
-            if (lane < g) {   // every warp keeps its own copy of (maximum, sum): a warp folds what warps of its quarter wrote
-                float mine = mx[0];
-#pragma unroll
-                for (int h = 1; h < G; h++) mine = lane == h ? mx[h] : mine;
-                const size_t row = ((size_t)it.b * p.nh + head0 + lane) * p.max_splits + it.split;
-                *reinterpret_cast<float2*>(p.part_ml + (row * 4 + quarter) * 2) =
-                    make_float2(mine, red_sum[grp][0][lane] + red_sum[grp][1][lane] + red_sum[grp][2][lane] + red_sum[grp][3][lane]);
-            }
-        }
-        // All partials of this warp are written.  One counter per (sequence, kv head, quarter of d) counts the
-        // chunks whose partials are in memory; a warp raises the counters of all its items at once (lane l the
-        // l-th item of the group).  A row is folded, in chunk order, by the warps that computed the row's LAST
-        // chunk, each for its quarter of d (so the folding is spread evenly over the CTAs): the warp waits, with
-        // a limit, until its counter shows that all chunks are in.
-        __threadfence();
-        __syncwarp();
-        if (ok && grp + 2 * lane < n_items) {
-            const Item& it = items[grp + 2 * lane];
-            atomicAdd(p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter, 1);
-        }
-        for (int i = grp; ok && i < n_items; i += 2) {
-            const Item& it = items[i];
-            if (it.split != it.pos / CHUNK) continue;        // not the row's last chunk
-            const int s_begin = it.lo / CHUNK, n_chunks = it.pos / CHUNK + 1 - s_begin;
-            int* counter = p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter;
-            int seen = 0;
-            if (lane == 0) {
-                uint32_t spins = 0;
-                while ((seen = *reinterpret_cast<volatile int*>(counter)) < n_chunks && ++spins < (1u << 22)) __nanosleep(20);
-                if (seen >= n_chunks) *counter = 0;          // ready for the next launch
-                else atomicExch(p.status, 128);              // a chunk never arrived: flag it, leave the row
-            }
-            seen = __shfl_sync(0xffffffffu, seen, 0);
-            if (seen < n_chunks) continue;
+            // All partials of this warp are written.  One counter per (sequence, kv head, quarter of d) counts the
+            // chunks whose partials are in memory; a warp raises the counters of all its items at once (lane l the
+            // l-th item of the group).  A row is folded, in chunk order, by the warps that computed the row's LAST
+            // chunk, each for its quarter of d (so the folding is spread evenly over the CTAs): the warp waits, with
+            // a limit, until its counter shows that all chunks are in.
             __threadfence();
-            // a lane takes four neighbouring d of one head: 8 lanes per head, 4 heads per round
-            const int head0 = it.kvh * g;
-            for (int unit = lane; unit < g * 8; unit += 32) {
-                const int h = unit >> 3, dd = quarter * 32 + (unit & 7) * 4;
-                const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + s_begin;
-                float M = -INFINITY, L = 0.f;
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int cb = 0; cb < n_chunks; cb += FOLD_BATCH) {
-                    float2 ml[FOLD_BATCH];
-                    float4 v[FOLD_BATCH];
-#pragma unroll
-                    for (int j = 0; j < FOLD_BATCH; j++) {   // all loads of the batch are in flight together
-                        const bool in = cb + j < n_chunks;
-                        ml[j] = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((row + cb + j) * 4 + quarter) * 2))
-                                   : make_float2(-INFINITY, 0.f);
-                        v[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + (row + cb + j) * D + dd))
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                    float Mb = M;
-#pragma unroll
-                    for (int j = 0; j < FOLD_BATCH; j++) Mb = fmaxf(Mb, ml[j].x);
-                    const float keep = M == -INFINITY ? 0.f : exp2f(M - Mb);
-                    L *= keep; a.x *= keep; a.y *= keep; a.z *= keep; a.w *= keep;
-#pragma unroll
-                    for (int j = 0; j < FOLD_BATCH; j++) {
-                        const float wc = ml[j].x == -INFINITY ? 0.f : exp2f(ml[j].x - Mb);
-                        L = fmaf(ml[j].y, wc, L);
-                        a.x = fmaf(v[j].x, wc, a.x); a.y = fmaf(v[j].y, wc, a.y);
-                        a.z = fmaf(v[j].z, wc, a.z); a.w = fmaf(v[j].w, wc, a.w);
-                    }
-                    M = Mb;
+            __syncwarp();
+            if (ok && grp + 2 * lane < n_items) {
+                const Item& it = items[grp + 2 * lane];
+                atomicAdd(p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter, 1);
+            }
+            for (int i = grp; ok && i < n_items; i += 2) {
+                const Item& it = items[i];
+                if (it.split != it.pos / CHUNK) continue;        // not the row's last chunk
+                const int s_begin = it.lo / CHUNK, n_chunks = it.pos / CHUNK + 1 - s_begin;
+                int* counter = p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter;
+                int seen = 0;
+                if (lane == 0) {
+                    uint32_t spins = 0;
+                    while ((seen = *reinterpret_cast<volatile int*>(counter)) < n_chunks && ++spins < (1u << 22)) __nanosleep(20);
+                    if (seen >= n_chunks) *counter = 0;          // ready for the next launch
+                    else atomicExch(p.status, 128);              // a chunk never arrived: flag it, leave the row
                 }
-                const float inv = L > 0.f ? 1.0f / L : 0.f;
-                __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(a.x * inv, a.y * inv), __floats2bfloat162_rn(a.z * inv, a.w * inv)};
-                *reinterpret_cast<uint2*>(p.out + ((size_t)it.b * p.nh + head0 + h) * D + dd) = *reinterpret_cast<uint2*>(o2);
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                if (seen < n_chunks) continue;
+                __threadfence();
+                // a lane takes four neighbouring d of one head: 8 lanes per head, 4 heads per round
+                const int head0 = it.kvh * g;
+                for (int unit = lane; unit < g * 8; unit += 32) {
+                    const int h = unit >> 3, dd = quarter * 32 + (unit & 7) * 4;
+                    const size_t row = ((size_t)it.b * p.nh + head0 + h) * p.max_splits + s_begin;
+                    float M = -INFINITY, L = 0.f;
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int cb = 0; cb < n_chunks; cb += FOLD_BATCH) {
+                        float2 ml[FOLD_BATCH];
+                        float4 v[FOLD_BATCH];
+    #pragma unroll
+                        for (int j = 0; j < FOLD_BATCH; j++) {   // all loads of the batch are in flight together
+                            const bool in = cb + j < n_chunks;
+                            ml[j] = in ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((row + cb + j) * 4 + quarter) * 2))
+                                       : make_float2(-INFINITY, 0.f);
+                            v[j] = in ? __ldcg(reinterpret_cast<const float4*>(p.part_acc + (row + cb + j) * D + dd))
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        float Mb = M;
+    #pragma unroll
+                        for (int j = 0; j < FOLD_BATCH; j++) Mb = fmaxf(Mb, ml[j].x);
+                        const float keep = M == -INFINITY ? 0.f : exp2f(M - Mb);
+                        L *= keep; a.x *= keep; a.y *= keep; a.z *= keep; a.w *= keep;
+    #pragma unroll
+                        for (int j = 0; j < FOLD_BATCH; j++) {
+                            const float wc = ml[j].x == -INFINITY ? 0.f : exp2f(ml[j].x - Mb);
+                            L = fmaf(ml[j].y, wc, L);
+                            a.x = fmaf(v[j].x, wc, a.x); a.y = fmaf(v[j].y, wc, a.y);
+                            a.z = fmaf(v[j].z, wc, a.z); a.w = fmaf(v[j].w, wc, a.w);
+                        }
+                        M = Mb;
+                    }
+                    const float inv = L > 0.f ? 1.0f / L : 0.f;
+                    __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(a.x * inv, a.y * inv), __floats2bfloat162_rn(a.z * inv, a.w * inv)};
+                    *reinterpret_cast<uint2*>(p.out + ((size_t)it.b * p.nh + head0 + h) * D + dd) = *reinterpret_cast<uint2*>(o2);
+                }
             }
         }
+
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();   // every role is through with this round
+        if (n_items < MAX_ITEMS) break;
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -546,7 +566,7 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
     HYMT2_REQUIRE(d == D, "attention_decode_tc: head_dim %d is not taken (128 is)", d);
     HYMT2_REQUIRE(block_tokens == BLOCK_KEYS, "attention_decode_tc: cache blocks must hold %d tokens", BLOCK_KEYS);
     HYMT2_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= NQ, "attention_decode_tc: at most %d heads per kv head", NQ);
-    HYMT2_REQUIRE(max_splits > 0 && max_splits <= 64, "attention_decode_tc: at most 64 chunks of 128 keys (8,192 positions) are taken, got %d", max_splits);
+    HYMT2_REQUIRE(max_splits > 0 && max_splits <= MAX_CHUNKS, "attention_decode_tc: at most %d chunks of 128 keys are taken, got %d", MAX_CHUNKS, max_splits);
     HYMT2_REQUIRE(part_acc && part_ml && counters && status, "attention_decode_tc: scratch is needed");
     HYMT2_REQUIRE(rows <= MAX_ROWS, "attention_decode_tc: at most %d sequences in one launch, got %d", MAX_ROWS, rows);
     CUtensorMap mq, mk, mv;
@@ -568,7 +588,8 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
         if (e != cudaSuccess) { hymt2_set_error("attention_decode_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
         configured[which] = true;
     }
-    // one CTA per SM walks the (chunk, kv head, sequence) items; a CTA takes at most MAX_ITEMS of them
+    // one CTA per SM walks the (sequence, kv head, chunk) items, MAX_ITEMS at a time.  All CTAs must run at the
+    // same time (a row is folded by a CTA that waits for the others' chunks): never more CTAs than SMs.
     const long total = (long)rows * nkv * max_splits;
     int sms = 148;
     {
@@ -576,8 +597,7 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    long ctas = total < sms ? total : sms;
-    if ((total + ctas - 1) / ctas > MAX_ITEMS) ctas = (total + MAX_ITEMS - 1) / MAX_ITEMS;
+    const long ctas = total < sms ? total : sms;
     cudaError_t e = launch_pdl(kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), smem, stream, mq, mk, mv, p);
     if (e != cudaSuccess) { hymt2_set_error("attention_decode_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("attention_decode_tc");

@@ -18,6 +18,7 @@ def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: in
 DECODE_CHUNK_KEYS = 256     # keys per partial of the streaming decode kernel, a constant of the kernel
 DECODE_TC_MAX_ROWS = 512       # sequences that one launch of the tcgen05 decode kernel takes
 DECODE_TC_CHUNK_KEYS = 128  # keys per partial of the tensor-core decode kernel
+DECODE_TC_MAX_CHUNKS = 2048  # chunks of one sequence that it takes
 
 
 def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale, window) -> bool:
@@ -27,7 +28,7 @@ def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale,
     bt = k_plane.shape[2]
     if out.dtype != torch.bfloat16 or d not in (64, 128) or bt & (bt - 1):
         return False
-    if (ctx.decode and d == 128 and bt == 64 and nh // nkv <= 16 and ctx.max_kv_len <= 64 * DECODE_TC_CHUNK_KEYS
+    if (ctx.decode and d == 128 and bt == 64 and nh // nkv <= 16 and ctx.max_kv_len <= DECODE_TC_MAX_CHUNKS * DECODE_TC_CHUNK_KEYS
             and ctx.num_tokens <= DECODE_TC_MAX_ROWS):
         splits = max(1, -(-ctx.max_kv_len // DECODE_TC_CHUNK_KEYS))
         na, nm, nc = ops.attention_decode_tc_scratch(ctx.num_tokens, nh, nkv, d, splits)

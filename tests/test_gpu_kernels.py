@@ -432,6 +432,44 @@ def test_attention_prefill_tcgen05(nh, nkv, d, window):
     assert torch.allclose(out.double(), ref2, **_tol(dtype))
 
 
+def test_attention_decode_tcgen05_more_chunks_than_a_cta_holds():
+    """Many long rows: more chunks of 128 keys than the CTAs hold at a time (they go through them in
+    rounds), rows beyond 8,192 positions, and one far key that carries all the weight of its row."""
+    ops = _ops()
+    torch.manual_seed(11)
+    dtype, d, nh, nkv = torch.bfloat16, 128, 8, 4
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows = 40
+    lens = [7700 + 13 * i for i in range(rows)]
+    lens[3], lens[17] = 8300, 9001
+    assert sum(-(-L // 128) for L in lens) * nkv > sms * 64
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    qs = [torch.randn(1, nh, d, device=DEV).to(dtype) for _ in lens]
+    # row 5, head 2 (kv head 1): key 37 is the query scaled up, so that it takes all the weight
+    keys[5][37, 1] = (qs[5][0, 2].float() * 4).to(dtype)
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=9)
+    q = torch.cat([x.reshape(1, nh * d) for x in qs])
+    slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    splits = -(-max(lens) // 128)
+    na, nm, nc = ops.attention_decode_tc_scratch(rows, nh, nkv, d, splits)
+    acc = torch.full((na,), float("nan"), device=DEV)
+    ml = torch.full((nm,), float("nan"), device=DEV)
+    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out = torch.full((rows, nh * d), 5.0, dtype=dtype, device=DEV)
+    for _ in range(2):
+        ops.attention_decode_tc(out, q, kp, vp, table, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, counters, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and int(counters.abs().sum()) == 0
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, 0, scale) for i in range(rows)])
+    assert torch.allclose(out.double(), ref, **_tol(dtype))
+    far = out[5].reshape(nh, d)[2].float()
+    assert torch.allclose(far, vals[5][37, 1].float(), atol=0.05)
+
+
 @pytest.mark.parametrize("nh, nkv, window", [(16, 4, 0), (4, 4, 0), (32, 2, 0), (6, 2, 300), (10, 2, 70)])
 def test_attention_decode_tcgen05(nh, nkv, window):
     """The tensor-core decode kernel (keys on the 128-row side, head_dim 128) against the float64
