@@ -86,6 +86,7 @@ class DecodeSession:
             else:
                 sampler.adopt(self.buf.sampler_tensors, self.buf.argmax_scratch)
         self.steps = 0
+        self._reserved = False   # whether the blocks of the coming step are already taken
 
     # -- what the step reads --------------------------------------------------------
     @property
@@ -97,13 +98,27 @@ class DecodeSession:
         return self.buf.kernels_per_step
 
     # -- host bookkeeping ---------------------------------------------------------
+    def _plan(self) -> list:
+        return [(s, 1) for s, alive in zip(self.slots, self.live) if alive]
+
     def _reserve(self) -> None:
-        plan = [(s, 1) for s, alive in zip(self.slots, self.live) if alive]
-        self.cache.begin_step(plan)
-        self._plan = plan
+        self.cache.begin_step(self._plan())
+        self._reserved = True
+
+    def _reserve_ahead(self) -> None:
+        """Blocks for the step after this one, taken while this one runs on the device.  A row that ends
+        meanwhile gives them back with its slot; a cache too full for it is asked again when the step comes."""
+        from ..cache.allocator import CacheFull
+        if self.max_total_len < max((l for l, a in zip(self.lengths, self.live) if a), default=0) + 1:
+            return
+        try:
+            self._reserve()
+        except CacheFull:
+            self._reserved = False
 
     def _commit(self) -> None:
-        self.cache.end_step(self._plan)
+        self.cache.end_step(self._plan())
+        self._reserved = False
         for i, alive in enumerate(self.live):
             if alive:
                 self.lengths[i] += 1
@@ -141,7 +156,8 @@ class DecodeSession:
         if self.max_total_len < max((l for l, a in zip(self.lengths, self.live) if a), default=0) + 1:
             raise RuntimeError("the session was opened for shorter sequences")
         with torch.cuda.device(self.engine.device):
-            self._reserve()
+            if not self._reserved:
+                self._reserve()
             if not self.use_graph:
                 self._launch()
             elif self.buf.graph is None or self.buf.graph_layout != self.cache.layout_version:
@@ -150,6 +166,7 @@ class DecodeSession:
                 self.buf.graph.replay()
                 ops.launches += self.buf.kernels_per_step
             self._commit()
+            self._reserve_ahead()
         self.steps += 1
         return self.buf.tokens
 
