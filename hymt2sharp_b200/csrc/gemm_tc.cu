@@ -13,9 +13,9 @@
 //            (BN = 16..128): a decode step streams every weight tile once at full tile height
 //            whatever the batch is.  With `splits` > 1 the K range is cut over gridDim.z.  The
 //            split CTAs of a tile form a thread-block cluster: each leaves its partial tile in
-//            its own shared memory, and after the cluster's barrier the first CTA adds the
-//            partials of its peers through distributed shared memory, in rank order (so the sum
-//            is the same every time), and runs the epilogue.  (A partial tile too large for the
+//            its own shared memory, and after the cluster's barrier every CTA adds the partials
+//            of all ranks for its share of the token columns through distributed shared memory,
+//            in rank order (so the sum is the same every time), and runs the epilogue for them.  (A partial tile too large for the
 //            stage ring goes through a global workspace instead, folded by the CTA that arrives
 //            last at the tile's counter, also in split order.)
 // Epilogues: store, accumulate into float32 C, SwiGLU (silu(gate) * up; W holds N gate rows,
@@ -356,8 +356,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         } else if (SWAPPED && p.cluster) {
-            // partial tile -> this CTA's shared memory (the stage ring is free now), [column][row];
-            // after the cluster's barrier the first CTA adds the partials of all its peers in rank order
+            // partial tile -> this CTA's shared memory (the stage ring is free now), [column][row].  After the
+            // cluster's barrier every CTA of the cluster takes a share of the token columns that exist, adds the
+            // partials of all ranks for them through distributed shared memory (in rank order: the sum is the
+            // same every time) and writes them out: the adding is spread over the cluster, and no one reads
+            // columns beyond the last token.
             for (int c = 0; c < ACC_COLS; c += CH) {
                 float g[CH];
                 if (ok && my_blocks > 0) tmem_load<CH>(lane_addr + c, g);
@@ -371,23 +374,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             __syncwarp();
             cluster_sync_all();
-            if (blockIdx.z == 0) {
-                for (int c = 0; c < OUT_COLS; c += CH) {
-                    float g[CH], u[CH];
+            {
+                constexpr int MAX_RANKS = 8;                       // a portable cluster
+                const int cols = min(BN, p.T - b_row0);            // token columns that exist in this tile
+                const int share = (cols + p.splits - 1) / p.splits;
+                const int c_begin = (int)blockIdx.z * share, c_end = min(cols, c_begin + share);
+                const int n = a_row0 + row;                        // output feature
+                for (int c = c_begin; c < c_end; c++) {
+                    float pg[MAX_RANKS], pu[MAX_RANKS];
 #pragma unroll
-                    for (int j = 0; j < CH; j++) { g[j] = 0.f; u[j] = 0.f; }
-                    for (int r = 0; r < p.splits; r++) {       // rank order: the sum is the same every time
-#pragma unroll
-                        for (int j = 0; j < CH; j++) {
-                            g[j] += ld_cluster_f32(tiles + ((c + j) * TILE_M + row) * 4, r);
-                            if (EPI == EPI_SWIGLU) u[j] += ld_cluster_f32(tiles + ((BN + c + j) * TILE_M + row) * 4, r);
-                        }
+                    for (int r = 0; r < MAX_RANKS; r++) {          // all loads first: they do not wait for each other
+                        const bool in = r < p.splits;
+                        pg[r] = in ? ld_cluster_f32(tiles + (c * TILE_M + row) * 4, r) : 0.f;
+                        pu[r] = (in && EPI == EPI_SWIGLU) ? ld_cluster_f32(tiles + ((BN + c) * TILE_M + row) * 4, r) : 0.f;
                     }
-                    emit(c, g, u);
+                    float g = 0.f, u = 0.f;
+#pragma unroll
+                    for (int r = 0; r < MAX_RANKS; r++) { g += pg[r]; u += pu[r]; }
+                    if (n < p.N) {
+                        TC* dst = C + (size_t)(b_row0 + c) * p.ldc + n;
+                        if (EPI == EPI_STORE) *dst = from_float<TC>(g);
+                        else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(to_float(*dst) + g);
+                        else *dst = from_float<TC>(silu_mul(g, u));
+                    }
                 }
             }
             __syncwarp();
-            cluster_sync_all();   // peers keep their shared memory until the first CTA has read it
+            cluster_sync_all();   // every CTA keeps its shared memory until its peers have read it
         } else if (SWAPPED) {
             // partial tile -> workspace [tile][split][acc][column][row]; the last arrival reduces
             const int tile = blockIdx.y * gridDim.x + blockIdx.x;
