@@ -172,9 +172,15 @@ def gemm_tc_supported(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
     return out.dtype == torch.bfloat16
 
 
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor) -> None:
+PREFETCH_MAX_BYTES = 48 << 20   # of a larger hint only the beginning is asked for: more would push too much else out of L2
+
+
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor,
+            prefetch: torch.Tensor | None = None) -> None:
     """out[T, N] = epilogue(a[T, K] @ w[N, K]^T) on the tcgen05 tensor cores (bfloat16 operands,
-    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows."""
+    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows.  `prefetch`: a
+    contiguous tensor that a later kernel will stream (the next product's weights); a decode-sized
+    product asks for it to be brought into L2 while it waits for its own input."""
     T, N = out.shape
     K = a.shape[1]
     rows_w = 2 * N if epilogue == EPILOGUE_SWIGLU else N
@@ -187,10 +193,16 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, 
     ws = cnt = None
     if floats.value:
         ws, cnt = _tc_workspace(out.device, floats.value, counters.value)
+    pf_bytes = 0
+    if prefetch is not None and prefetch.is_contiguous():
+        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES)
+    else:
+        prefetch = None
     _check(_lib().hymt2_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(T), c_int(N), c_int(K),
                                 c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)), c_int(epilogue),
                                 _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(cnt),
-                                c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream()), "gemm_tc")
+                                c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _ptr(prefetch),
+                                c_long(pf_bytes), _stream()), "gemm_tc")
 
 
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,

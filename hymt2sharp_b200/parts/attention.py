@@ -88,7 +88,7 @@ class GQAAttention:
                     self.q_gain, self.k_gain, self.eps, nh, nkv, d)
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=qkv.device)
         self.attend(out, q, k_plane, v_plane, block_table, ctx)
-        self.out(out, out=residual)
+        self.out(out, out=residual, then=ctx.weights_ahead if ctx.decode else None)
 
     def attend(self, out, q, k_plane, v_plane, block_table, ctx) -> None:
         from ..kernels import fast

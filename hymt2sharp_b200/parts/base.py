@@ -95,6 +95,9 @@ class StepContext:
     host_slots: list = field(default_factory=list)       # the same facts on the host, for parts
     host_new_tokens: list = field(default_factory=list)  # that plan their work there
     host_starts: list = field(default_factory=list)
+    # a hint from whoever arranges the parts: the weights that the next large kernel AFTER the running part will
+    # stream (or None); a part whose last kernel leaves the memory idle may ask for them ahead of time
+    weights_ahead: torch.Tensor | None = None
 
     @property
     def decode(self) -> bool:

@@ -28,7 +28,10 @@ class PreNormBlock:
 
     def forward(self, residual, ctx, slot) -> None:
         x = self.norm1.forward(residual, ctx, ctx.dtype)
+        # what the feed-forward streams first, for a mixer whose last kernel can ask for it ahead of time
+        ctx.weights_ahead = getattr(self.feed_forward, "first_weights", lambda: None)()
         self.mixer.forward(x, residual, ctx, slot)
+        ctx.weights_ahead = None
         x = self.norm2.forward(residual, ctx, ctx.dtype)
         self.feed_forward.forward(x, residual, ctx)
 

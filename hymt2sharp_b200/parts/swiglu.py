@@ -30,6 +30,10 @@ class SwiGLU:
         self.gate_up = Linear(compute_form(stacked, device, dtype), ops.EPILOGUE_SWIGLU)
         self.down = Linear(compute_form(weights[n["d"]], device, dtype), ops.EPILOGUE_ACCUMULATE)
 
+    def first_weights(self):
+        """The weights that this part's first kernel streams."""
+        return self.gate_up.weight if self.gate_up is not None else None
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         act = self.gate_up(x)
         self.down(act, out=residual)
