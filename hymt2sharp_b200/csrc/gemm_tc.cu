@@ -31,7 +31,13 @@
 
 namespace {
 
-constexpr int BLOCK_K = 64, UMMA_K = 16, TILE_M = 128, NUM_THREADS = 192, MAX_STAGES = 8;
+constexpr int BLOCK_K = 64, UMMA_K = 16, TILE_M = 128, MAX_STAGES = 8;
+constexpr int NUM_THREADS = 192;          // persistent kernel: warp 0 TMA, warp 1 MMAs, warps 2-5 epilogue
+// one-tile kernel: with few accumulator columns a second warp issues MMAs too (warp 6), see ISSUERS in the kernel
+__host__ __device__ constexpr int tile_issuers(int bn, bool swapped, int epi) {
+    return (swapped && bn * ((swapped && epi == 2) ? 2 : 1) <= 32) ? 2 : 1;   // measured: no gain with 64 columns and more
+}
+__host__ __device__ constexpr int tile_threads(int bn, bool swapped, int epi) { return tile_issuers(bn, swapped, epi) > 1 ? 224 : 192; }
 constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 constexpr int PERSISTENT_BN = 256;   // tile width of the persistent kernel for many tokens
@@ -146,14 +152,22 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 template <int BN, bool SWAPPED, int EPI, typename TC>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
     constexpr int NUM_ACC = (SWAPPED && EPI == EPI_SWIGLU) ? 2 : 1;   // accumulators = A tiles per stage
     constexpr bool SPLIT_B = !SWAPPED && EPI == EPI_SWIGLU;           // B tile = gate rows, then up rows
     constexpr int B_TILE_BYTES = BN * BLOCK_K * 2;
     constexpr int STAGE_BYTES = NUM_ACC * A_TILE_BYTES + B_TILE_BYTES;
     constexpr int ACC_COLS = NUM_ACC * BN;
-    constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+    // With few columns the thread that issues the MMAs is the bottleneck, not the tensor core (an MMA costs that
+    // thread ~56 cycles, a look at an mbarrier ~190, whatever N is).  So two threads of different warps issue:
+    // issuer j takes the k blocks that land in the stages j, j + 2, ... of the ring (so each stage's barrier has one
+    // reader, who sees every phase of it) and adds them up in an accumulator of its own; the epilogue adds the
+    // accumulators, always in the same order.
+    constexpr int ISSUERS = tile_issuers(BN, SWAPPED, EPI);
+    static_assert(ISSUERS == 1 || ACC_COLS <= 32, "two issuers are for narrow accumulators");
+    constexpr int PHYS_COLS = ACC_COLS * ISSUERS;   // accumulator a of issuer j: columns (a * ISSUERS + j) * BN ..
+    constexpr int TMEM_COLS = PHYS_COLS <= 32 ? 32 : PHYS_COLS <= 64 ? 64 : PHYS_COLS <= 128 ? 128 : PHYS_COLS <= 256 ? 256 : 512;
     constexpr int CH = BN >= 32 ? 32 : 16;                            // accumulator columns per epilogue chunk
     constexpr int OUT_COLS = SPLIT_B ? BN / 2 : BN;                   // output columns that the tile covers
     // instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128
@@ -182,7 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(done_bar, 1);
+        mbar_init(done_bar, ISSUERS);
         abort_s = 0;
         last_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -256,32 +270,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int i = max(0, issued - stages); i < issued; i++)
                 for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full0 + 8 * (i % stages), (i / stages) & 1); t++) {}
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ---------------------------------------------------------------------
-        // One thread issues every MMA, and with few columns an MMA is over sooner than a chain of address
-        // arithmetic in that thread: so the loop carries the stage's descriptor along (the address sits in the
-        // low bits, in units of 16 bytes, and the ring is far too small to carry out of them) and adds constants.
+    } else if ((warp == 1 || (warp >= 6 && warp - 5 < ISSUERS)) && lane == 0) {
+        // ---- MMA issuers: warp 1 is issuer 0, warp 6 is issuer 1 ------------------------------------
+        // The loop carries the stage's descriptor along (the address sits in the low bits, in units of 16 bytes,
+        // and the ring is far too small to carry out of them) and adds constants: a chain of address arithmetic
+        // per MMA would cost the issuing thread more than the MMA.
         constexpr uint64_t K_STEP = (UMMA_K * 2) >> 4, A2_STEP = A_TILE_BYTES >> 4, B_STEP = (NUM_ACC * A_TILE_BYTES) >> 4;
+        const int me = warp == 1 ? 0 : warp - 5;
+        const uint32_t acc0 = tmem_base + me * BN, acc1 = tmem_base + (ISSUERS + me) * BN;
         const uint64_t desc0 = smem_desc_sw128(tiles);
-        uint64_t adesc = desc0;
-        uint32_t s = 0, phase = 0;
+        uint32_t s = 0, phase = 0, any = 0;
         for (int i = 0; i < my_blocks; i++) {
-            if (!mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t bdesc = adesc + B_STEP;
-            umma_bf16(tmem_base, adesc, bdesc, IDESC, i > 0 ? 1u : 0u);
-            if (NUM_ACC == 2) umma_bf16(tmem_base + BN, adesc + A2_STEP, bdesc, IDESC, i > 0 ? 1u : 0u);
+            if ((int)(s % ISSUERS) == me) {
+                if (!mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = desc0 + (uint64_t)s * (uint64_t)(STAGE_BYTES >> 4), bdesc = adesc + B_STEP;
+                umma_bf16(acc0, adesc, bdesc, IDESC, any);
+                if (NUM_ACC == 2) umma_bf16(acc1, adesc + A2_STEP, bdesc, IDESC, any);
+                any = 1;
 #pragma unroll
-            for (int k = 1; k < BLOCK_K / UMMA_K; k++) {
-                umma_bf16_add(tmem_base, adesc + k * K_STEP, bdesc + k * K_STEP, IDESC);
-                if (NUM_ACC == 2) umma_bf16_add(tmem_base + BN, adesc + A2_STEP + k * K_STEP, bdesc + k * K_STEP, IDESC);
+                for (int k = 1; k < BLOCK_K / UMMA_K; k++) {
+                    umma_bf16_add(acc0, adesc + k * K_STEP, bdesc + k * K_STEP, IDESC);
+                    if (NUM_ACC == 2) umma_bf16_add(acc1, adesc + A2_STEP + k * K_STEP, bdesc + k * K_STEP, IDESC);
+                }
+                umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs have read it
             }
-            umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs have read it
-            if (++s == (uint32_t)stages) { s = 0; phase ^= 1; adesc = desc0; }
-            else adesc += (uint64_t)(STAGE_BYTES >> 4);
+            if (++s == (uint32_t)stages) { s = 0; phase ^= 1; }
         }
-        umma_commit(done_bar);             // the accumulator is complete once all MMAs are done
-    } else if (warp >= 2) {
+        umma_commit(done_bar);             // this issuer's accumulator is complete once its MMAs are done
+    } else if (warp >= 2 && warp < 6) {
         // ---- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 --------------------------
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                   // row of the tile that this thread owns
@@ -290,6 +307,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         TC* C = (TC*)p.C;
+        // CH columns of the accumulators from column c on (c counts gate columns, then up columns): the sum over the
+        // issuers that had a k block, in issuer order (issuer 1 has one as soon as there are two blocks and two stages)
+        const int used = min(ISSUERS, min(my_blocks, stages));
+        auto acc_load = [&](int c, float* g) {
+            const uint32_t at = lane_addr + (uint32_t)((c / BN) * ISSUERS * BN + c % BN);
+            tmem_load<CH>(at, g);
+#pragma unroll
+            for (int j = 1; j < ISSUERS; j++) {
+                if (j < used) {
+                    float more[CH];
+                    tmem_load<CH>(at + j * BN, more);
+#pragma unroll
+                    for (int q = 0; q < CH; q++) g[q] += more[q];
+                }
+            }
+        };
 
         // one chunk of CH accumulator columns: g (and u for SwiGLU) -> C
         auto emit = [&](int c, const float* g, const float* u) {
@@ -365,8 +398,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (ok) {
                 for (int c = 0; c < OUT_COLS; c += CH) {
                     float g[CH], u[CH];
-                    tmem_load<CH>(lane_addr + c, g);
-                    if (EPI == EPI_SWIGLU) tmem_load<CH>(lane_addr + (SWAPPED ? BN : BN / 2) + c, u);
+                    acc_load(c, g);
+                    if (EPI == EPI_SWIGLU) {
+                        if (SWAPPED) acc_load(BN + c, u);
+                        else tmem_load<CH>(lane_addr + BN / 2 + c, u);
+                    }
                     emit(c, g, u);
                 }
             }
@@ -378,7 +414,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // columns beyond the last token.
             for (int c = 0; c < ACC_COLS; c += CH) {
                 float g[CH];
-                if (ok && my_blocks > 0) tmem_load<CH>(lane_addr + c, g);
+                if (ok && my_blocks > 0) acc_load(c, g);
                 else {
 #pragma unroll
                     for (int j = 0; j < CH; j++) g[j] = 0.f;
@@ -423,7 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             float* mine = ws_tile + (size_t)blockIdx.z * (ACC_COLS * TILE_M);
             for (int c = 0; c < ACC_COLS; c += CH) {
                 float g[CH];
-                if (ok && my_blocks > 0) tmem_load<CH>(lane_addr + c, g);
+                if (ok && my_blocks > 0) acc_load(c, g);
                 else {
 #pragma unroll
                     for (int j = 0; j < CH; j++) g[j] = 0.f;
@@ -472,7 +508,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     }
 
-    if (p.cluster && p.splits > 1 && warp < 2) {   // the warps without an epilogue take part in both barriers
+    if (p.cluster && p.splits > 1 && (warp < 2 || warp >= 6)) {   // the warps without an epilogue take part in both barriers
         __syncwarp();
         cluster_sync_all();
         cluster_sync_all();
@@ -700,7 +736,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, 
     if (p.cluster && p.splits > 1) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
-        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.blockDim = dim3(tile_threads(BN, SWAPPED, EPI));
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
@@ -714,7 +750,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, 
         cfg.numAttrs = 2;
         e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, p);
     } else {
-        e = launch_pdl(kernel, grid, dim3(NUM_THREADS), smem, stream, ma, mb, p);
+        e = launch_pdl(kernel, grid, dim3(tile_threads(BN, SWAPPED, EPI)), smem, stream, ma, mb, p);
     }
     if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("gemm_tc");
