@@ -22,7 +22,7 @@
 namespace {
 
 constexpr int CHUNK = 128, BLOCK_KEYS = 64, D = 128, NQ = 16;
-constexpr int NUM_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 and 6-9: two softmax groups that take turns
+constexpr int NUM_THREADS = 352;   // warp 0 TMA, warp 1 MMAs of the scores, warps 2-5 and 6-9: two softmax groups that take turns, warp 10 MMAs of the sums
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct DecodeTcParams {
@@ -280,66 +280,55 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 if (lane < 10) load_box(it, s, lane);
             }
         } else if (warp == 1 && lane == 0) {
-            // ---- MMA issuer: takes whatever is ready: the scores of the next item whose keys have landed (and
-            // whose accumulator pair is free), or the weighted sum of the oldest item whose P^T is written.
-            // The descriptors of stage 0 once; per instruction only constants are added (the address sits in the low
-            // bits in units of 16 bytes, and shared memory is too small to carry out of them).
-            const uint64_t k_desc0 = desc_k_major(k_of(0)), q_desc0 = desc_k_major(q_of(0)), p_desc0 = desc_k_major(p_of(0));
-            const uint64_t v_desc0 = desc_mn_major(v_of(0), BOX);
+            // ---- MMAs of the scores: S^T(n) = K(n) Q^T as soon as the keys have landed and the accumulator pair of
+            // n's parity is free.  (A thread that issues MMAs is slow at it: an MMA costs it ~56 cycles and a look
+            // at a barrier ~190, so the two kinds of product have a thread each.  The descriptors of stage 0 are
+            // built once; per instruction only constants are added: the address sits in the low bits in units of
+            // 16 bytes, and shared memory is too small to carry out of them.)
+            const uint64_t k_desc0 = desc_k_major(k_of(0)), q_desc0 = desc_k_major(q_of(0));
             constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
-            int next_s = 0, next_o = 0;       // next item that needs its scores / its weighted sum
-            uint32_t idle = 0;
-            while (next_o < n_items && !*abort_flag) {
-                bool progressed = false;
-                if (next_s < n_items && next_s <= next_o + 1) {
-                    const int n = next_s, s = n % STAGES, t = n & 1;
-                    if (mbar_try_wait(kq_full + 8 * s, (uint32_t)((n / STAGES) & 1)) &&
-                        (n < 2 || mbar_try_wait(tmem_free + 8 * t, (uint32_t)(((n >> 1) - 1) & 1)))) {
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint64_t kd = k_desc0 + s * STAGE_STEP, qd = q_desc0 + s * STAGE_STEP;
+            for (int n = 0; n < n_items; n++) {
+                const int s = n % STAGES, t = n & 1;
+                if (!mbar_wait(kq_full + 8 * s, (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 121)) break;
+                if (n >= 2 && !mbar_wait(tmem_free + 8 * t, (uint32_t)(((n >> 1) - 1) & 1), abort_flag, p.status, 123)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t kd = k_desc0 + s * STAGE_STEP, qd = q_desc0 + s * STAGE_STEP;
     #pragma unroll
-                        for (int k = 0; k < D / 16; k++) {
-                            constexpr int HALF_Q = NQ * 128;
-                            const uint64_t k_off = ((k / 4) * HALF_K + (k % 4) * 32) >> 4, q_off = ((k / 4) * HALF_Q + (k % 4) * 32) >> 4;
-                            umma_bf16(tmem_base + 32 * t, kd + k_off, qd + q_off, IDESC_S, k > 0 ? 1u : 0u);
-                        }
-                        umma_commit(s_done + 8 * t);
-                        next_s++;
-                        progressed = true;
+                for (int k = 0; k < D / 16; k++) {
+                    constexpr int HALF_Q = NQ * 128;
+                    const uint64_t k_off = ((k / 4) * HALF_K + (k % 4) * 32) >> 4, q_off = ((k / 4) * HALF_Q + (k % 4) * 32) >> 4;
+                    umma_bf16(tmem_base + 32 * t, kd + k_off, qd + q_off, IDESC_S, k > 0 ? 1u : 0u);
+                }
+                umma_commit(s_done + 8 * t);
+            }
+        } else if (warp == 10 && lane == 0) {
+            // ---- MMAs of the weighted sums: O^T(n) = V(n)^T P^T(n) once P^T is written and the values have landed
+            const uint64_t p_desc0 = desc_k_major(p_of(0)), v_desc0 = desc_mn_major(v_of(0), BOX);
+            constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
+            int n = 0;
+            for (; n < n_items; n++) {
+                const int s = n % STAGES, t = n & 1;
+                if (!mbar_wait(p_ready + 8 * t, (uint32_t)((n >> 1) & 1), abort_flag, p.status, 127)) break;
+                if (!mbar_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 129)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t vd = v_desc0 + s * STAGE_STEP, pd = p_desc0 + s * STAGE_STEP;
+                const int blocks_here = items[n].blocks_here;
+    #pragma unroll
+                for (int kb = 0; kb < 2; kb++) {
+                    if (kb < blocks_here) {
+    #pragma unroll
+                        for (int k = 0; k < BLOCK_KEYS / 16; k++)
+                            umma_bf16(tmem_base + 32 * t + 16, vd + ((kb * 2 * BOX + k * (16 * 128)) >> 4),
+                                      pd + ((kb * (NQ * 128) + k * 32) >> 4), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                 }
-                if (next_o < next_s) {
-                    const int n = next_o, s = n % STAGES, t = n & 1;
-                    if (mbar_try_wait(p_ready + 8 * t, (uint32_t)((n >> 1) & 1)) &&
-                        mbar_try_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1))) {
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint64_t vd = v_desc0 + s * STAGE_STEP, pd = p_desc0 + s * STAGE_STEP;
-                        const int blocks_here = items[n].blocks_here;
-    #pragma unroll
-                        for (int kb = 0; kb < 2; kb++) {
-                            if (kb < blocks_here) {
-    #pragma unroll
-                                for (int k = 0; k < BLOCK_KEYS / 16; k++)
-                                    umma_bf16(tmem_base + 32 * t + 16, vd + ((kb * 2 * BOX + k * (16 * 128)) >> 4),
-                                              pd + ((kb * (NQ * 128) + k * 32) >> 4), IDESC_O, (kb > 0 || k > 0) ? 1u : 0u);
-                            }
-                        }
-                        umma_commit(o_done + 8 * t);
-                        umma_commit(stage_free + 8 * s);
-                        next_o++;
-                        progressed = true;
-                    }
-                }
-                if (progressed) idle = 0;
-                else if (++idle > WAIT_LIMIT) {   // nothing became ready for a long time: give up, flag it
-                    *abort_flag = 1;
-                    atomicExch(p.status, 121);
-                }
+                umma_commit(o_done + 8 * t);
+                umma_commit(stage_free + 8 * s);
             }
             // the last commits have arrived before the barriers are set up again for another round
-            for (int n = max(0, n_items - STAGES); n < n_items && !*abort_flag; n++)
-                mbar_wait(stage_free + 8 * (n % STAGES), (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 122);
-        } else if (warp >= 2) {
+            for (int m = max(0, n - STAGES); m < n && !*abort_flag; m++)
+                mbar_wait(stage_free + 8 * (m % STAGES), (uint32_t)((m / STAGES) & 1), abort_flag, p.status, 122);
+        } else if (warp >= 2 && warp < 10) {
             // ---- softmax (thread = key), then partial output (thread = d).  Two groups of four warps take turns:
             // group 0 the even items of this CTA with accumulator pair 0, group 1 the odd ones with pair 1.
             const int grp = (warp - 2) >> 2, quarter = warp & 3, t = quarter * 32 + lane;
