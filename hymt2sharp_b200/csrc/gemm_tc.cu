@@ -15,9 +15,10 @@
 //            split CTAs of a tile form a thread-block cluster: each leaves its partial tile in
 //            its own shared memory, and after the cluster's barrier every CTA adds the partials
 //            of all ranks for its share of the token columns through distributed shared memory,
-//            in rank order (so the sum is the same every time), and runs the epilogue for them.  (A partial tile too large for the
-//            stage ring goes through a global workspace instead, folded by the CTA that arrives
-//            last at the tile's counter, also in split order.)
+//            in rank order (so the sum is the same every time), and runs the epilogue for them.
+//            (Where a ring for two CTAs on an SM would be too shallow, each split CTA has an SM to
+//            itself and a deep ring; partial tiles then go through a global workspace, folded by the
+//            CTA that arrives last at the tile's counter, also in split order.)
 // Epilogues: store, accumulate into float32 C, SwiGLU (silu(gate) * up; W holds N gate rows,
 // then N up rows; src/HyMT2Sharp/Ops.cs:1053).  Rows and K beyond the matrices are zero-filled
 // by TMA and masked in the epilogue, so any T and N are taken; K, lda and ldw must be multiples
@@ -815,13 +816,15 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     pl.grid.z = pl.splits;
     const int stage_bytes = num_acc * A_TILE_BYTES + pl.bn * BLOCK_K * 2;
     const long ctas = (long)pl.grid.x * pl.grid.y * pl.splits;
-    // A split whose whole K slice is short goes the cluster way, with shared memory for two CTAs on an SM
-    // (clusters must be placed whole inside a GPC; with one CTA per SM they would not all fit at once).
-    // Long slices stream best with one CTA per SM and a deep ring, and fold through the global workspace.
-    pl.cluster = pl.splits > 1 && pl.splits <= 8 && (long)pl.k_blocks_per_split * stage_bytes <= 128 * 1024 &&
+    // Splits go the cluster way when a ring for two CTAs on an SM still holds four stages (clusters must be placed
+    // whole inside a GPC; with one CTA per SM they would not all fit at once): the fold through distributed shared
+    // memory is quick.  Wide stages (two accumulators) stream best with one CTA per SM and a deep ring, and fold
+    // through the global workspace.
+    constexpr int CLUSTER_BUDGET = 110 * 1024;
+    pl.cluster = pl.splits > 1 && pl.splits <= 8 && CLUSTER_BUDGET / stage_bytes >= 4 &&
                  (size_t)num_acc * pl.bn * TILE_M * 4 <= 96 * 1024;
     // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
-    const int budget = ((ctas <= sm_count && !pl.cluster) || pl.persistent) ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM
+    const int budget = pl.cluster ? CLUSTER_BUDGET : (ctas <= sm_count || pl.persistent) ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM
     int stages = budget / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
     if (pl.swapped && stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
