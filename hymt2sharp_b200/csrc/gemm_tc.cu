@@ -43,7 +43,26 @@ constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 constexpr int PERSISTENT_BN = 256;   // tile width of the persistent kernel for many tokens
 
-enum { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE_KV = 3 };
+
+// What the EPI_ROPE_KV epilogue needs: the product is the fused q/k/v projection of a few tokens with heads of 128 (one
+// tile of 128 output features = one head), and the epilogue does what the rotation kernel would do next
+// (src/HyMT2Sharp/Ops.cs:98-195, src/HyMT2Sharp/HunyuanDenseModel.Prefill.cs:53-61): rotate-half rotation of q and k heads,
+// per-head RMSNorm after it, q to its own tensor, k and v to their rows of the paged cache.
+struct RopeEpilogue {
+    __nv_bfloat16* q_out;      // [T, nh * 128]
+    __nv_bfloat16* k_cache;    // one layer's plane [blocks][nkv][block_tokens][128]
+    __nv_bfloat16* v_cache;
+    const int* block_table;
+    const int* token_seq;      // [T] batch row of each token
+    const int* token_pos;      // [T] position of each token
+    const int* slot_ids;       // [B] cache slot of each batch row, -1: padding
+    const float* inv_freq;     // [rope_dim / 2], null when rope_dim == 0
+    const void* q_gain;        // [128] or null
+    const void* k_gain;
+    int table_stride, block_tokens, nh, nkv, rope_dim, write_kv, gain_bf16;
+    float eps;
+};
 
 struct GemmTcParams {
     void* C;
@@ -55,6 +74,7 @@ struct GemmTcParams {
     float* workspace;        // [tile][split][acc][BN][128] partial tiles (splits > 1)
     int* counters;           // [tile] arrivals, zero between launches
     int* status;
+    RopeEpilogue rope;       // EPI_ROPE_KV only
     const uint8_t* prefetch;  // what a LATER kernel will stream (its weights): asked into L2 while this kernel waits
     long prefetch_bytes;
 };
@@ -176,7 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
-    pdl_launch_dependents();
+    // (the kernel that follows the q/k/v epilogue, attention, reads lengths, tables and old cache blocks before its
+    // own wait: it may only start once everything in front of THIS kernel is complete, see the epilogue warps)
+    if (EPI != EPI_ROPE_KV) pdl_launch_dependents();
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
@@ -305,6 +327,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int row = quarter * 32 + lane;                   // row of the tile that this thread owns
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         pdl_wait();   // C, the workspace and the counters may still be in use by the kernel before
+        if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();   // wait first, release after
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         TC* C = (TC*)p.C;
@@ -443,7 +466,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float g = 0.f, u = 0.f;
 #pragma unroll
                     for (int r = 0; r < MAX_RANKS; r++) { g += pg[r]; u += pu[r]; }
-                    if (n < p.N) {
+                    if constexpr (EPI == EPI_ROPE_KV) {
+                        // this tile is head blockIdx.x of token b_row0 + c, this thread its value d = row
+                        const RopeEpilogue& rp = p.rope;
+                        const int t = b_row0 + c, head = blockIdx.x, d = row;
+                        const float x = __bfloat162float(__float2bfloat16_rn(g));   // what the projection would have stored
+                        const int pos = rp.token_pos[t], slot = rp.slot_ids[rp.token_seq[t]];
+                        const bool is_q = head < rp.nh, is_k = !is_q && head < rp.nh + rp.nkv;
+                        size_t cache_at = 0;
+                        const bool write_kv = !is_q && rp.write_kv && slot >= 0;
+                        if (write_kv) {
+                            const int block = rp.block_table[(size_t)slot * rp.table_stride + pos / rp.block_tokens];
+                            const int kvh = is_k ? head - rp.nh : head - rp.nh - rp.nkv;
+                            cache_at = (((size_t)block * rp.nkv + kvh) * rp.block_tokens + (pos % rp.block_tokens)) * TILE_M + d;
+                        }
+                        if (!is_q && !is_k) {   // a value head: as it is (the whole CTA is this head: no barrier is missed)
+                            if (write_kv) rp.v_cache[cache_at] = __float2bfloat16_rn(x);
+                        } else {
+                            const uint32_t ex = tiles + ACC_COLS * TILE_M * 4;   // 128 values to trade partners, then 4 sums
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + d * 4), "f"(x) : "memory");
+                            asm volatile("bar.sync 1, 128;" ::: "memory");
+                            const int half = rp.rope_dim / 2;
+                            float y = x;
+                            if (d < rp.rope_dim) {
+                                const bool low = d < half;
+                                float other, sn, cs;
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(ex + (low ? d + half : d - half) * 4) : "memory");
+                                sincosf((float)pos * rp.inv_freq[low ? d : d - half], &sn, &cs);
+                                y = low ? x * cs - other * sn : other * sn + x * cs;
+                            }
+                            const void* gain = is_q ? rp.q_gain : rp.k_gain;
+                            if (gain) {
+                                const float ss = warp_sum(y * y);
+                                if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + (TILE_M + quarter) * 4), "f"(ss) : "memory");
+                                asm volatile("bar.sync 1, 128;" ::: "memory");
+                                float s0, s1, s2, s3;
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s0) : "r"(ex + (TILE_M + 0) * 4) : "memory");
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s1) : "r"(ex + (TILE_M + 1) * 4) : "memory");
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s2) : "r"(ex + (TILE_M + 2) * 4) : "memory");
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s3) : "r"(ex + (TILE_M + 3) * 4) : "memory");
+                                const float scale = 1.0f / sqrtf((((s0 + s1) + s2) + s3) / (float)TILE_M + rp.eps);
+                                const float gv = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[d]) : ((const float*)gain)[d];
+                                y = y * scale * gv;
+                            }
+                            if (is_q) rp.q_out[((size_t)t * rp.nh + head) * TILE_M + d] = __float2bfloat16_rn(y);
+                            else if (write_kv) rp.k_cache[cache_at] = __float2bfloat16_rn(y);
+                            asm volatile("bar.sync 1, 128;" ::: "memory");   // the next column trades through the same words
+                        }
+                    } else if (n < p.N) {
                         TC* dst = C + (size_t)(b_row0 + c) * p.ldc + n;
                         if (EPI == EPI_STORE) *dst = from_float<TC>(g);
                         else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(to_float(*dst) + g);
@@ -910,7 +980,7 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
     GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
-                   (const uint8_t*)prefetch, (prefetch && (uintptr_t)prefetch % 16 == 0 && pl.swapped) ? prefetch_bytes : 0};
+                   RopeEpilogue{}, (const uint8_t*)prefetch, (prefetch && (uintptr_t)prefetch % 16 == 0 && pl.swapped) ? prefetch_bytes : 0};
     if (pl.swapped) {
         switch (pl.bn) {
             case 16: return dispatch_epilogue<16, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
@@ -921,4 +991,51 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     }
     if (pl.persistent) return launch_persistent(ma, mb, p, pl, epilogue, c_dtype, stream);
     return dispatch_epilogue<128, false>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+}
+
+// Whether hymt2_gemm_tc_rope_kv takes a projection of T tokens onto N = (nh + 2 nkv) * 128 features over K: it needs
+// the split-K cluster plan, whose CTAs each hold whole heads of a few tokens.
+HYMT2_API int hymt2_gemm_tc_rope_kv_supported(int T, int N, int K) {
+    if (T <= 0 || T > 64 || N <= 0 || N % TILE_M || K <= 0 || K % 8) return 0;
+    Plan pl;
+    make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl);
+    return (pl.swapped && pl.cluster && pl.bn <= 64) ? 1 : 0;
+}
+
+// The fused q/k/v projection of a few tokens with everything that follows it up to the cache: q_out[T, nh*128] gets the
+// rotated (and normed) queries, the cache planes get the rotated (and normed) keys and the values of every token whose
+// batch row has a slot.  X[T, K] (lda), W[(nh + 2 nkv) * 128, K] (ldw), both bfloat16; head_dim is 128.
+HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, long lda, long ldw, void* q_out, void* k_cache,
+                                    void* v_cache, const int* block_table, int table_stride, int block_tokens,
+                                    const int* token_seq, const int* token_pos, const int* slot_ids, const float* inv_freq,
+                                    int rope_dim, const void* q_gain, const void* k_gain, int gain_dtype, float eps, int nh,
+                                    int nkv, int write_kv, int* status, const void* prefetch, long prefetch_bytes,
+                                    cudaStream_t stream) {
+    if (T == 0) return HYMT2_OK;
+    const int N = (nh + 2 * nkv) * TILE_M;
+    HYMT2_REQUIRE(T > 0 && nh > 0 && nkv > 0 && K > 0, "gemm_tc_rope_kv: bad sizes T=%d nh=%d nkv=%d K=%d", T, nh, nkv, K);
+    HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_rope_kv: K, lda and ldw must be multiples of 8");
+    HYMT2_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc_rope_kv: operands must be 16-byte aligned");
+    HYMT2_REQUIRE(rope_dim >= 0 && rope_dim <= TILE_M && rope_dim % 2 == 0, "gemm_tc_rope_kv: rope_dim %d must be even and at most 128", rope_dim);
+    HYMT2_REQUIRE(rope_dim == 0 || inv_freq, "gemm_tc_rope_kv: rope_dim %d needs a frequency table", rope_dim);
+    HYMT2_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "gemm_tc_rope_kv: q and k gains come together");
+    HYMT2_REQUIRE(!q_gain || gain_dtype == HYMT2_BF16 || gain_dtype == HYMT2_F32, "gemm_tc_rope_kv: gains must be bfloat16 or float32");
+    HYMT2_REQUIRE(block_tokens > 0 && q_out && status, "gemm_tc_rope_kv: missing arguments");
+    HYMT2_REQUIRE(!write_kv || (k_cache && v_cache), "gemm_tc_rope_kv: the cache planes are needed to write keys and values");
+    HYMT2_REQUIRE(hymt2_gemm_tc_rope_kv_supported(T, N, K), "gemm_tc_rope_kv: T=%d N=%d K=%d does not get the cluster plan", T, N, K);
+    Plan pl;
+    make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl);
+    CUtensorMap ma, mb;
+    HYMT2_REQUIRE(make_map(&ma, W, N, K, ldw, TILE_M) && make_map(&mb, X, T, K, lda, pl.bn),
+                  "gemm_tc_rope_kv: cuTensorMapEncodeTiled refused the operands");
+    RopeEpilogue rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, token_seq, token_pos,
+                      slot_ids, inv_freq, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
+                      gain_dtype == HYMT2_BF16 ? 1 : 0, eps};
+    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, 1, nullptr, nullptr, status, rope,
+                   (const uint8_t*)prefetch, (prefetch && (uintptr_t)prefetch % 16 == 0) ? prefetch_bytes : 0};
+    switch (pl.bn) {
+        case 16: return launch<16, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
+        case 32: return launch<32, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
+        default: return launch<64, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
+    }
 }

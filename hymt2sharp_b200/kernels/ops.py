@@ -205,6 +205,66 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, 
                                 c_long(pf_bytes), _stream()), "gemm_tc")
 
 
+def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: int, d: int, cache_dtype) -> bool:
+    """Whether the fused projection + rotation + cache append takes these operands: bfloat16, head_dim 128,
+    few enough tokens that the product is cut over K among clusters."""
+    if d != 128 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or cache_dtype != torch.bfloat16:
+        return False
+    if x.dim() != 2 or w.dim() != 2 or x.stride(1) != 1 or w.stride(1) != 1 or w.shape != ((nh + 2 * nkv) * d, x.shape[1]):
+        return False
+    K = x.shape[1]
+    if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    return bool(_lib().hymt2_gemm_tc_rope_kv_supported(c_int(x.shape[0]), c_int(w.shape[0]), c_int(K)))
+
+
+def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None,
+                    v_plane: torch.Tensor | None, block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor,
+                    token_pos: torch.Tensor, slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int,
+                    q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float, nh: int, nkv: int,
+                    status: torch.Tensor, prefetch: torch.Tensor | None = None) -> None:
+    """q_out[T, nh*128] = rotation and per-head norm of the query part of x @ w^T; the key part, rotated and
+    normed, and the value part go to the rows of the cache planes that (slot, position) of every token name
+    (k_plane None: nothing is written).  One tcgen05 kernel; head_dim 128; see rope_kv for the arguments."""
+    d = 128
+    T = x.shape[0]
+    if not gemm_tc_rope_kv_supported(x, w, nh, nkv, d, (k_plane if k_plane is not None else q_out).dtype):
+        raise KernelError(f"gemm_tc_rope_kv: operands x {tuple(x.shape)} {x.dtype} w {tuple(w.shape)} {w.dtype} are not taken")
+    _need(q_out, "q_out", torch.bfloat16, 2)
+    if q_out.shape != (T, nh * d) or not q_out.is_contiguous():
+        raise KernelError(f"gemm_tc_rope_kv: q_out is {tuple(q_out.shape)}, expected {(T, nh * d)}")
+    write = k_plane is not None
+    if write:
+        for t, n in ((k_plane, "k_plane"), (v_plane, "v_plane")):
+            _need(t, n, torch.bfloat16, 4)
+            if t.shape[1:] != (nkv, block_tokens, d):
+                raise KernelError(f"gemm_tc_rope_kv: {n} is {tuple(t.shape)}, expected [blocks, {nkv}, {block_tokens}, {d}]")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slot_ids, "slot_ids")):
+        _need(t, n, torch.int32, 1)
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rope_dim // 2:
+            raise KernelError("gemm_tc_rope_kv: inv_freq must hold rope_dim/2 values")
+    gain_dtype = F32
+    if q_gain is not None:
+        _need(q_gain, "q_gain", None, 1); _need(k_gain, "k_gain", q_gain.dtype, 1)
+        if q_gain.shape[0] != d or k_gain.shape[0] != d:
+            raise KernelError("gemm_tc_rope_kv: the gains must hold head_dim values")
+        gain_dtype = dtype_code(q_gain.dtype)
+    pf_bytes = 0
+    if prefetch is not None and prefetch.is_contiguous():
+        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES)
+    else:
+        prefetch = None
+    _check(_lib().hymt2_gemm_tc_rope_kv(_ptr(x), _ptr(w), c_int(T), c_int(x.shape[1]), c_long(x.stride(0)), c_long(w.stride(0)),
+                                        _ptr(q_out), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
+                                        c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq), _ptr(token_pos),
+                                        _ptr(slot_ids), _ptr(inv_freq), c_int(rope_dim), _ptr(q_gain), _ptr(k_gain),
+                                        c_int(gain_dtype), c_float(eps), c_int(nh), c_int(nkv), c_int(1 if write else 0),
+                                        _ptr(status), _ptr(prefetch), c_long(pf_bytes), _stream()), "gemm_tc_rope_kv")
+
+
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,
             block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor,
             slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int, q_gain: torch.Tensor | None,

@@ -75,18 +75,27 @@ class GQAAttention:
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot) -> None:
         T = ctx.num_tokens
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim
-        qkv = self.qkv(x)
         table = self.position.rotary_table() if self.position is not None else None
-        if table is None and self.position is not None:
-            self.position.apply(qkv, ctx, nh, nkv, d)
         inv_freq, rope_dim = table if table is not None else (None, 0)
         k_plane, v_plane = ctx.cache.plane(slot.group, slot.plane)
         block_table = ctx.cache.tables[slot.group]
-        q = torch.empty((T, nh * d), dtype=qkv.dtype, device=qkv.device)
-        ops.rope_kv(qkv, q, k_plane if slot.writes else None, v_plane if slot.writes else None, block_table,
-                    ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids, inv_freq, rope_dim,
-                    self.q_gain, self.k_gain, self.eps, nh, nkv, d)
-        out = torch.empty((T, nh * d), dtype=qkv.dtype, device=qkv.device)
+        fused = (table is not None or self.position is None) and x.shape[0] == T and \
+            ops.gemm_tc_rope_kv_supported(x, self.qkv.weight, nh, nkv, d, k_plane.dtype)
+        if fused:
+            # a few tokens: projection, rotation, norm and cache append are one kernel
+            q = torch.empty((T, nh * d), dtype=x.dtype, device=x.device)
+            ops.gemm_tc_rope_kv(x, self.qkv.weight, q, k_plane if slot.writes else None, v_plane if slot.writes else None,
+                                block_table, ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids, inv_freq,
+                                rope_dim, self.q_gain, self.k_gain, self.eps, nh, nkv, ops.device_status(x.device))
+        else:
+            qkv = self.qkv(x)
+            if table is None and self.position is not None:
+                self.position.apply(qkv, ctx, nh, nkv, d)
+            q = torch.empty((T, nh * d), dtype=qkv.dtype, device=qkv.device)
+            ops.rope_kv(qkv, q, k_plane if slot.writes else None, v_plane if slot.writes else None, block_table,
+                        ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids, inv_freq, rope_dim,
+                        self.q_gain, self.k_gain, self.eps, nh, nkv, d)
+        out = torch.empty((T, nh * d), dtype=q.dtype, device=q.device)
         self.attend(out, q, k_plane, v_plane, block_table, ctx)
         self.out(out, out=residual, then=ctx.weights_ahead if ctx.decode else None)
 

@@ -256,6 +256,71 @@ def test_rope_qknorm_kv_append(dtype, nh, nkv, d, rope_dim, norm):
     assert torch.equal(q2, q_out)
 
 
+@pytest.mark.parametrize("T, nh, nkv, K, rope_dim, norm, gain_dtype", [
+    (11, 16, 4, 2048, 128, True, torch.bfloat16), (1, 4, 2, 1024, 128, False, torch.bfloat16),
+    (11, 6, 1, 1096, 48, True, torch.float32), (8, 16, 4, 2048, 0, True, torch.bfloat16), (40, 8, 2, 2048, 128, True, torch.bfloat16)])
+def test_projection_with_rotation_and_cache_append_in_one_kernel(T, nh, nkv, K, rope_dim, norm, gain_dtype):
+    """The fused kernel (q/k/v projection, rotation, per-head norm, cache append; head_dim 128) against the
+    kernels it replaces: the plain projection followed by rope_kv.  Positions across block borders, a padding
+    row, a rotation of part of the head, no rotation, gains of both types, and a run that writes no keys."""
+    ops = _ops()
+    torch.manual_seed(T + nh + K)
+    d, bt, dtype = 128, 64, torch.bfloat16
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    base_pos = [0, 1, 2, 63, 64, 65, 500, 7000, 3, 4, 127]
+    base_seq = [0, 0, 0, 1, 1, 1, 2, 3, 4, 4, 5]
+    if T <= 11:
+        pos, seq = base_pos[:T], base_seq[:T]
+    else:
+        pos, seq = list(range(100, 100 + T)), [0] * T
+    pos_t, seq_t = torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32)
+    slots = torch.tensor([2, 0, 3, 1, -1, 4], dtype=torch.int32)   # batch row 4 is padding
+    table = torch.full((5, 120), -1, dtype=torch.int32)
+    nblocks = 0
+    for t in range(T):
+        s = int(slots[seq[t]])
+        if s >= 0 and table[s, pos[t] // bt] < 0:
+            table[s, pos[t] // bt] = nblocks
+            nblocks += 1
+    x = torch.randn(T, K, device=DEV).to(dtype)
+    w = (torch.randn((nh + 2 * nkv) * d, K, device=DEV) / math.sqrt(K)).to(dtype)
+    inv = (1.0 / (10000.0 ** (torch.arange(rope_dim // 2, dtype=torch.float32) / max(1, rope_dim // 2)))).to(DEV) \
+        if rope_dim else None
+    qg = (1 + 0.1 * torch.randn(d, device=DEV)).to(gain_dtype) if norm else None
+    kg = (1 + 0.1 * torch.randn(d, device=DEV)).to(gain_dtype) if norm else None
+    eps = 1e-5
+    assert ops.gemm_tc_rope_kv_supported(x, w, nh, nkv, d, dtype)
+    dev = lambda t: t.to(DEV)
+    # the two kernels
+    qkv = torch.empty(T, (nh + 2 * nkv) * d, dtype=dtype, device=DEV)
+    ops.gemm_tc(qkv, x, w, ops.EPILOGUE_STORE, status)
+    kp2, vp2 = (torch.zeros(nblocks, nkv, bt, d, dtype=dtype, device=DEV) for _ in range(2))
+    q2 = torch.empty(T, nh * d, dtype=dtype, device=DEV)
+    ops.rope_kv(qkv, q2, kp2, vp2, dev(table), bt, dev(seq_t), dev(pos_t), dev(slots), inv, rope_dim, qg, kg, eps, nh, nkv, d)
+    # the one kernel
+    kp1, vp1 = (torch.zeros(nblocks, nkv, bt, d, dtype=dtype, device=DEV) for _ in range(2))
+    q1 = torch.full((T, nh * d), 9.0, dtype=dtype, device=DEV)
+    ops.gemm_tc_rope_kv(x, w, q1, kp1, vp1, dev(table), bt, dev(seq_t), dev(pos_t), dev(slots), inv, rope_dim, qg, kg, eps,
+                        nh, nkv, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert torch.equal(vp1, vp2)                                   # values are copied: the same bits
+    # rotation and norm round once more: at most the last bit of a bfloat16 differs
+    for one, two, what in ((q1, q2, "q"), (kp1, kp2, "k")):
+        diff = (one.float() - two.float()).abs()
+        assert float((diff / two.float().abs().clamp_min(1e-2)).max()) <= 2 ** -7, what
+        assert float((diff > 0).float().mean()) < 0.02, what
+    # a run that reads another layer's cache writes only q
+    q3 = torch.empty_like(q1)
+    ops.gemm_tc_rope_kv(x, w, q3, None, None, dev(table), bt, dev(seq_t), dev(pos_t), dev(slots), inv, rope_dim, qg, kg, eps,
+                        nh, nkv, status)
+    assert torch.equal(q3, q1)
+    # what it does not take: another head size, a prompt's worth of tokens
+    assert not ops.gemm_tc_rope_kv_supported(x, w, nh * 2, nkv * 2, 64, dtype)
+    big = torch.randn(300, K, device=DEV).to(dtype)
+    assert not ops.gemm_tc_rope_kv_supported(big, w, nh, nkv, d, dtype)
+
+
 def test_argmax_takes_the_first_maximum():
     ops = _ops()
     x = torch.randn(7, 120818, device=DEV)
