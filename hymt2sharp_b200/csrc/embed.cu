@@ -43,3 +43,26 @@ HYMT2_API int hymt2_advance_decode(int* token_pos, int* kv_lens, const int* slot
     launch_pdl(advance_decode_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, token_pos, kv_lens, slot_ids, rows);
     return hymt2_check_launch("advance_decode");
 }
+
+// Asks for `bytes` from `ptr` on to be brought into L2 (cp.async.bulk.prefetch.L2 in pieces of 16 KB), for a stream
+// beside the one that computes: a decode step leaves the memory idle most of the time, and the next large product's
+// weights can come in meanwhile.  Nothing is written anywhere.
+__global__ void l2_prefetch_kernel(const uint8_t* ptr, long bytes) {
+    constexpr long PIECE = 16384;
+    const long pieces = (bytes + PIECE - 1) / PIECE;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (long)gridDim.x * blockDim.x) {
+        const long off = i * PIECE;
+        const uint32_t n = (uint32_t)min(PIECE, bytes - off);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr + off), "r"(n) : "memory");
+    }
+}
+
+HYMT2_API int hymt2_l2_prefetch(const void* ptr, long bytes, cudaStream_t stream) {
+    bytes &= ~15L;
+    if (bytes <= 0) return HYMT2_OK;
+    HYMT2_REQUIRE(ptr != nullptr && (uintptr_t)ptr % 16 == 0, "l2_prefetch: the address must be 16-byte aligned");
+    const long pieces = (bytes + 16383) / 16384;
+    const unsigned blocks = (unsigned)(pieces < 128 * 32 ? (pieces + 31) / 32 : 128);
+    l2_prefetch_kernel<<<blocks, 32, 0, stream>>>((const uint8_t*)ptr, bytes);
+    return hymt2_check_launch("l2_prefetch");
+}

@@ -116,6 +116,7 @@ class DecoderModel:
         ops.embed(residual, self.embedding, ctx.tokens, ctx.status)
         for run, slot in zip(self.spec.order, self.slots):
             self.blocks[run.layer].forward(residual, ctx, slot)
+        ops.join_beside(ctx.device)   # what parts asked into L2 on the side stream
         if num_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=ctx.device)
         normed = self.final_norm.forward(residual, ctx, ctx.dtype, rows_index=want_rows, rows=num_want)

@@ -80,6 +80,39 @@ def advance_decode(token_pos: torch.Tensor, kv_lens: torch.Tensor, slot_ids: tor
                                        _stream()), "advance_decode")
 
 
+_side = {}   # device index -> (side stream, event, whether the side stream has work that the main stream has not joined)
+
+
+def prefetch_beside(t: torch.Tensor) -> None:
+    """Asks for the beginning of `t` (at most PREFETCH_MAX_BYTES) to be brought into L2 by a small kernel on a
+    stream BESIDE the current one, ordered after everything launched on the current stream so far.  The current
+    stream does not wait for it (join_beside does, once, at the end of a step), so kernels that follow run while
+    the memory fetches; in a captured step this is a branch of the graph."""
+    if t is None or not t.is_contiguous() or t.data_ptr() % 16:
+        return
+    nbytes = min(t.numel() * t.element_size(), PREFETCH_MAX_BYTES)
+    key = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    if key not in _side:
+        _side[key] = [torch.cuda.Stream(device=t.device), torch.cuda.Event(), False]
+    side, event, _ = _side[key]
+    main = torch.cuda.current_stream(t.device)
+    event.record(main)
+    side.wait_event(event)
+    with torch.cuda.stream(side):
+        _check(_lib().hymt2_l2_prefetch(_ptr(t), c_long(nbytes), _stream()), "l2_prefetch")
+    _side[key][2] = True
+
+
+def join_beside(device) -> None:
+    """The current stream waits for what prefetch_beside put on the side stream (a step calls it at its end)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _side.get(key)
+    if st and st[2]:
+        torch.cuda.current_stream(device).wait_stream(st[0])
+        st[2] = False
+
+
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float,
             rows_index: torch.Tensor | None = None) -> None:
     """out[r] = rmsnorm(x[rows_index[r]] or x[r]) * gain, computed in float32."""

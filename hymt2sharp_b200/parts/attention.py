@@ -97,7 +97,12 @@ class GQAAttention:
                         self.q_gain, self.k_gain, self.eps, nh, nkv, d)
         out = torch.empty((T, nh * d), dtype=q.dtype, device=q.device)
         self.attend(out, q, k_plane, v_plane, block_table, ctx)
-        self.out(out, out=residual, then=ctx.weights_ahead if ctx.decode else None)
+        if ctx.decode and ctx.weights_ahead is not None:
+            # the feed-forward's first weights come into L2 beside the output projection and the norm, which leave
+            # the memory idle; the request starts once the attention is through (not earlier: its last loads and
+            # the folding of its partials are sensitive to traffic)
+            ops.prefetch_beside(ctx.weights_ahead)
+        self.out(out, out=residual)
 
     def attend(self, out, q, k_plane, v_plane, block_table, ctx) -> None:
         from ..kernels import fast
