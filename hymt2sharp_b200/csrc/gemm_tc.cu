@@ -75,8 +75,6 @@ struct GemmTcParams {
     int* counters;           // [tile] arrivals, zero between launches
     int* status;
     RopeEpilogue rope;       // EPI_ROPE_KV only
-    const uint8_t* prefetch;  // what a LATER kernel will stream (its weights): asked into L2 while this kernel waits
-    long prefetch_bytes;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -263,19 +261,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int i = 0; i < ahead; i++) {   // fresh stages: nothing to wait for
             mbar_expect_tx(full0 + 8 * (i % stages), STAGE_BYTES);
             load_weights(i);
-        }
-        if (p.prefetch_bytes > 0) {
-            // this CTA's share of a later kernel's weights, behind its own first loads in the queue and before the wait
-            // for the kernel in front: a product of a few tokens leaves the memory idle most of its time, and the
-            // requests must be on their way early, since a kernel is only complete once they have been served
-            const long ctas = (long)gridDim.x * gridDim.y * gridDim.z;
-            const long cta = ((long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-            const long share = ((p.prefetch_bytes + ctas - 1) / ctas + 15) & ~15L;
-            const long begin = cta * share, end = min(p.prefetch_bytes & ~15L, begin + share);
-            for (long off = begin; off < end; off += 16384) {
-                const uint32_t n = (uint32_t)min(16384L, end - off);
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(n) : "memory");
-            }
         }
         pdl_wait();
         for (int i = 0; i < ahead; i++) load_activations(i);
@@ -953,11 +938,9 @@ HYMT2_API int hymt2_gemm_tc_plan(int T, int N, int K, int epilogue, long* worksp
 }
 
 // C[T,N] (ldc) = epilogue(X[T,K] (lda) · W[N,K]^T (ldw)), X and W bfloat16; for SwiGLU W has 2N rows.
-// prefetch / prefetch_bytes (may be null / 0): memory that a LATER kernel will stream, typically the next
-// product's weights; a product of few tokens asks for it to be brought into L2 while it waits for its input.
 HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
                             long ldc, int epilogue, float* workspace, long workspace_floats, int* counters,
-                            int num_counters, int* status, const void* prefetch, long prefetch_bytes, cudaStream_t stream) {
+                            int num_counters, int* status, cudaStream_t stream) {
     if (T == 0 || N == 0) return HYMT2_OK;
     HYMT2_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
     HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K, lda and ldw must be multiples of 8 (K=%d lda=%ld ldw=%ld)", K, lda, ldw);
@@ -980,7 +963,7 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
     GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
-                   RopeEpilogue{}, (const uint8_t*)prefetch, (prefetch && (uintptr_t)prefetch % 16 == 0 && pl.swapped) ? prefetch_bytes : 0};
+                   RopeEpilogue{}};
     if (pl.swapped) {
         switch (pl.bn) {
             case 16: return dispatch_epilogue<16, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
@@ -1009,8 +992,7 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
                                     void* v_cache, const int* block_table, int table_stride, int block_tokens,
                                     const int* token_seq, const int* token_pos, const int* slot_ids, const float* inv_freq,
                                     int rope_dim, const void* q_gain, const void* k_gain, int gain_dtype, float eps, int nh,
-                                    int nkv, int write_kv, int* status, const void* prefetch, long prefetch_bytes,
-                                    cudaStream_t stream) {
+                                    int nkv, int write_kv, int* status, cudaStream_t stream) {
     if (T == 0) return HYMT2_OK;
     const int N = (nh + 2 * nkv) * TILE_M;
     HYMT2_REQUIRE(T > 0 && nh > 0 && nkv > 0 && K > 0, "gemm_tc_rope_kv: bad sizes T=%d nh=%d nkv=%d K=%d", T, nh, nkv, K);
@@ -1031,8 +1013,7 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
     RopeEpilogue rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, token_seq, token_pos,
                       slot_ids, inv_freq, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
                       gain_dtype == HYMT2_BF16 ? 1 : 0, eps};
-    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, 1, nullptr, nullptr, status, rope,
-                   (const uint8_t*)prefetch, (prefetch && (uintptr_t)prefetch % 16 == 0) ? prefetch_bytes : 0};
+    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, 1, nullptr, nullptr, status, rope};
     switch (pl.bn) {
         case 16: return launch<16, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
         case 32: return launch<32, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);

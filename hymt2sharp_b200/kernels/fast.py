@@ -6,13 +6,12 @@ from __future__ import annotations
 import torch
 
 
-def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int, then: torch.Tensor | None = None) -> bool:
-    """bfloat16 operands with 16-byte aligned rows go to the tcgen05 kernel; anything else is refused.
-    `then`: what a later kernel will stream (see ops.gemm_tc)."""
+def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int) -> bool:
+    """bfloat16 operands with 16-byte aligned rows go to the tcgen05 kernel; anything else is refused."""
     from . import ops
     if not ops.gemm_tc_supported(out, x, w, epilogue):
         return False
-    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device), then)
+    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device))
     return True
 
 

@@ -80,6 +80,7 @@ def advance_decode(token_pos: torch.Tensor, kv_lens: torch.Tensor, slot_ids: tor
                                        _stream()), "advance_decode")
 
 
+PREFETCH_MAX_BYTES = 48 << 20   # of a larger tensor only the beginning is asked for: more would push too much else out of L2
 _side = {}   # device index -> (side stream, event, whether the side stream has work that the main stream has not joined)
 
 
@@ -205,15 +206,9 @@ def gemm_tc_supported(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
     return out.dtype == torch.bfloat16
 
 
-PREFETCH_MAX_BYTES = 48 << 20   # of a larger hint only the beginning is asked for: more would push too much else out of L2
-
-
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor,
-            prefetch: torch.Tensor | None = None) -> None:
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor) -> None:
     """out[T, N] = epilogue(a[T, K] @ w[N, K]^T) on the tcgen05 tensor cores (bfloat16 operands,
-    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows.  `prefetch`: a
-    contiguous tensor that a later kernel will stream (the next product's weights); a decode-sized
-    product asks for it to be brought into L2 while it waits for its own input."""
+    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows."""
     T, N = out.shape
     K = a.shape[1]
     rows_w = 2 * N if epilogue == EPILOGUE_SWIGLU else N
@@ -226,16 +221,10 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, 
     ws = cnt = None
     if floats.value:
         ws, cnt = _tc_workspace(out.device, floats.value, counters.value)
-    pf_bytes = 0
-    if prefetch is not None and prefetch.is_contiguous():
-        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES)
-    else:
-        prefetch = None
     _check(_lib().hymt2_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(T), c_int(N), c_int(K),
                                 c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)), c_int(epilogue),
                                 _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(cnt),
-                                c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _ptr(prefetch),
-                                c_long(pf_bytes), _stream()), "gemm_tc")
+                                c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream()), "gemm_tc")
 
 
 def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: int, d: int, cache_dtype) -> bool:
@@ -255,7 +244,7 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
                     v_plane: torch.Tensor | None, block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor,
                     token_pos: torch.Tensor, slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int,
                     q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float, nh: int, nkv: int,
-                    status: torch.Tensor, prefetch: torch.Tensor | None = None) -> None:
+                    status: torch.Tensor) -> None:
     """q_out[T, nh*128] = rotation and per-head norm of the query part of x @ w^T; the key part, rotated and
     normed, and the value part go to the rows of the cache planes that (slot, position) of every token name
     (k_plane None: nothing is written).  One tcgen05 kernel; head_dim 128; see rope_kv for the arguments."""
@@ -285,17 +274,12 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
         if q_gain.shape[0] != d or k_gain.shape[0] != d:
             raise KernelError("gemm_tc_rope_kv: the gains must hold head_dim values")
         gain_dtype = dtype_code(q_gain.dtype)
-    pf_bytes = 0
-    if prefetch is not None and prefetch.is_contiguous():
-        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES)
-    else:
-        prefetch = None
     _check(_lib().hymt2_gemm_tc_rope_kv(_ptr(x), _ptr(w), c_int(T), c_int(x.shape[1]), c_long(x.stride(0)), c_long(w.stride(0)),
                                         _ptr(q_out), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
                                         c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq), _ptr(token_pos),
                                         _ptr(slot_ids), _ptr(inv_freq), c_int(rope_dim), _ptr(q_gain), _ptr(k_gain),
                                         c_int(gain_dtype), c_float(eps), c_int(nh), c_int(nkv), c_int(1 if write else 0),
-                                        _ptr(status), _ptr(prefetch), c_long(pf_bytes), _stream()), "gemm_tc_rope_kv")
+                                        _ptr(status), _stream()), "gemm_tc_rope_kv")
 
 
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,

@@ -96,7 +96,8 @@ class StepContext:
     host_new_tokens: list = field(default_factory=list)  # that plan their work there
     host_starts: list = field(default_factory=list)
     # a hint from whoever arranges the parts: the weights that the next large kernel AFTER the running part will
-    # stream (or None); a part whose last kernel leaves the memory idle may ask for them ahead of time
+    # stream (or None); a part that leaves the memory idle towards its end may ask for them ahead of time
+    # (kernels.ops.prefetch_beside)
     weights_ahead: torch.Tensor | None = None
 
     @property

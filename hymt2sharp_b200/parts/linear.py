@@ -26,19 +26,16 @@ class Linear:
         self.out_features = rows // 2 if epilogue == ops.EPILOGUE_SWIGLU else rows
         self.in_features = weight.shape[1]
 
-    def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-                 then: torch.Tensor | None = None):
-        """`then`: the weights that the next large kernel after this product will stream, if the caller
-        knows them; a kernel that can asks for them to be brought into L2 while it waits for its own input."""
+    def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None):
         if out is None:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
-        matmul(out, x, self.weight, self.epilogue, then)
+        matmul(out, x, self.weight, self.epilogue)
         return out
 
 
-def matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int, then: torch.Tensor | None = None) -> None:
+def matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int) -> None:
     """Picks the kernel: tensor-core kernels where they take the shape and types, else CUDA cores."""
     from ..kernels import fast
-    if fast.try_matmul(out, x, w, epilogue, then):
+    if fast.try_matmul(out, x, w, epilogue):
         return
     ops.gemm_simt(out, x, w, epilogue)
