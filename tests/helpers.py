@@ -42,6 +42,14 @@ CONFIGS = {
                           rope_theta=10000.0, rope_scaling={"type": "dynamic", "alpha": 1000.0}, rms_norm_eps=1e-5,
                           use_qk_norm=True, tie_word_embeddings=True, max_position_embeddings=4096),
               seed=3, sigma=0.03, gain_dtype="bfloat16"),
+    # head_dim 128, the head size of the full-size models, with 2 heads per kv head and a q width (512) wider than
+    # the hidden size: the bfloat16 engine runs every tcgen05 kernel on this one (projection with rotation and
+    # cache append in its epilogue, decode attention with keys on the 128-row side, prompt attention, split-K products)
+    "H": dict(config=dict(architectures=[ARCH], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+                          num_key_value_heads=2, head_dim=128, intermediate_size=392, vocab_size=777,
+                          rope_theta=50000.0, rope_scaling={"type": "dynamic", "alpha": 4.0}, rms_norm_eps=1e-5,
+                          use_qk_norm=True, tie_word_embeddings=False, max_position_embeddings=4096),
+              seed=4, sigma=0.03, gain_dtype="bfloat16"),
 }
 
 # Tolerances, fixed before the kernels were tuned.  32-bit: differences come from the order of

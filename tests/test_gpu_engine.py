@@ -24,7 +24,7 @@ def _poison(eng):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W", "M"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "M", "H"])
 def test_long_decoding_from_the_first_token(name, dtype, model_dirs, plain_models):
     """A one-token prompt, then 420 tokens one by one (across block ends and past the length at
     which decode attention starts to split its keys), in a cache whose unwritten rows are NaN."""
@@ -168,3 +168,23 @@ def test_no_device_means_a_loud_error(monkeypatch):
     with pytest.raises(e.EngineError) as err:
         e.require_gpu("cuda:0")
     assert "no CPU path" in str(err.value)
+
+
+def test_the_fast_kernels_are_what_a_bfloat16_step_of_full_size_heads_runs(model_dirs):
+    """With heads of 128 a bfloat16 decode step is, per layer: norm, the projection that also rotates and
+    appends to the cache, attention, the request for the next weights, output projection, norm, gate/up, down.
+    A silent fall to the general kernels would show as more launches (a rotation kernel, a split attention
+    with its merge)."""
+    from hymt2sharp_b200.engine.engine import StepEntry
+    from hymt2sharp_b200.kernels import ops
+    eng = _engine(model_dirs, "H", "bfloat16")
+    slot = eng.alloc_slots(1)[0]
+    eng.step([StepEntry(slot, list(range(1, 301)), [299])])
+    before = ops.launches
+    eng.step([StepEntry(slot, [5], [0])])
+    layers = eng.config.num_hidden_layers
+    assert ops.launches - before == 1 + 8 * layers + 2   # embedding; the layers; final norm and head
+    q = torch.empty(1, 4 * 128, dtype=torch.bfloat16, device=DEV)
+    assert ops.gemm_tc_rope_kv_supported(torch.empty(1, 256, dtype=torch.bfloat16, device=DEV),
+                                         eng.model.blocks[0].mixer.qkv.weight, 4, 2, 128, q.dtype)
+    eng.check()

@@ -11,7 +11,7 @@ from plain.hunyuan_plain import PlainSampler, plain_generate
 
 pytestmark = pytest.mark.gpu
 
-PROMPT_LENS = {"A": [5, 9, 1], "B": [17, 3, 11, 6]}   # the workloads of the two tiny configurations
+PROMPT_LENS = {"A": [5, 9, 1], "B": [17, 3, 11, 6], "H": [70, 2, 130]}   # the workloads of the tiny configurations
 
 
 @pytest.fixture(scope="module")
@@ -34,7 +34,7 @@ def _margin_ok(plain, seq, tok, floor):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "H"])
 def test_greedy_generation_matches_plain(name, dtype, engines, plain_models):
     plain = plain_models(name)
     eng = engines(name, dtype)
