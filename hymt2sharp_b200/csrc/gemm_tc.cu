@@ -856,11 +856,12 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         }
         pl.tiles = tiles;
     } else {
-        // many tiles: the persistent kernel with 256-wide tiles (one CTA per SM, epilogue hidden behind the
-        // next tile); few tiles: 128-wide tiles, two CTAs per SM, so that all SMs get work
+        // a wide tile for every SM: the persistent kernel with 256-wide tiles (one CTA per SM, epilogue hidden
+        // behind the next tile); fewer: 128-wide tiles, two CTAs per SM, so that all SMs get work.  (Narrower
+        // persistent tiles, 128 and 192 wide, were measured too: they cost more per flop than they save in waves.)
         const int wide_cols = epilogue == EPI_SWIGLU ? PERSISTENT_BN / 2 : PERSISTENT_BN;
         const long wide_tiles = (long)((T + TILE_M - 1) / TILE_M) * ((N + wide_cols - 1) / wide_cols);
-        pl.persistent = wide_tiles * 2 >= 5L * sm_count;
+        pl.persistent = wide_tiles >= sm_count;   // measured at 2,048 tokens: QKV (192 wide tiles) gains, O and down (128) lose
         pl.bn = pl.persistent ? PERSISTENT_BN : 128;
         const int out_cols = epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn;
         pl.grid = dim3((T + TILE_M - 1) / TILE_M, (N + out_cols - 1) / out_cols, 1);
