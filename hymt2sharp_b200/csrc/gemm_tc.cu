@@ -876,12 +876,12 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     // whole inside a GPC; with one CTA per SM they would not all fit at once): the fold through distributed shared
     // memory is quick.  Wide stages (two accumulators) stream best with one CTA per SM and a deep ring, and fold
     // through the global workspace.
-    constexpr int CLUSTER_BUDGET = 110 * 1024;
-    pl.cluster = pl.splits > 1 && pl.splits <= 8 && CLUSTER_BUDGET / stage_bytes >= 4 &&
+    constexpr int CLUSTER_RING_BYTES = 110 * 1024;
+    pl.cluster = pl.splits > 1 && pl.splits <= 8 && CLUSTER_RING_BYTES / stage_bytes >= 4 &&
                  (size_t)num_acc * pl.bn * TILE_M * 4 <= 96 * 1024;
     // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
-    const int budget = pl.cluster ? CLUSTER_BUDGET : (ctas <= sm_count || pl.persistent) ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM
-    int stages = budget / stage_bytes;
+    const int ring_bytes = pl.cluster ? CLUSTER_RING_BYTES : (ctas <= sm_count || pl.persistent) ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM
+    int stages = ring_bytes / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
     if (pl.swapped && stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
     pl.stages = stages;
