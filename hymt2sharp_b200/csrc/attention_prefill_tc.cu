@@ -12,10 +12,13 @@
 // The running maximum of a row is only raised when the new maximum exceeds it by more than 2^8;
 // then the row's O in TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st).  Until then P is
 // taken relative to the older maximum, which gives the same quotient O / l.
-// Q, K and V tiles arrive by TMA (128-byte swizzle); K/V tiles are double-buffered, and so is S in tensor
-// memory: the scores of tile i + 1 are computed while the softmax warps work on tile i, and P·V of tile i
-// runs while they work on tile i + 1.  mbarriers order producer, MMA issuer and softmax warps; every wait
-// is bounded.
+// Q, K and V tiles arrive by TMA (128-byte swizzle).  S is double-buffered in tensor memory: the scores of
+// tile i + 1 are computed while the softmax warps work on tile i, and P·V of tile i runs while they work on
+// tile i + 1.  So K(i + 1) is needed at the same time as V(i), and the two travel together under one barrier;
+// K(0) comes with Q.  V has two slots and K three: P(i) is written over K(i), which therefore stays until
+// P·V of tile i is through, while K(i + 1) is in use and K(i + 2) is landing.  With K and V of a tile in one
+// slot of two, the copy of tile i + 2 could only start after P·V of tile i, and its latency lay on every
+// tile's path.  mbarriers order producer, MMA issuer and softmax warps; every wait is bounded.
 // Formulas: src/HyMT2Sharp/Ops.cs:359-455 (scores, kv head = head / group), :198-325 (softmax
 // over the visible keys), :535-595 (combine).  A query at position p sees keys
 // [max(0, p - window + 1), p].
@@ -26,7 +29,7 @@
 
 namespace {
 
-constexpr int Q_ROWS = 128, KEY_TILE = 64, NUM_THREADS = 192, KV_STAGES = 2;
+constexpr int Q_ROWS = 128, KEY_TILE = 64, NUM_THREADS = 192, KV_STAGES = 2, K_SLOTS = 3;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct PrefillParams {
@@ -126,20 +129,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, PrefillParams p) {
     constexpr int D_BOXES = D / 64;                         // TMA boxes of 64 elements along d
     constexpr int Q_BYTES = Q_ROWS * D * 2, KV_TILE_BYTES = KEY_TILE * D * 2, P_BYTES = Q_ROWS * KEY_TILE * 2;
-    // P of a tile (16 KB) takes the place of the tile's K (free once S is computed) when K is that large;
-    // else every stage has a P region of its own
-    constexpr bool P_IN_K = KV_TILE_BYTES >= P_BYTES;
-    constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES + (P_IN_K ? 0 : P_BYTES);
+    // P of a tile (16 KB) takes the place of the tile's K (free once S is computed): a K slot holds the larger of the two
+    constexpr int K_SLOT_BYTES = KV_TILE_BYTES >= P_BYTES ? KV_TILE_BYTES : P_BYTES;
+    constexpr int BARS_OFFSET = Q_BYTES + K_SLOTS * K_SLOT_BYTES + KV_STAGES * KV_TILE_BYTES;
     constexpr int TMEM_COLS = 256;                          // S of even tiles: columns [0, 64), of odd tiles [64, 128); O: [128, 128 + D)
     constexpr uint32_t S_COL = 0, O_COL = 128;
     // D float32, A and B bfloat16; S: both K-major, N = 64; O: B is MN-major, N = D
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KEY_TILE >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
     constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
 
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * KV_STAGES + 8];
-    __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s;
+    // No static shared memory: the dynamic part then starts on a 1 KB boundary, which the swizzled tiles need,
+    // and two CTAs of 112 KB fit an SM.  Barriers and the two words lie behind the tiles.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + BARS_OFFSET);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 8) * 8);
+    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 8) * 8 + 4);
 
     // The last query tiles of a prompt walk the most keys: CTAs are numbered by falling query tile, so the long
     // ones start first and the short ones fill the gaps.  When all CTAs fit on the SMs at once (two each), the
@@ -160,11 +164,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int tile_end = last_pos / KEY_TILE + 1;
     const int num_tiles = tile_end - tile_begin;
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_smem = base, kv_smem = q_smem + Q_BYTES;
-    auto k_of = [&](int s) { return kv_smem + s * STAGE_BYTES; };
-    auto v_of = [&](int s) { return kv_smem + s * STAGE_BYTES + KV_TILE_BYTES; };
-    auto p_of = [&](int s) { return P_IN_K ? kv_smem + s * STAGE_BYTES : kv_smem + s * STAGE_BYTES + 2 * KV_TILE_BYTES; };
+    const uint32_t base = smem_u32(smem_raw);
+    if (base & 1023u) {   // never seen; a swizzled tile off its boundary would give wrong numbers, not a fault
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 119);
+        return;
+    }
+    const uint32_t q_smem = base, k_smem = q_smem + Q_BYTES, v_smem = k_smem + K_SLOTS * K_SLOT_BYTES;
+    auto k_of = [&](int tile) { return k_smem + (tile % K_SLOTS) * K_SLOT_BYTES; };   // K of a tile, then its P
+    auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * KV_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
     const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
     const uint32_t s_full = q_full + 16, s_free = q_full + 32, p_full = q_full + 48;   // two of each: even and odd tiles
@@ -196,41 +203,45 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t tmem_base = tmem_base_s;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: Q once, then the K and V tiles ------------------------------------------
-        mbar_expect_tx(q_full, Q_BYTES);
-        for (int x = 0; x < D_BOXES; x++)
-            tma_load_2d(q_smem + x * (Q_ROWS * 128), &map_q, q_full, head * D + x * 64, tok0 + qtile * Q_ROWS);
+        // ---- producer: Q with K(0), then K(i + 1) with V(i) ---------------------------------------
         const int* table = p.block_table + (size_t)slot * p.table_stride;
+        auto cache_row = [&](int tile) { return (table[tile_begin + tile] * p.nkv + kvh) * KEY_TILE; };
+        mbar_expect_tx(q_full, Q_BYTES + KV_TILE_BYTES);
+        for (int x = 0; x < D_BOXES; x++) {
+            tma_load_2d(q_smem + x * (Q_ROWS * 128), &map_q, q_full, head * D + x * 64, tok0 + qtile * Q_ROWS);
+            tma_load_2d(k_of(0) + x * (KEY_TILE * 128), &map_k, q_full, x * 64, cache_row(0));
+        }
         int issued = 0;
         for (int i = 0; i < num_tiles; i++) {
             const int s = i % KV_STAGES;
+            // P·V of tile i - 2 is through: V's slot is free, and so is the slot of K(i - 2), which takes K(i + 1)
             if (!mbar_wait(kv_empty + 8 * s, ((i / KV_STAGES) & 1) ^ 1, abort_flag, p.status, 111)) break;
-            const int block = table[tile_begin + i];
-            const int row = (block * p.nkv + kvh) * KEY_TILE;
-            const uint32_t k_dst = k_of(s), v_dst = v_of(s);
-            mbar_expect_tx(kv_full + 8 * s, 2 * KV_TILE_BYTES);
+            const bool more = i + 1 < num_tiles;
+            mbar_expect_tx(kv_full + 8 * s, (more ? 2 : 1) * KV_TILE_BYTES);
+            const int v_row = cache_row(i), k_row = more ? cache_row(i + 1) : 0;
+            const uint32_t k_dst = k_of(i + 1), v_dst = v_of(i);
             for (int x = 0; x < D_BOXES; x++) {
-                tma_load_2d(k_dst + x * (KEY_TILE * 128), &map_k, kv_full + 8 * s, x * 64, row);
-                tma_load_2d(v_dst + x * (KEY_TILE * 128), &map_v, kv_full + 8 * s, x * 64, row);
+                if (more) tma_load_2d(k_dst + x * (KEY_TILE * 128), &map_k, kv_full + 8 * s, x * 64, k_row);
+                tma_load_2d(v_dst + x * (KEY_TILE * 128), &map_v, kv_full + 8 * s, x * 64, v_row);
             }
             issued = i + 1;
         }
-        if (*abort_flag)
+        if (*abort_flag) {   // nothing may still be landing when the CTA leaves
+            for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(q_full, 0); t++) {}
             for (int i = max(0, issued - KV_STAGES); i < issued; i++)
                 for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1); t++) {}
+        }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: S of the next tile goes out before P·V of this one -------------------------
-        // The descriptors of stage 0 once; per instruction only constants are added (the address sits in the
+        // The descriptors of slot 0 once; per instruction only constants are added (the address sits in the
         // low bits in units of 16 bytes, and shared memory is too small to carry out of them).
-        const uint64_t q_desc = desc_k_major(q_smem), k_desc0 = desc_k_major(k_of(0)), p_desc0 = desc_k_major(p_of(0));
-        const uint64_t v_desc0 = desc_mn_major(v_of(0), KEY_TILE * 128);
-        constexpr uint64_t STAGE_STEP = STAGE_BYTES >> 4;
-        auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T over d in steps of 16, into the S buffer of i's parity
-            const int s = i % KV_STAGES;
-            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) return false;
+        const uint64_t q_desc = desc_k_major(q_smem), k_desc0 = desc_k_major(k_smem);
+        const uint64_t v_desc0 = desc_mn_major(v_smem, KEY_TILE * 128);
+        constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
+        auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T over d in steps of 16, into the S buffer of i's parity; K(i) has landed
             if (i >= 2 && !mbar_wait(s_free + 8 * (i & 1), ((i >> 1) - 1) & 1, abort_flag, p.status, 118)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t kd = k_desc0 + s * STAGE_STEP;
+            const uint64_t kd = k_desc0 + (i % K_SLOTS) * K_STEP;
 #pragma unroll
             for (int k = 0; k < D / 16; k++) {
                 const uint64_t q_off = ((k / 4) * (Q_ROWS * 128) + (k % 4) * 32) >> 4, k_off = ((k / 4) * (KEY_TILE * 128) + (k % 4) * 32) >> 4;
@@ -240,14 +251,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             return true;
         };
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 112);
-        if (ok && num_tiles > 0) ok = issue_scores(0);
+        if (ok) ok = issue_scores(0);
         for (int i = 0; ok && i < num_tiles; i++) {
             const int s = i % KV_STAGES;
+            // K(i + 1) and V(i) have landed
+            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
             if (i + 1 < num_tiles && !(ok = issue_scores(i + 1))) break;
             // O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
             if (!mbar_wait(p_full + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 114)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t pd = p_desc0 + s * STAGE_STEP, vd = v_desc0 + s * STAGE_STEP;
+            const uint64_t pd = k_desc0 + (i % K_SLOTS) * K_STEP, vd = v_desc0 + s * V_STEP;
 #pragma unroll
             for (int k = 0; k < KEY_TILE / 16; k++)
                 umma_bf16(tmem_base + O_COL, pd + ((k * 32) >> 4), vd + ((k * (16 * 128)) >> 4), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
@@ -309,7 +322,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // a row that has seen no key yet (m = -inf) has only masked scores: -inf * scale + 0 = -inf, exp2 gives 0
             const float neg_m = m == -INFINITY ? 0.f : -m;
             // P as bfloat16 into the swizzled K-major tile: row r, 16-byte chunk c8 at chunk (c8 ^ (r & 7))
-            const uint32_t p_dst = p_of(i % KV_STAGES);
+            const uint32_t p_dst = k_of(i);
 #pragma unroll
             for (int c8 = 0; c8 < KEY_TILE / 8; c8++) {
                 uint32_t packed[4];
@@ -328,12 +341,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             l += psum;
             // rows of V at and past the sequence's length were never written by this sequence: their
-            // weight is 0, but 0 x (whatever bits lie there) must stay 0 (K and V of the tile have
-            // landed: the scores came from them)
+            // weight is 0, but 0 x (whatever bits lie there) must stay 0.  Only a sequence's last tile has
+            // such rows; V of the tile must have landed before they are overwritten.
+            if (key0 + KEY_TILE > kv_len &&
+                !(ok = mbar_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1, abort_flag, p.status, 110))) break;
             if (r < KEY_TILE && key0 + r >= kv_len) {
 #pragma unroll
                 for (int x = 0; x < D_BOXES; x++) {
-                    const uint32_t rowp = v_of(i % KV_STAGES) + x * (KEY_TILE * 128) + r * 128;
+                    const uint32_t rowp = v_of(i) + x * (KEY_TILE * 128) + r * 128;
 #pragma unroll
                     for (int c = 0; c < 8; c++)
                         asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowp + c * 16), "r"(0) : "memory");
@@ -405,12 +420,14 @@ template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid,
            cudaStream_t stream) {
     constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
-    constexpr size_t smem = Q_ROWS * D * 2 + KV_STAGES * (2 * kv_tile + (kv_tile >= p_tile ? 0 : p_tile)) + 1024;
+    constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (kv_tile >= p_tile ? kv_tile : p_tile) + KV_STAGES * kv_tile +
+                            (2 * KV_STAGES + 8) * 8 + 8;   // tiles, barriers, two words
     auto kernel = attention_prefill_tc_kernel<D>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { hymt2_set_error("attention_prefill_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // two CTAs an SM
         configured = true;
     }
     kernel<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p);
