@@ -142,8 +142,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // and two CTAs of 112 KB fit an SM.  Barriers and the two words lie behind the tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + BARS_OFFSET);
-    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 8) * 8);
-    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 8) * 8 + 4);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 6) * 8);
+    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 6) * 8 + 4);
 
     // The last query tiles of a prompt walk the most keys: CTAs are numbered by falling query tile, so the long
     // ones start first and the short ones fill the gaps.  When all CTAs fit on the SMs at once (two each), the
@@ -174,7 +174,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * KV_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
     const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
-    const uint32_t s_full = q_full + 16, s_free = q_full + 32, p_full = q_full + 48;   // two of each: even and odd tiles
+    const uint32_t s_full = q_full + 16, p_full = q_full + 32;   // two of each: even and odd tiles
     volatile int* abort_flag = &abort_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -187,7 +187,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(o_full, 1);
         for (int t = 0; t < 2; t++) {
             mbar_init(s_full + 8 * t, 1);
-            mbar_init(s_free + 8 * t, 128);
             mbar_init(p_full + 8 * t, 128);
         }
         abort_s = 0;
@@ -238,9 +237,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint64_t q_desc = desc_k_major(q_smem), k_desc0 = desc_k_major(k_smem);
         const uint64_t v_desc0 = desc_mn_major(v_smem, KEY_TILE * 128);
         constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
-        auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T over d in steps of 16, into the S buffer of i's parity; K(i) has landed
-            if (i >= 2 && !mbar_wait(s_free + 8 * (i & 1), ((i >> 1) - 1) & 1, abort_flag, p.status, 118)) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // S(i) = Q K(i)^T over d in steps of 16, into the S buffer of i's parity.  K(i) has landed; the buffer's
+        // last scores, those of tile i - 2, have been read: the softmax warps read a tile's scores before they
+        // announce its P, and P(i - 2) was waited for before P·V of tile i - 2.
+        auto issue_scores = [&](int i) {
             const uint64_t kd = k_desc0 + (i % K_SLOTS) * K_STEP;
 #pragma unroll
             for (int k = 0; k < D / 16; k++) {
@@ -248,15 +248,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 umma_bf16(tmem_base + S_COL + 64 * (i & 1), q_desc + q_off, kd + k_off, IDESC_S, k > 0 ? 1u : 0u);
             }
             umma_commit(s_full + 8 * (i & 1));
-            return true;
         };
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 112);
-        if (ok) ok = issue_scores(0);
+        if (ok) issue_scores(0);
         for (int i = 0; ok && i < num_tiles; i++) {
             const int s = i % KV_STAGES;
             // K(i + 1) and V(i) have landed
             if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
-            if (i + 1 < num_tiles && !(ok = issue_scores(i + 1))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (i + 1 < num_tiles) issue_scores(i + 1);
             // O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
             if (!mbar_wait(p_full + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 114)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -283,8 +283,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float s[KEY_TILE];
             tmem_load32(lane_addr + S_COL + 64 * (i & 1), s);
             tmem_load32(lane_addr + S_COL + 64 * (i & 1) + 32, s + 32);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(s_free + 8 * (i & 1));   // the scores are in registers: this buffer may take the tile after next
             // s stays unscaled: the scale (> 0) goes into the exponent's multiply-add; most tiles lie wholly
             // inside the row's visible range and need no mask
             float tile_max = -INFINITY;
@@ -421,7 +419,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            cudaStream_t stream) {
     constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
     constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (kv_tile >= p_tile ? kv_tile : p_tile) + KV_STAGES * kv_tile +
-                            (2 * KV_STAGES + 8) * 8 + 8;   // tiles, barriers, two words
+                            (2 * KV_STAGES + 6) * 8 + 8;   // tiles, barriers, two words
     auto kernel = attention_prefill_tc_kernel<D>;
     static bool configured = false;
     if (!configured) {
