@@ -29,7 +29,7 @@
 
 namespace {
 
-constexpr int Q_ROWS = 128, KEY_TILE = 64, NUM_THREADS = 192, KV_STAGES = 2, K_SLOTS = 3;
+constexpr int Q_ROWS = 128, KEY_TILE = 64, NUM_THREADS = 256, KV_STAGES = 2, K_SLOTS = 3;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct PrefillParams {
@@ -110,6 +110,30 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void tmem_store32(uint32_t taddr, const float* v) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
     asm volatile(
@@ -142,8 +166,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // and two CTAs of 112 KB fit an SM.  Barriers and the two words lie behind the tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + BARS_OFFSET);
-    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 6) * 8);
-    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 6) * 8 + 4);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 7) * 8);
+    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 7) * 8 + 4);
 
     // The last query tiles of a prompt walk the most keys: CTAs are numbered by falling query tile, so the long
     // ones start first and the short ones fill the gaps.  When all CTAs fit on the SMs at once (two each), the
@@ -174,7 +198,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * KV_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
     const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
-    const uint32_t s_full = q_full + 16, p_full = q_full + 32;   // two of each: even and odd tiles
+    const uint32_t s_full = q_full + 24, p_full = q_full + 40;   // two of each, and of o_full: even and odd tiles
     volatile int* abort_flag = &abort_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -184,8 +208,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(kv_empty + 8 * s, 1);
         }
         mbar_init(q_full, 1);
-        mbar_init(o_full, 1);
         for (int t = 0; t < 2; t++) {
+            mbar_init(o_full + 8 * t, 1);
             mbar_init(s_full + 8 * t, 1);
             mbar_init(p_full + 8 * t, 128);
         }
@@ -231,15 +255,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1); t++) {}
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer: S of the next tile goes out before P·V of this one -------------------------
+        // ---- first MMA issuer: the scores, one tile ahead of the softmax warps ---------------------------
+        // Two threads issue, each with a wait or two and a dozen instructions a tile: one thread doing both was
+        // the slowest link of the chain.
         // The descriptors of slot 0 once; per instruction only constants are added (the address sits in the
         // low bits in units of 16 bytes, and shared memory is too small to carry out of them).
         const uint64_t q_desc = desc_k_major(q_smem), k_desc0 = desc_k_major(k_smem);
-        const uint64_t v_desc0 = desc_mn_major(v_smem, KEY_TILE * 128);
-        constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
+        constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4;
         // S(i) = Q K(i)^T over d in steps of 16, into the S buffer of i's parity.  K(i) has landed; the buffer's
         // last scores, those of tile i - 2, have been read: the softmax warps read a tile's scores before they
-        // announce its P, and P(i - 2) was waited for before P·V of tile i - 2.
+        // announce its P, and P(i - 2) is waited for first.
         auto issue_scores = [&](int i) {
             const uint64_t kd = k_desc0 + (i % K_SLOTS) * K_STEP;
 #pragma unroll
@@ -250,24 +275,38 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             umma_commit(s_full + 8 * (i & 1));
         };
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 112);
-        if (ok) issue_scores(0);
-        for (int i = 0; ok && i < num_tiles; i++) {
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_scores(0);
+        }
+        for (int i = 0; ok && i + 1 < num_tiles; i++) {
+            // K(i + 1) has landed (with V(i))
+            if (!mbar_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
+            // P·V of tile i - 2 is through.  The softmax warps, who wait for P·V of the tile before theirs only when a
+            // maximum rose, then never meet a barrier more than one phase behind (a parity cannot tell two apart).
+            if (i >= 2 && !mbar_wait(o_full + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, p.status, 108)) break;
+            // the scores of tile i - 1 have been read: their buffer takes those of tile i + 1
+            if (i >= 1 && !mbar_wait(p_full + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.status, 118)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_scores(i + 1);
+        }
+    } else if (warp == 2 && lane == 0) {
+        // ---- second MMA issuer: O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
+        const uint64_t p_desc0 = desc_k_major(k_smem), v_desc0 = desc_mn_major(v_smem, KEY_TILE * 128);
+        constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
+        for (int i = 0; i < num_tiles; i++) {
             const int s = i % KV_STAGES;
-            // K(i + 1) and V(i) have landed
-            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i + 1 < num_tiles) issue_scores(i + 1);
-            // O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
             if (!mbar_wait(p_full + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 114)) break;
+            if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 109)) break;   // V(i) has landed
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t pd = k_desc0 + (i % K_SLOTS) * K_STEP, vd = v_desc0 + s * V_STEP;
+            const uint64_t pd = p_desc0 + (i % K_SLOTS) * K_STEP, vd = v_desc0 + s * V_STEP;
 #pragma unroll
             for (int k = 0; k < KEY_TILE / 16; k++)
                 umma_bf16(tmem_base + O_COL, pd + ((k * 32) >> 4), vd + ((k * (16 * 128)) >> 4), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
             umma_commit(kv_empty + 8 * s);
-            umma_commit(o_full);
+            umma_commit(o_full + 8 * (i & 1));
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 4) {
         // ---- softmax: one thread per query row; O stays in TMEM ------------------------------------
         const int quarter = warp & 3, r = quarter * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -304,15 +343,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (raise) m = tile_max;
             if (i > 0 && __any_sync(0xffffffffu, raise)) {
                 // the O of the tiles so far is complete, then every row of the warp scales its own O
-                if (!(ok = mbar_wait(o_full, (i - 1) & 1, abort_flag, p.status, 116))) break;
+                if (!(ok = mbar_wait(o_full + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.status, 116))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    float o[32];
-                    tmem_load32(lane_addr + O_COL + c, o);
+                for (int c = 0; c < D; c += 16) {   // 16 columns at a time: the row's 64 scores are live in registers
+                    float o[16];
+                    tmem_load16(lane_addr + O_COL + c, o);
 #pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] *= corr;
-                    tmem_store32(lane_addr + O_COL + c, o);
+                    for (int j = 0; j < 16; j++) o[j] *= corr;
+                    tmem_store16(lane_addr + O_COL + c, o);
                 }
             }
             l *= corr;
@@ -326,11 +365,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 uint32_t packed[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const float p0 = exp2f(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, neg_m));
-                    const float p1 = exp2f(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, neg_m));
+                    // the special-function unit is this kernel's scarcest resource: one instruction an element
+                    // (exp2f brings a range fix-up of several more; -inf gives 0 either way, and P has 8 bits)
+                    const float p0 = ex2_approx(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, neg_m));
+                    const float p1 = ex2_approx(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, neg_m));
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    // the sum uses the rounded values that the tensor core will multiply with
-                    psum += __low2float(h) + __high2float(h);
+                    psum += p0 + p1;
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 const uint32_t dst = p_dst + r * 128 + ((c8 ^ (r & 7)) << 4);
@@ -356,7 +396,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full + 8 * (i & 1));
         }
-        if (ok) ok = mbar_wait(o_full, (num_tiles - 1) & 1, abort_flag, p.status, 117);
+        if (ok) ok = mbar_wait(o_full + 8 * ((num_tiles - 1) & 1), ((num_tiles - 1) >> 1) & 1, abort_flag, p.status, 117);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -419,7 +459,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            cudaStream_t stream) {
     constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
     constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (kv_tile >= p_tile ? kv_tile : p_tile) + KV_STAGES * kv_tile +
-                            (2 * KV_STAGES + 6) * 8 + 8;   // tiles, barriers, two words
+                            (2 * KV_STAGES + 7) * 8 + 8;   // tiles, barriers, two words
     auto kernel = attention_prefill_tc_kernel<D>;
     static bool configured = false;
     if (!configured) {
