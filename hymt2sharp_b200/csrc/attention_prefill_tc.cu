@@ -324,19 +324,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_load32(lane_addr + S_COL + 64 * (i & 1) + 32, s + 32);
             // s stays unscaled: the scale (> 0) goes into the exponent's multiply-add; most tiles lie wholly
             // inside the row's visible range and need no mask
-            float tile_max = -INFINITY;
+            // four running maxima (and four sums below): one chain of 64 dependent operations would leave
+            // the thread waiting on each result, and only two such warps share a scheduler
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (row_ok && key0 >= lo && key0 + KEY_TILE - 1 <= pos) {
 #pragma unroll
-                for (int c = 0; c < KEY_TILE; c++) tile_max = fmaxf(tile_max, s[c]);
+                for (int c = 0; c < KEY_TILE; c++) mx[c & 3] = fmaxf(mx[c & 3], s[c]);
             } else {
 #pragma unroll
                 for (int c = 0; c < KEY_TILE; c++) {
                     const int key = key0 + c;
                     s[c] = (row_ok && key >= lo && key <= pos) ? s[c] : -INFINITY;
-                    tile_max = fmaxf(tile_max, s[c]);
+                    mx[c & 3] = fmaxf(mx[c & 3], s[c]);
                 }
             }
-            tile_max *= p.scale_log2;
+            float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
             // raise the row's maximum only when it grows by more than 2^8 (or at its first visible key)
             const bool raise = tile_max > m + 8.0f || (m == -INFINITY && tile_max > -INFINITY);
             const float corr = raise ? exp2f(m - tile_max) : 1.f;   // m = -inf: 0
@@ -355,7 +357,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             l *= corr;
-            float psum = 0.f;
+            float psum[4] = {0.f, 0.f, 0.f, 0.f};
             // a row that has seen no key yet (m = -inf) has only masked scores: -inf * scale + 0 = -inf, exp2 gives 0
             const float neg_m = m == -INFINITY ? 0.f : -m;
             // P as bfloat16 into the swizzled K-major tile: row r, 16-byte chunk c8 at chunk (c8 ^ (r & 7))
@@ -370,14 +372,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const float p0 = ex2_approx(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, neg_m));
                     const float p1 = ex2_approx(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, neg_m));
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    psum += p0 + p1;
+                    psum[j] += p0 + p1;
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 const uint32_t dst = p_dst + r * 128 + ((c8 ^ (r & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
                              "r"(packed[2]), "r"(packed[3]) : "memory");
             }
-            l += psum;
+            l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
             // rows of V at and past the sequence's length were never written by this sequence: their
             // weight is 0, but 0 x (whatever bits lie there) must stay 0.  Only a sequence's last tile has
             // such rows; V of the tile must have landed before they are overwritten.
