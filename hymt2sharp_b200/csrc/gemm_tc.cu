@@ -58,6 +58,7 @@ struct RopeEpilogue {
     const int* token_pos;      // [T] position of each token
     const int* slot_ids;       // [B] cache slot of each batch row, -1: padding
     const float* inv_freq;     // [rope_dim / 2], null when rope_dim == 0
+    const float* angles;       // [T][rope_dim / 2] (cos, sin) of position * inv_freq: where tokens are the accumulator's rows
     const void* q_gain;        // [128] or null
     const void* k_gain;
     int table_stride, block_tokens, nh, nkv, rope_dim, write_kv, gain_bf16;
@@ -170,8 +171,81 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const float* v) {   // dst is 32-byte aligned
+    __nv_bfloat162 h[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) h[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+    reinterpret_cast<uint4*>(dst)[0] = reinterpret_cast<const uint4*>(h)[0];
+    reinterpret_cast<uint4*>(dst)[1] = reinterpret_cast<const uint4*>(h)[1];
+}
+
+// The EPI_ROPE_KV epilogue where tokens are the accumulator's rows (many tokens): this thread owns token t and finds one
+// head's 128 projected values in its lane of tensor memory from `head_at` on.  It does what the rotation kernel does
+// (src/HyMT2Sharp/Ops.cs:98-195): the values as the projection would have stored them (bfloat16), rotate-half rotation
+// over all 128 (rope_dim 128) or none (0), RMSNorm over the head where the model has it, then q to its tensor, k and v
+// to the token's row of the paged cache.  Every thread of the warp comes along (the tensor-memory accesses are
+// warp-wide); `active` says whether the token exists.
+__device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int head, bool active, const RopeEpilogue& rp) {
+    const bool is_q = head < rp.nh, is_k = !is_q && head < rp.nh + rp.nkv;
+    int pos = 0, slot = -1;
+    if (active) {
+        pos = rp.token_pos[t];
+        slot = rp.slot_ids[rp.token_seq[t]];
+    }
+    __nv_bfloat16* dst = nullptr;                      // where this head's 128 values go; null: nowhere
+    if (is_q) {
+        if (active) dst = rp.q_out + ((size_t)t * rp.nh + head) * TILE_M;
+    } else if (rp.write_kv && slot >= 0) {
+        const int block = rp.block_table[(size_t)slot * rp.table_stride + pos / rp.block_tokens];
+        const int kvh = is_k ? head - rp.nh : head - rp.nh - rp.nkv;
+        dst = (is_k ? rp.k_cache : rp.v_cache) + (((size_t)block * rp.nkv + kvh) * rp.block_tokens + (pos % rp.block_tokens)) * TILE_M;
+    }
+    const void* gain = is_q ? rp.q_gain : is_k ? rp.k_gain : nullptr;
+    const bool rotate = (is_q || is_k) && rp.rope_dim == TILE_M;
+    constexpr int HALF = TILE_M / 2;
+    // the head's 128 values stay in registers between the rotation and the norm (the kernels that come here have
+    // one CTA per SM or few registers otherwise); every index below is known when the loops are unrolled
+    float v[TILE_M];
+#pragma unroll
+    for (int c = 0; c < TILE_M; c += 16) tmem_load<16>(head_at + c, v + c);
+#pragma unroll
+    for (int i = 0; i < TILE_M; i++) v[i] = bf16_round(v[i]);      // what the projection would have stored
+    if (rotate) {
+        const float4* angles = reinterpret_cast<const float4*>(rp.angles) + (size_t)(active ? t : 0) * (HALF / 2);
+#pragma unroll
+        for (int c = 0; c < HALF; c += 8) {
+            float4 a[4];                                   // (cos, sin) of 8 angles
+#pragma unroll
+            for (int j = 0; j < 4; j++) a[j] = __ldg(angles + c / 2 + j);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float x = v[c + j], y = v[HALF + c + j];
+                const float cs = j & 1 ? a[j / 2].z : a[j / 2].x, sn = j & 1 ? a[j / 2].w : a[j / 2].y;
+                v[c + j] = x * cs - y * sn;
+                v[HALF + c + j] = x * sn + y * cs;
+            }
+        }
+    }
+    if (gain) {
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < TILE_M; i++) ss[i & 3] += v[i] * v[i];
+        const float scale = 1.0f / sqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) / (float)TILE_M + rp.eps);
+#pragma unroll
+        for (int i = 0; i < TILE_M; i++) {
+            const float gv = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[i]) : ((const float*)gain)[i];
+            v[i] = v[i] * scale * gv;
+        }
+    }
+    if (dst) {
+#pragma unroll
+        for (int c = 0; c < TILE_M; c += 16) store_bf16x16(dst + c, v + c);
+    }
+}
+
 template <int BN, bool SWAPPED, int EPI, typename TC>
-__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), 1)
+__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), (!SWAPPED && EPI == EPI_ROPE_KV) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
     constexpr int NUM_ACC = (SWAPPED && EPI == EPI_SWIGLU) ? 2 : 1;   // accumulators = A tiles per stage
     constexpr bool SPLIT_B = !SWAPPED && EPI == EPI_SWIGLU;           // B tile = gate rows, then up rows
@@ -403,7 +477,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         };
 
-        if (!SWAPPED || p.splits == 1) {   // K is only split in the swapped orientation
+        if (!SWAPPED && EPI == EPI_ROPE_KV) {   // the tile is one head of 128 tokens, this thread's row a token
+            if (ok) rope_head_from_tmem(lane_addr, a_row0 + row, b_row0 / TILE_M, a_row0 + row < p.T, p.rope);
+        } else if (!SWAPPED || p.splits == 1) {   // K is only split in the swapped orientation
             if (ok) {
                 for (int c = 0; c < OUT_COLS; c += CH) {
                     float g[CH], u[CH];
@@ -597,7 +673,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
-    pdl_launch_dependents();
+    if (EPI != EPI_ROPE_KV) pdl_launch_dependents();
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
@@ -683,6 +759,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         // ---- epilogue ---------------------------------------------------------------------------------
         const int quarter = warp & 3, row = quarter * 32 + lane;
         pdl_wait();   // C may still be in use by the kernel before
+        // the kernel after this one may read the cache before its own wait; it must not start while the kernel
+        // before this one still runs: wait first, release after
+        if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();
         TC* C = (TC*)p.C;
         int j = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, j++) {
@@ -692,6 +771,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
             const int m = a_row0 + row;
+            if constexpr (EPI == EPI_ROPE_KV) {
+                // the tile holds BN / 128 heads of 128 tokens: this thread's token, head after head
+                const int heads = p.rope.nh + 2 * p.rope.nkv;
+#pragma unroll 1
+                for (int h = 0; h < BN / TILE_M; h++) {
+                    const int head = b_row0 / TILE_M + h;
+                    if (head < heads) rope_head_from_tmem(lane_addr + h * TILE_M, m, head, m < p.T, p.rope);
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < OUT_COLS; c += 16) {
                 float g[16], u[16];
@@ -977,14 +1065,20 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     return dispatch_epilogue<128, false>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
 }
 
-// Whether hymt2_gemm_tc_rope_kv takes a projection of T tokens onto N = (nh + 2 nkv) * 128 features over K: it needs
-// the split-K cluster plan, whose CTAs each hold whole heads of a few tokens.
-HYMT2_API int hymt2_gemm_tc_rope_kv_supported(int T, int N, int K) {
-    if (T <= 0 || T > 64 || N <= 0 || N % TILE_M || K <= 0 || K % 8) return 0;
+// Whether hymt2_gemm_tc_rope_kv takes a projection of T tokens onto N = (nh + 2 nkv) * 128 features over K.  A few tokens
+// need the split-K cluster plan, whose CTAs each hold whole heads of a few tokens, and take any even rope_dim; more than
+// 128 tokens are an accumulator's rows, whose threads rotate all of a head or nothing.
+HYMT2_API int hymt2_gemm_tc_rope_kv_supported(int T, int N, int K, int rope_dim) {
+    if (T <= 0 || N <= 0 || N % TILE_M || K <= 0 || K % 8) return 0;
     Plan pl;
     make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl);
-    return (pl.swapped && pl.cluster && pl.bn <= 64) ? 1 : 0;
+    if (pl.swapped) return (T <= 64 && pl.cluster && pl.bn <= 64) ? 1 : 0;
+    return (rope_dim == 0 || rope_dim == TILE_M) ? 1 : 0;   // tokens as rows: a thread rotates its token's whole head
 }
+
+// Whether hymt2_gemm_tc_rope_kv wants `angles`, the table that hymt2_rope_angles makes of the step's positions: where
+// tokens are the accumulator's rows and are rotated.
+HYMT2_API int hymt2_gemm_tc_rope_kv_wants_angles(int T, int rope_dim) { return (T > TILE_M && rope_dim > 0) ? 1 : 0; }
 
 // The fused q/k/v projection of a few tokens with everything that follows it up to the cache: q_out[T, nh*128] gets the
 // rotated (and normed) queries, the cache planes get the rotated (and normed) keys and the values of every token whose
@@ -992,8 +1086,8 @@ HYMT2_API int hymt2_gemm_tc_rope_kv_supported(int T, int N, int K) {
 HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, long lda, long ldw, void* q_out, void* k_cache,
                                     void* v_cache, const int* block_table, int table_stride, int block_tokens,
                                     const int* token_seq, const int* token_pos, const int* slot_ids, const float* inv_freq,
-                                    int rope_dim, const void* q_gain, const void* k_gain, int gain_dtype, float eps, int nh,
-                                    int nkv, int write_kv, int* status, cudaStream_t stream) {
+                                    const float* angles, int rope_dim, const void* q_gain, const void* k_gain, int gain_dtype,
+                                    float eps, int nh, int nkv, int write_kv, int* status, cudaStream_t stream) {
     if (T == 0) return HYMT2_OK;
     const int N = (nh + 2 * nkv) * TILE_M;
     HYMT2_REQUIRE(T > 0 && nh > 0 && nkv > 0 && K > 0, "gemm_tc_rope_kv: bad sizes T=%d nh=%d nkv=%d K=%d", T, nh, nkv, K);
@@ -1005,16 +1099,24 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
     HYMT2_REQUIRE(!q_gain || gain_dtype == HYMT2_BF16 || gain_dtype == HYMT2_F32, "gemm_tc_rope_kv: gains must be bfloat16 or float32");
     HYMT2_REQUIRE(block_tokens > 0 && q_out && status, "gemm_tc_rope_kv: missing arguments");
     HYMT2_REQUIRE(!write_kv || (k_cache && v_cache), "gemm_tc_rope_kv: the cache planes are needed to write keys and values");
-    HYMT2_REQUIRE(hymt2_gemm_tc_rope_kv_supported(T, N, K), "gemm_tc_rope_kv: T=%d N=%d K=%d does not get the cluster plan", T, N, K);
+    HYMT2_REQUIRE(hymt2_gemm_tc_rope_kv_supported(T, N, K, rope_dim), "gemm_tc_rope_kv: T=%d N=%d K=%d rope_dim=%d is not taken", T, N, K, rope_dim);
     Plan pl;
     make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl);
     CUtensorMap ma, mb;
-    HYMT2_REQUIRE(make_map(&ma, W, N, K, ldw, TILE_M) && make_map(&mb, X, T, K, lda, pl.bn),
-                  "gemm_tc_rope_kv: cuTensorMapEncodeTiled refused the operands");
+    const bool maps = pl.swapped ? make_map(&ma, W, N, K, ldw, TILE_M) && make_map(&mb, X, T, K, lda, pl.bn)
+                                 : make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, N, K, ldw, pl.bn);
+    HYMT2_REQUIRE(maps, "gemm_tc_rope_kv: cuTensorMapEncodeTiled refused the operands");
+    HYMT2_REQUIRE(!hymt2_gemm_tc_rope_kv_wants_angles(T, rope_dim) || (angles && (uintptr_t)angles % 16 == 0),
+                  "gemm_tc_rope_kv: %d tokens are the accumulator's rows and need the table of their angles (hymt2_rope_angles)", T);
     RopeEpilogue rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, token_seq, token_pos,
-                      slot_ids, inv_freq, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
+                      slot_ids, inv_freq, angles, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
                       gain_dtype == HYMT2_BF16 ? 1 : 0, eps};
-    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, 1, nullptr, nullptr, status, rope};
+    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, nullptr, nullptr, status, rope};
+    if (pl.persistent) {
+        const int ctas = pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count;
+        return launch_persistent_one<PERSISTENT_BN, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);
+    }
+    if (!pl.swapped) return launch<128, false, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
     switch (pl.bn) {
         case 16: return launch<16, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
         case 32: return launch<32, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);

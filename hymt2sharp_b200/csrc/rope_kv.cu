@@ -163,7 +163,32 @@ rope_kv_vec_kernel(RopeKvParams p, int tokens) {
     *reinterpret_cast<Vec*>(dst) = outv;
 }
 
+// out[t][i] = (cos, sin) of (float)pos[t] * inv_freq[i]: the angles of a step's tokens, the same float32 product and
+// the same functions as in the kernels above, for the epilogue of a projection whose threads own whole tokens and
+// would otherwise compute every angle once per head and layer.
+__global__ void __launch_bounds__(128)
+rope_angles_kernel(float2* out, const int* token_pos, const float* inv_freq, int tokens, int half) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)tokens * half) return;
+    float sn, cs;
+    sincosf((float)token_pos[i / half] * inv_freq[i % half], &sn, &cs);
+    out[i] = make_float2(cs, sn);
+}
+
 }  // namespace
+
+HYMT2_API int hymt2_rope_angles(float* out, const int* token_pos, const float* inv_freq, int tokens, int half,
+                                cudaStream_t stream) {
+    if (tokens == 0 || half == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && half > 0 && out && token_pos && inv_freq, "rope_angles: bad arguments");
+    HYMT2_REQUIRE((uintptr_t)out % 16 == 0, "rope_angles: the table must be 16-byte aligned");
+    const long items = (long)tokens * half;
+    launch_pdl(rope_angles_kernel, dim3((unsigned)((items + 127) / 128)), dim3(128), 0, stream, (float2*)out, token_pos,
+               inv_freq, tokens, half);
+    return hymt2_check_launch("rope_angles");
+}
 
 HYMT2_API int hymt2_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache, int dtype,
                             const int* block_table, int table_stride, int block_tokens,

@@ -227,9 +227,10 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, 
                                 c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream()), "gemm_tc")
 
 
-def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: int, d: int, cache_dtype) -> bool:
-    """Whether the fused projection + rotation + cache append takes these operands: bfloat16, head_dim 128,
-    few enough tokens that the product is cut over K among clusters."""
+def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: int, d: int, cache_dtype, rope_dim: int) -> bool:
+    """Whether the fused projection + rotation + cache append takes these operands: bfloat16, head_dim 128, and
+    either few enough tokens that the product is cut over K among clusters (any even rope_dim), or more than 128
+    tokens, which are the accumulator's rows (rope_dim 0 or 128)."""
     if d != 128 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or cache_dtype != torch.bfloat16:
         return False
     if x.dim() != 2 or w.dim() != 2 or x.stride(1) != 1 or w.stride(1) != 1 or w.shape != ((nh + 2 * nkv) * d, x.shape[1]):
@@ -237,20 +238,29 @@ def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: in
     K = x.shape[1]
     if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         return False
-    return bool(_lib().hymt2_gemm_tc_rope_kv_supported(c_int(x.shape[0]), c_int(w.shape[0]), c_int(K)))
+    return bool(_lib().hymt2_gemm_tc_rope_kv_supported(c_int(x.shape[0]), c_int(w.shape[0]), c_int(K), c_int(rope_dim)))
 
 
 def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None,
                     v_plane: torch.Tensor | None, block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor,
                     token_pos: torch.Tensor, slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int,
                     q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float, nh: int, nkv: int,
-                    status: torch.Tensor) -> None:
+                    status: torch.Tensor, angles: torch.Tensor | None = None) -> None:
     """q_out[T, nh*128] = rotation and per-head norm of the query part of x @ w^T; the key part, rotated and
     normed, and the value part go to the rows of the cache planes that (slot, position) of every token name
-    (k_plane None: nothing is written).  One tcgen05 kernel; head_dim 128; see rope_kv for the arguments."""
+    (k_plane None: nothing is written).  One tcgen05 kernel; head_dim 128; see rope_kv for the arguments.
+    `angles`: what rope_angles(token_pos, inv_freq) gave, where gemm_tc_rope_kv_wants_angles says so."""
     d = 128
     T = x.shape[0]
-    if not gemm_tc_rope_kv_supported(x, w, nh, nkv, d, (k_plane if k_plane is not None else q_out).dtype):
+    if gemm_tc_rope_kv_wants_angles(T, rope_dim):
+        if angles is None:
+            raise KernelError(f"gemm_tc_rope_kv: {T} tokens need the table of their angles (rope_angles)")
+        _need(angles, "angles", torch.float32, 3)
+        if angles.shape != (T, rope_dim // 2, 2) or not angles.is_contiguous():
+            raise KernelError(f"gemm_tc_rope_kv: angles is {tuple(angles.shape)}, expected {(T, rope_dim // 2, 2)}")
+    else:
+        angles = None
+    if not gemm_tc_rope_kv_supported(x, w, nh, nkv, d, (k_plane if k_plane is not None else q_out).dtype, rope_dim):
         raise KernelError(f"gemm_tc_rope_kv: operands x {tuple(x.shape)} {x.dtype} w {tuple(w.shape)} {w.dtype} are not taken")
     _need(q_out, "q_out", torch.bfloat16, 2)
     if q_out.shape != (T, nh * d) or not q_out.is_contiguous():
@@ -277,9 +287,26 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
     _check(_lib().hymt2_gemm_tc_rope_kv(_ptr(x), _ptr(w), c_int(T), c_int(x.shape[1]), c_long(x.stride(0)), c_long(w.stride(0)),
                                         _ptr(q_out), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
                                         c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq), _ptr(token_pos),
-                                        _ptr(slot_ids), _ptr(inv_freq), c_int(rope_dim), _ptr(q_gain), _ptr(k_gain),
+                                        _ptr(slot_ids), _ptr(inv_freq), _ptr(angles), c_int(rope_dim), _ptr(q_gain), _ptr(k_gain),
                                         c_int(gain_dtype), c_float(eps), c_int(nh), c_int(nkv), c_int(1 if write else 0),
                                         _ptr(status), _stream()), "gemm_tc_rope_kv")
+
+
+def gemm_tc_rope_kv_wants_angles(tokens: int, rope_dim: int) -> bool:
+    """Whether gemm_tc_rope_kv of this many tokens wants the table of their angles: where tokens are the
+    accumulator's rows, a thread owns a whole token and would compute every angle once per head."""
+    return bool(_lib().hymt2_gemm_tc_rope_kv_wants_angles(c_int(tokens), c_int(rope_dim)))
+
+
+def rope_angles(token_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[T, rope_dim/2, 2] float32: (cos, sin) of float32(position) * inv_freq, the product and the functions of
+    the rotation kernels; once per step and frequency table, for every layer that uses that table."""
+    _need(token_pos, "token_pos", torch.int32, 1)
+    _need(inv_freq, "inv_freq", torch.float32, 1)
+    out = torch.empty((token_pos.shape[0], inv_freq.shape[0], 2), dtype=torch.float32, device=token_pos.device)
+    _check(_lib().hymt2_rope_angles(_ptr(out), _ptr(token_pos), _ptr(inv_freq), c_int(token_pos.shape[0]),
+                                    c_int(inv_freq.shape[0]), _stream()), "rope_angles")
+    return out
 
 
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,

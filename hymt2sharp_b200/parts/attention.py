@@ -80,13 +80,21 @@ class GQAAttention:
         k_plane, v_plane = ctx.cache.plane(slot.group, slot.plane)
         block_table = ctx.cache.tables[slot.group]
         fused = (table is not None or self.position is None) and x.shape[0] == T and \
-            ops.gemm_tc_rope_kv_supported(x, self.qkv.weight, nh, nkv, d, k_plane.dtype)
+            ops.gemm_tc_rope_kv_supported(x, self.qkv.weight, nh, nkv, d, k_plane.dtype, rope_dim)
         if fused:
-            # a few tokens: projection, rotation, norm and cache append are one kernel
+            # projection, rotation, norm and cache append are one kernel
             q = torch.empty((T, nh * d), dtype=x.dtype, device=x.device)
+            angles = None
+            if ops.gemm_tc_rope_kv_wants_angles(T, rope_dim):
+                # a prompt's worth of tokens: their angles once per step, not once per head and layer
+                key = ("rotary angles", inv_freq.data_ptr())
+                angles = ctx.shared.get(key)
+                if angles is None:
+                    angles = ctx.shared[key] = ops.rope_angles(ctx.token_pos[:T], inv_freq)
             ops.gemm_tc_rope_kv(x, self.qkv.weight, q, k_plane if slot.writes else None, v_plane if slot.writes else None,
                                 block_table, ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids, inv_freq,
-                                rope_dim, self.q_gain, self.k_gain, self.eps, nh, nkv, ops.device_status(x.device))
+                                rope_dim, self.q_gain, self.k_gain, self.eps, nh, nkv, ops.device_status(x.device),
+                                angles=angles)
         else:
             qkv = self.qkv(x)
             if table is None and self.position is not None:

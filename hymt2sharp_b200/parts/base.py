@@ -99,6 +99,9 @@ class StepContext:
     # stream (or None); a part that leaves the memory idle towards its end may ask for them ahead of time
     # (kernels.ops.prefetch_beside)
     weights_ahead: torch.Tensor | None = None
+    # what parts worked out from the step's tokens and other parts of the same kind can use again, by key: the
+    # angles of a rotary table, say, are the same in every layer that rotates by that table
+    shared: dict = field(default_factory=dict)
 
     @property
     def decode(self) -> bool:

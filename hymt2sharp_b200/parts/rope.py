@@ -18,6 +18,9 @@ import torch
 from .base import register_part
 
 
+_TABLES: dict = {}   # (device, the frequencies' bytes) -> their tensor on the device
+
+
 class NeoXRotary:
     def __init__(self, head_dim: int, rope_dim: int, base: float):
         if rope_dim % 2 or rope_dim > head_dim or rope_dim < 0:
@@ -36,7 +39,12 @@ class NeoXRotary:
         return {}
 
     def load(self, weights, device, dtype):
-        self.inv_freq = torch.from_numpy(self._host).to(device)
+        # layers with the same frequencies share one tensor on the device: what a step works out from a table
+        # (the angles of its tokens) then serves all of them
+        key = (str(torch.device(device)), self._host.tobytes())
+        if key not in _TABLES:
+            _TABLES[key] = torch.from_numpy(self._host).to(device)
+        self.inv_freq = _TABLES[key]
 
     def rotary_table(self):
         return self.inv_freq, self.rope_dim

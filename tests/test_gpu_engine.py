@@ -186,5 +186,5 @@ def test_the_fast_kernels_are_what_a_bfloat16_step_of_full_size_heads_runs(model
     assert ops.launches - before == 1 + 8 * layers + 2   # embedding; the layers; final norm and head
     q = torch.empty(1, 4 * 128, dtype=torch.bfloat16, device=DEV)
     assert ops.gemm_tc_rope_kv_supported(torch.empty(1, 256, dtype=torch.bfloat16, device=DEV),
-                                         eng.model.blocks[0].mixer.qkv.weight, 4, 2, 128, q.dtype)
+                                         eng.model.blocks[0].mixer.qkv.weight, 4, 2, 128, q.dtype, 128)
     eng.check()

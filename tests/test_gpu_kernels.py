@@ -258,7 +258,11 @@ def test_rope_qknorm_kv_append(dtype, nh, nkv, d, rope_dim, norm):
 
 @pytest.mark.parametrize("T, nh, nkv, K, rope_dim, norm, gain_dtype", [
     (11, 16, 4, 2048, 128, True, torch.bfloat16), (1, 4, 2, 1024, 128, False, torch.bfloat16),
-    (11, 6, 1, 1096, 48, True, torch.float32), (8, 16, 4, 2048, 0, True, torch.bfloat16), (40, 8, 2, 2048, 128, True, torch.bfloat16)])
+    (11, 6, 1, 1096, 48, True, torch.float32), (8, 16, 4, 2048, 0, True, torch.bfloat16), (40, 8, 2, 2048, 128, True, torch.bfloat16),
+    # more than 128 tokens: tokens are the accumulator's rows; tiles of one head (300, 700 tokens) and the
+    # persistent kernel's tiles of two heads (2,500 tokens; 4,800 with 7 heads: the last tile holds one)
+    (300, 8, 2, 512, 128, True, torch.bfloat16), (700, 3, 1, 264, 0, True, torch.float32), (300, 4, 2, 512, 128, False, torch.bfloat16),
+    (2500, 16, 4, 512, 128, True, torch.bfloat16), (4800, 5, 1, 256, 128, True, torch.float32), (2500, 16, 4, 256, 0, False, torch.bfloat16)])
 def test_projection_with_rotation_and_cache_append_in_one_kernel(T, nh, nkv, K, rope_dim, norm, gain_dtype):
     """The fused kernel (q/k/v projection, rotation, per-head norm, cache append; head_dim 128) against the
     kernels it replaces: the plain projection followed by rope_kv.  Positions across block borders, a padding
@@ -271,8 +275,14 @@ def test_projection_with_rotation_and_cache_append_in_one_kernel(T, nh, nkv, K, 
     base_seq = [0, 0, 0, 1, 1, 1, 2, 3, 4, 4, 5]
     if T <= 11:
         pos, seq = base_pos[:T], base_seq[:T]
-    else:
+    elif T <= 128:
         pos, seq = list(range(100, 100 + T)), [0] * T
+    else:
+        # several prompts in one step: two long ones, five tokens of a padding row, one that starts inside a block
+        a, b = T // 2, T // 4
+        rest = T - a - b - 5
+        pos = list(range(100, 100 + a)) + list(range(b)) + list(range(5)) + list(range(60, 60 + rest))
+        seq = [0] * a + [2] * b + [4] * 5 + [5] * rest
     pos_t, seq_t = torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32)
     slots = torch.tensor([2, 0, 3, 1, -1, 4], dtype=torch.int32)   # batch row 4 is padding
     table = torch.full((5, 120), -1, dtype=torch.int32)
@@ -289,7 +299,7 @@ def test_projection_with_rotation_and_cache_append_in_one_kernel(T, nh, nkv, K, 
     qg = (1 + 0.1 * torch.randn(d, device=DEV)).to(gain_dtype) if norm else None
     kg = (1 + 0.1 * torch.randn(d, device=DEV)).to(gain_dtype) if norm else None
     eps = 1e-5
-    assert ops.gemm_tc_rope_kv_supported(x, w, nh, nkv, d, dtype)
+    assert ops.gemm_tc_rope_kv_supported(x, w, nh, nkv, d, dtype, rope_dim)
     dev = lambda t: t.to(DEV)
     # the two kernels
     qkv = torch.empty(T, (nh + 2 * nkv) * d, dtype=dtype, device=DEV)
@@ -300,8 +310,12 @@ def test_projection_with_rotation_and_cache_append_in_one_kernel(T, nh, nkv, K, 
     # the one kernel
     kp1, vp1 = (torch.zeros(nblocks, nkv, bt, d, dtype=dtype, device=DEV) for _ in range(2))
     q1 = torch.full((T, nh * d), 9.0, dtype=dtype, device=DEV)
+    angles = ops.rope_angles(dev(pos_t), inv) if ops.gemm_tc_rope_kv_wants_angles(T, rope_dim) else None
+    if angles is not None:   # the table holds the angles that the rotation kernels compute in place
+        want = dev(pos_t).float()[:, None] * inv[None, :]
+        assert torch.allclose(angles[..., 0], torch.cos(want), atol=2e-6) and torch.allclose(angles[..., 1], torch.sin(want), atol=2e-6)
     ops.gemm_tc_rope_kv(x, w, q1, kp1, vp1, dev(table), bt, dev(seq_t), dev(pos_t), dev(slots), inv, rope_dim, qg, kg, eps,
-                        nh, nkv, status)
+                        nh, nkv, status, angles=angles)
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]
     assert torch.equal(vp1, vp2)                                   # values are copied: the same bits
@@ -313,12 +327,12 @@ def test_projection_with_rotation_and_cache_append_in_one_kernel(T, nh, nkv, K, 
     # a run that reads another layer's cache writes only q
     q3 = torch.empty_like(q1)
     ops.gemm_tc_rope_kv(x, w, q3, None, None, dev(table), bt, dev(seq_t), dev(pos_t), dev(slots), inv, rope_dim, qg, kg, eps,
-                        nh, nkv, status)
+                        nh, nkv, status, angles=angles)
     assert torch.equal(q3, q1)
-    # what it does not take: another head size, a prompt's worth of tokens
-    assert not ops.gemm_tc_rope_kv_supported(x, w, nh * 2, nkv * 2, 64, dtype)
+    # what it does not take: another head size; a prompt's worth of tokens whose heads are rotated in part
+    assert not ops.gemm_tc_rope_kv_supported(x, w, nh * 2, nkv * 2, 64, dtype, rope_dim)
     big = torch.randn(300, K, device=DEV).to(dtype)
-    assert not ops.gemm_tc_rope_kv_supported(big, w, nh, nkv, d, dtype)
+    assert not ops.gemm_tc_rope_kv_supported(big, w, nh, nkv, d, dtype, 48)
 
 
 def test_argmax_takes_the_first_maximum():
