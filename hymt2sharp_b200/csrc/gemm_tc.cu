@@ -70,6 +70,7 @@ struct GemmTcParams {
     long ldc;
     int T, N, K;             // tokens, output features, reduction length
     int stages;
+    int bn;                  // persistent kernel: the tile's width in weight rows (<= its template width, a multiple of 16; SwiGLU: of 32)
     int splits, k_blocks_per_split;
     int cluster;             // splits > 1: the split CTAs of a tile form a cluster and reduce through shared memory
     float* workspace;        // [tile][split][acc][BN][128] partial tiles (splits > 1)
@@ -115,6 +116,41 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
+// A look at a barrier that never suspends the thread.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// The copies of one stage (activations, weights, and for a split weight tile its second half) with, in front of them, a
+// look at the barrier of the stage that comes next: the answer takes a few hundred cycles under load, which pass
+// while the copies are issued instead of in front of the next ones.  Returns what the look saw.
+__device__ __forceinline__ bool tma_stage_looking_ahead(uint32_t bar, uint32_t bytes, uint32_t a_dst, const CUtensorMap* map_a, int ax,
+                                                        int ay, uint32_t b_dst, const CUtensorMap* map_b, int bx, int by,
+                                                        uint32_t b2_dst, int b2y, uint32_t has_b2, uint32_t next_bar,
+                                                        uint32_t next_parity) {
+    uint32_t seen;
+    asm volatile(
+        "{\n\t.reg .pred look, second;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 look, [%13], %14;\n\t"
+        "setp.ne.b32 second, %12, 0;\n\t"
+        "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %2;\n\t"
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%7], [%8, {%9, %10}], [%1];\n\t"
+        "@second cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%11], [%8, {%9, %15}], [%1];\n\t"
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%3], [%4, {%5, %6}], [%1];\n\t"
+        "selp.u32 %0, 1, 0, look;\n\t}"
+        : "=r"(seen)
+        : "r"(bar), "r"(bytes), "r"(a_dst), "l"((uint64_t)map_a), "r"(ax), "r"(ay), "r"(b_dst), "l"((uint64_t)map_b), "r"(bx), "r"(by),
+          "r"(b2_dst), "r"(has_b2), "r"(next_bar), "r"(next_parity), "r"(b2y)
+        : "memory");
+    return seen != 0;
+}
+
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     // K-major operand, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
@@ -134,6 +170,32 @@ __device__ __forceinline__ void umma_bf16_add(uint32_t tmem_d, uint64_t adesc, u
         "setp.eq.u32 p, 1, 1;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+// The four MMAs of a k block (BLOCK_K / UMMA_K) and the release of its stage with, in front of them, a look at the
+// barrier of the stage that comes next (see tma_stage_looking_ahead).  Returns what the look saw.
+__device__ __forceinline__ bool umma_block_looking_ahead(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                         uint32_t accumulate, uint32_t empty_bar, uint32_t next_bar,
+                                                         uint32_t next_parity) {
+    static_assert(BLOCK_K / UMMA_K == 4 && ((UMMA_K * 2) >> 4) == 2, "four MMAs a k block, descriptors 2 units apart");
+    uint32_t seen;
+    asm volatile(
+        "{\n\t.reg .pred look, first, yes;\n\t.reg .b64 a, b;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 look, [%7], %8;\n\t"
+        "setp.ne.b32 first, %5, 0;\n\t"
+        "setp.eq.u32 yes, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, first;\n\t"
+        "add.u64 a, %2, 2;\n\tadd.u64 b, %3, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n\t"
+        "add.u64 a, %2, 4;\n\tadd.u64 b, %3, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n\t"
+        "add.u64 a, %2, 6;\n\tadd.u64 b, %3, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n\t"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+        "selp.u32 %0, 1, 0, look;\n\t}"
+        : "=r"(seen)
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(empty_bar), "r"(next_bar), "r"(next_parity)
+        : "memory");
+    return seen != 0;
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -662,12 +724,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
+    // BN is the widest tile (the accumulators lie BN columns apart); the width in use comes with the launch, chosen so
+    // that the tiles fill whole waves of SMs
     constexpr bool SPLIT_B = EPI == EPI_SWIGLU;
-    constexpr int B_TILE_BYTES = BN * BLOCK_K * 2;
-    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    const int bn = p.bn;
+    const int B_TILE_BYTES = bn * BLOCK_K * 2;
+    const int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int TMEM_COLS = 2 * BN;                       // 256 or 512
-    constexpr int OUT_COLS = SPLIT_B ? BN / 2 : BN;
-    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+    const int OUT_COLS = SPLIT_B ? bn / 2 : bn;
+    const uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
@@ -706,33 +771,43 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     const uint32_t tmem_base = tmem_base_s;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: weights (B) of the first ring before the wait, then everything in order ----
-        long it = 0;
-        bool waited = false;
+        // ---- producer: the first stage's weights (B) before the wait, then everything in order ----
+        // Stage and phase are counted along; whether the next stage is free was looked up while this one's copies
+        // were issued (the stages of the first round are free anyway).
+        uint32_t s = 0, round = 0;
+        bool first = true, looked = true;
         for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
             const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
-            for (int kb = 0; kb < num_k_blocks; kb++, it++) {
-                const int s = (int)(it % stages);
-                if (it >= stages && !mbar_wait(empty0 + 8 * s, (uint32_t)(((it / stages) & 1) ^ 1), abort_flag, p.status, 101)) break;
+            for (int kb = 0; kb < num_k_blocks; kb++) {
+                if (round > 0 && !looked && !mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, abort_flag, p.status, 101)) break;
                 const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
                 const int k = kb * BLOCK_K;
-                mbar_expect_tx(bar, STAGE_BYTES);
-                if (SPLIT_B) {
+                const uint32_t s_next = s + 1 == (uint32_t)stages ? 0 : s + 1, round_next = s_next ? round : round + 1;
+                if (first) {
+                    mbar_expect_tx(bar, STAGE_BYTES);
                     tma_load_2d(b_dst, &map_b, bar, k, b_row0);
-                    tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, bar, k, p.N + b_row0);
+                    if (SPLIT_B) tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, bar, k, p.N + b_row0);
+                    pdl_wait();   // the activations come from the kernel before
+                    tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+                    first = false;
+                    looked = round_next == 0;
                 } else {
-                    tma_load_2d(b_dst, &map_b, bar, k, b_row0);
+                    const bool seen = tma_stage_looking_ahead(bar, STAGE_BYTES, a_dst, &map_a, k, a_row0, b_dst, &map_b, k, b_row0,
+                                                              b_dst + B_TILE_BYTES / 2, p.N + b_row0, SPLIT_B ? 1u : 0u,
+                                                              empty0 + 8 * s_next, (round_next & 1) ^ 1);
+                    looked = round_next == 0 || seen;
                 }
-                if (!waited) { pdl_wait(); waited = true; }   // the activations come from the kernel before
-                tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+                s = s_next;
+                round = round_next;
             }
         }
-        if (!waited) pdl_wait();
+        if (first) pdl_wait();
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: the stage's descriptor is carried along, see gemm_tc_kernel --------------
         const uint64_t desc0 = smem_desc_sw128(tiles);
         uint64_t adesc = desc0;
         uint32_t s = 0, phase = 0;
+        bool looked = false;   // whether the stage's barrier was already seen complete
         int j = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, j++) {
             const int buf = j & 1;
@@ -741,16 +816,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             bool ok = true;
             const uint32_t acc_at = tmem_base + buf * BN;
             for (int kb = 0; kb < num_k_blocks; kb++) {
-                if (!(ok = mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102))) break;
+                if (!looked && !(ok = mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t bdesc = adesc + (A_TILE_BYTES >> 4);
-                umma_bf16(acc_at, adesc, bdesc, IDESC, kb > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 1; k < BLOCK_K / UMMA_K; k++)
-                    umma_bf16_add(acc_at, adesc + k * ((UMMA_K * 2) >> 4), bdesc + k * ((UMMA_K * 2) >> 4), IDESC);
-                umma_commit(empty0 + 8 * s);
-                if (++s == (uint32_t)stages) { s = 0; phase ^= 1; adesc = desc0; }
-                else adesc += (uint64_t)(STAGE_BYTES >> 4);
+                const uint32_t s_next = s + 1 == (uint32_t)stages ? 0 : s + 1, phase_next = s_next ? phase : phase ^ 1;
+                // a look at a stage that will never be filled (behind the last one) is thrown away by the loops' ends
+                looked = umma_block_looking_ahead(acc_at, adesc, adesc + (A_TILE_BYTES >> 4), IDESC, kb > 0 ? 1u : 0u, empty0 + 8 * s,
+                                                  full0 + 8 * s_next, phase_next);
+                s = s_next;
+                phase = phase_next;
+                adesc = s ? adesc + (uint64_t)(STAGE_BYTES >> 4) : desc0;
             }
             if (!ok) break;
             umma_commit(acc_full0 + 8 * buf);
@@ -775,7 +849,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 // the tile holds BN / 128 heads of 128 tokens: this thread's token, head after head
                 const int heads = p.rope.nh + 2 * p.rope.nkv;
 #pragma unroll 1
-                for (int h = 0; h < BN / TILE_M; h++) {
+                for (int h = 0; h < bn / TILE_M; h++) {
                     const int head = b_row0 / TILE_M + h;
                     if (head < heads) rope_head_from_tmem(lane_addr + h * TILE_M, m, head, m < p.T, p.rope);
                 }
@@ -784,7 +858,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             for (int c = 0; c < OUT_COLS; c += 16) {
                 float g[16], u[16];
                 tmem_load<16>(lane_addr + c, g);
-                if (EPI == EPI_SWIGLU) tmem_load<16>(lane_addr + BN / 2 + c, u);
+                if (EPI == EPI_SWIGLU) tmem_load<16>(lane_addr + bn / 2 + c, u);
                 if (m >= p.T) continue;
                 const int n0 = b_row0 + c;
                 TC* dst = C + (size_t)m * p.ldc + n0;
@@ -968,7 +1042,7 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && CLUSTER_RING_BYTES / stage_bytes >= 4 &&
                  (size_t)num_acc * pl.bn * TILE_M * 4 <= 96 * 1024;
     // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
-    const int ring_bytes = pl.cluster ? CLUSTER_RING_BYTES : (ctas <= sm_count || pl.persistent) ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM
+    const int ring_bytes = pl.cluster ? CLUSTER_RING_BYTES : pl.persistent ? 224 * 1024 : ctas <= sm_count ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM, all it has
     int stages = ring_bytes / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
     if (pl.swapped && stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
@@ -985,7 +1059,7 @@ int launch_persistent_one(const CUtensorMap& ma, const CUtensorMap& mb, const Ge
     auto kernel = gemm_tc_persistent_kernel<BN, EPI, TC>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
         if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
         configured = true;
     }
@@ -1051,7 +1125,7 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
         ok = make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, w_rows, K, ldw, epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn);
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
-    GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
+    GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
                    RopeEpilogue{}};
     if (pl.swapped) {
         switch (pl.bn) {
@@ -1111,7 +1185,7 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
     RopeEpilogue rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, token_seq, token_pos,
                       slot_ids, inv_freq, angles, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
                       gain_dtype == HYMT2_BF16 ? 1 : 0, eps};
-    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, nullptr, nullptr, status, rope};
+    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, nullptr, nullptr, status, rope};
     if (pl.persistent) {
         const int ctas = pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count;
         return launch_persistent_one<PERSISTENT_BN, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);
