@@ -307,7 +307,7 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
 }
 
 template <int BN, bool SWAPPED, int EPI, typename TC>
-__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), (!SWAPPED && EPI == EPI_ROPE_KV) ? 2 : 1)
+__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
     constexpr int NUM_ACC = (SWAPPED && EPI == EPI_SWIGLU) ? 2 : 1;   // accumulators = A tiles per stage
     constexpr bool SPLIT_B = !SWAPPED && EPI == EPI_SWIGLU;           // B tile = gate rows, then up rows
@@ -539,9 +539,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         };
 
-        if (!SWAPPED && EPI == EPI_ROPE_KV) {   // the tile is one head of 128 tokens, this thread's row a token
-            if (ok) rope_head_from_tmem(lane_addr, a_row0 + row, b_row0 / TILE_M, a_row0 + row < p.T, p.rope);
-        } else if (!SWAPPED || p.splits == 1) {   // K is only split in the swapped orientation
+        if (!SWAPPED || p.splits == 1) {   // K is only split in the swapped orientation
             if (ok) {
                 for (int c = 0; c < OUT_COLS; c += CH) {
                     float g[CH], u[CH];
@@ -1018,13 +1016,25 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         }
         pl.tiles = tiles;
     } else {
-        // a wide tile for every SM: the persistent kernel with 256-wide tiles (one CTA per SM, epilogue hidden
-        // behind the next tile); fewer: 128-wide tiles, two CTAs per SM, so that all SMs get work.  (Narrower
-        // persistent tiles, 128 and 192 wide, were measured too: they cost more per flop than they save in waves.)
-        const int wide_cols = epilogue == EPI_SWIGLU ? PERSISTENT_BN / 2 : PERSISTENT_BN;
-        const long wide_tiles = (long)((T + TILE_M - 1) / TILE_M) * ((N + wide_cols - 1) / wide_cols);
-        pl.persistent = wide_tiles >= sm_count;   // measured at 2,048 tokens: QKV (192 wide tiles) gains, O and down (128) lose
-        pl.bn = pl.persistent ? PERSISTENT_BN : 128;
+        // The persistent kernel (one CTA per SM, wide tiles, epilogue hidden behind the next tile) wherever the output
+        // is written once; where it is added to the float32 residual (twice the epilogue traffic), only when there is a
+        // 256-wide tile for every SM: below that, 128-wide tiles with two CTAs per SM measured faster.
+        const int row_tiles = (T + TILE_M - 1) / TILE_M;
+        const long wide_tiles = (long)row_tiles * ((N + PERSISTENT_BN - 1) / PERSISTENT_BN);
+        pl.persistent = epilogue != EPI_ACCUMULATE || wide_tiles >= sm_count;
+        pl.bn = 128;
+        if (pl.persistent) {
+            // The tile's width: the one whose tiles fill whole waves of SMs best.  A k block of a tile bn wide
+            // costs about 350 + 1.84 bn cycles (measured at 192 to 256), and a wave lasts as long as one tile.
+            const int step = epilogue == EPI_SWIGLU ? 32 : epilogue == EPI_ROPE_KV ? TILE_M : 16;   // SwiGLU: gate and up halves in chunks of 16; rotation: whole heads
+            double best = 0;
+            for (int bn = PERSISTENT_BN; bn >= 128; bn -= step) {
+                const int out = epilogue == EPI_SWIGLU ? bn / 2 : bn;
+                const long tiles = (long)row_tiles * ((N + out - 1) / out);
+                const double cost = (double)((tiles + sm_count - 1) / sm_count) * (350.0 + 1.84 * bn);
+                if (bn == PERSISTENT_BN || cost < best) { best = cost; pl.bn = bn; }
+            }
+        }
         const int out_cols = epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn;
         pl.grid = dim3((T + TILE_M - 1) / TILE_M, (N + out_cols - 1) / out_cols, 1);
         pl.tiles = pl.grid.x * pl.grid.y;
@@ -1145,7 +1155,7 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
 HYMT2_API int hymt2_gemm_tc_rope_kv_supported(int T, int N, int K, int rope_dim) {
     if (T <= 0 || N <= 0 || N % TILE_M || K <= 0 || K % 8) return 0;
     Plan pl;
-    make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl);
+    make_plan(T, N, K, EPI_ROPE_KV, sm_count_of_current_device(), &pl);
     if (pl.swapped) return (T <= 64 && pl.cluster && pl.bn <= 64) ? 1 : 0;
     return (rope_dim == 0 || rope_dim == TILE_M) ? 1 : 0;   // tokens as rows: a thread rotates its token's whole head
 }
@@ -1175,7 +1185,7 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
     HYMT2_REQUIRE(!write_kv || (k_cache && v_cache), "gemm_tc_rope_kv: the cache planes are needed to write keys and values");
     HYMT2_REQUIRE(hymt2_gemm_tc_rope_kv_supported(T, N, K, rope_dim), "gemm_tc_rope_kv: T=%d N=%d K=%d rope_dim=%d is not taken", T, N, K, rope_dim);
     Plan pl;
-    make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl);
+    make_plan(T, N, K, EPI_ROPE_KV, sm_count_of_current_device(), &pl);
     CUtensorMap ma, mb;
     const bool maps = pl.swapped ? make_map(&ma, W, N, K, ldw, TILE_M) && make_map(&mb, X, T, K, lda, pl.bn)
                                  : make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, N, K, ldw, pl.bn);
@@ -1190,7 +1200,6 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
         const int ctas = pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count;
         return launch_persistent_one<PERSISTENT_BN, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);
     }
-    if (!pl.swapped) return launch<128, false, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
     switch (pl.bn) {
         case 16: return launch<16, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
         case 32: return launch<32, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
