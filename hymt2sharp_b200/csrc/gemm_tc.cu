@@ -266,8 +266,9 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
     const void* gain = is_q ? rp.q_gain : is_k ? rp.k_gain : nullptr;
     const bool rotate = (is_q || is_k) && rp.rope_dim == TILE_M;
     constexpr int HALF = TILE_M / 2;
-    // the head's 128 values stay in registers between the rotation and the norm (the kernels that come here have
-    // one CTA per SM or few registers otherwise); every index below is known when the loops are unrolled
+    // the head's 128 values stay in registers between the rotation and the norm (the persistent kernel has one CTA
+    // per SM and registers to spare; through tensor memory, tcgen05.st and back, it took four times as long);
+    // every index below is known when the loops are unrolled
     float v[TILE_M];
 #pragma unroll
     for (int c = 0; c < TILE_M; c += 16) tmem_load<16>(head_at + c, v + c);
@@ -1025,13 +1026,17 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         pl.bn = 128;
         if (pl.persistent) {
             // The tile's width: the one whose tiles fill whole waves of SMs best.  A k block of a tile bn wide
-            // costs about 350 + 1.84 bn cycles (measured at 192 to 256), and a wave lasts as long as one tile.
+            // costs about 350 + 1.84 bn cycles (measured at 192 to 256), and a wave lasts as long as one tile; behind
+            // the last wave one epilogue stands alone, which costs about 60 cycles a column where it rotates and
+            // norms heads (measured: tiles of one head win up to a few thousand tokens, of two heads beyond), 30
+            // where it adds into float32, 15 else.
             const int step = epilogue == EPI_SWIGLU ? 32 : epilogue == EPI_ROPE_KV ? TILE_M : 16;   // SwiGLU: gate and up halves in chunks of 16; rotation: whole heads
             double best = 0;
             for (int bn = PERSISTENT_BN; bn >= 128; bn -= step) {
                 const int out = epilogue == EPI_SWIGLU ? bn / 2 : bn;
                 const long tiles = (long)row_tiles * ((N + out - 1) / out);
-                const double cost = (double)((tiles + sm_count - 1) / sm_count) * (350.0 + 1.84 * bn);
+                const double epilogue_cycles = (epilogue == EPI_ROPE_KV ? 60.0 : epilogue == EPI_ACCUMULATE ? 30.0 : 15.0) * bn;
+                const double cost = (double)((tiles + sm_count - 1) / sm_count) * num_k_blocks * (350.0 + 1.84 * bn) + epilogue_cycles;
                 if (bn == PERSISTENT_BN || cost < best) { best = cost; pl.bn = bn; }
             }
         }
