@@ -51,26 +51,33 @@ def make_context(cache, entries: list, vocab: int, dtype, device, status, meta_b
     builds the StepContext: packed tokens, each token's batch row and position, the rows'
     offsets, slots and lengths.  Returns (context, wanted rows or None, their count, plan);
     `plan` goes to cache.end_step once the step has been launched."""
+    # whole arrays at a time: a prompt of thousands of tokens costs the host microseconds, not one Python step a token
     tokens, token_seq, token_pos, cu, slots, kv_lens, want = [], [], [], [0], [], [], []
     starts, news = [], []
     for b, e in enumerate(entries):
-        n = len(e.tokens)
+        try:
+            ids = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+        except (OverflowError, TypeError, ValueError) as err:
+            raise EngineError(f"the tokens of an entry are not integer ids: {err}") from None
+        n = int(ids.shape[0])
         start = cache.length(e.slot)
-        for t in e.tokens:
-            if not (0 <= int(t) < vocab):
-                raise EngineError(f"token id {t} is outside the vocabulary of {vocab}")
+        if n and (int(ids.min()) < 0 or int(ids.max()) >= vocab):
+            bad = ids[(ids < 0) | (ids >= vocab)][0]
+            raise EngineError(f"token id {int(bad)} is outside the vocabulary of {vocab}")
         for w in e.want:
             if not (0 <= int(w) < n):
                 raise EngineError(f"wanted place {w} is outside the {n} tokens of the entry")
             want.append(cu[-1] + int(w))
-        tokens.extend(int(t) for t in e.tokens)
-        token_seq.extend([b] * n)
-        token_pos.extend(range(start, start + n))
+        tokens.append(ids.astype(np.int32))
+        token_seq.append(np.full(n, b, dtype=np.int32))
+        token_pos.append(np.arange(start, start + n, dtype=np.int32))
         cu.append(cu[-1] + n)
         slots.append(e.slot)
         kv_lens.append(start + n)
         starts.append(start)
         news.append(n)
+    num_tokens = cu[-1]
+    tokens, token_seq, token_pos = (np.concatenate(a) for a in (tokens, token_seq, token_pos))
     plan = list(zip(slots, news))
     cache.begin_step(plan)  # raises CacheFull before anything changed
     arrays = [np.asarray(a, dtype=np.int32) for a in (tokens, token_seq, token_pos, cu, slots, kv_lens, want)]
@@ -82,7 +89,7 @@ def make_context(cache, entries: list, vocab: int, dtype, device, status, meta_b
     for n in sizes:
         v.append(meta[o:o + n])
         o += n
-    ctx = StepContext(device=torch.device(device), dtype=dtype, num_tokens=len(tokens), num_seqs=len(entries),
+    ctx = StepContext(device=torch.device(device), dtype=dtype, num_tokens=num_tokens, num_seqs=len(entries),
                       tokens=v[0], token_seq=v[1], token_pos=v[2], cu_seqlens=v[3], slot_ids=v[4], kv_lens=v[5],
                       max_new_tokens=max(news), max_kv_len=max(kv_lens), cache=cache, status=status,
                       host_slots=slots, host_new_tokens=news, host_starts=starts)
