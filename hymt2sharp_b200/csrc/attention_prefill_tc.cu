@@ -166,8 +166,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // and two CTAs of 112 KB fit an SM.  Barriers and the two words lie behind the tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + BARS_OFFSET);
-    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 7) * 8);
-    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 7) * 8 + 4);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 9) * 8);
+    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 9) * 8 + 4);
 
     // The last query tiles of a prompt walk the most keys: CTAs are numbered by falling query tile, so the long
     // ones start first and the short ones fill the gaps.  When all CTAs fit on the SMs at once (two each), the
@@ -198,19 +198,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * KV_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
     const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
-    const uint32_t s_full = q_full + 24, p_full = q_full + 40;   // two of each, and of o_full: even and odd tiles
+    const uint32_t s_full = q_full + 32, p_full = q_full + 48;   // s_full: one for even, one for odd tiles; o_full and p_full: three each
+    // Why these counts.  A parity cannot tell a barrier's phase from the one two later, so no reader may fall two
+    // phases behind a barrier, however long its thread is kept from running.  S(j) is only issued once P·V of tile
+    // j - 3 is through: with P's barrier of tile j the one of tile j - 3, P(j) cannot be announced before the
+    // P·V issuer has taken P(j - 3); with two barriers it could, while that thread still waited for P(j - 2)'s
+    // predecessor: one CTA in tens of thousands then waited for ever (status 114, met with 32 heads and 16,384
+    // tokens in a step).  O's barrier has three for the score issuer's sake, who reads P·V(j - 3) after issuing S(j - 1),
+    // and the copies' stages are held by both their readers (kv_empty below).
     volatile int* abort_flag = &abort_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < KV_STAGES; s++) {
             mbar_init(kv_full + 8 * s, 1);
-            mbar_init(kv_empty + 8 * s, 1);
+            mbar_init(kv_empty + 8 * s, 2);   // P·V of the tile is through, and the score issuer has seen the copy land
         }
         mbar_init(q_full, 1);
-        for (int t = 0; t < 2; t++) {
+        for (int t = 0; t < 2; t++) mbar_init(s_full + 8 * t, 1);
+        for (int t = 0; t < 3; t++) {
             mbar_init(o_full + 8 * t, 1);
-            mbar_init(s_full + 8 * t, 1);
             mbar_init(p_full + 8 * t, 128);
         }
         abort_s = 0;
@@ -282,11 +289,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int i = 0; ok && i + 1 < num_tiles; i++) {
             // K(i + 1) has landed (with V(i))
             if (!mbar_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1, abort_flag, p.status, 113)) break;
+            mbar_arrive(kv_empty + 8 * (i % KV_STAGES));   // seen: the stage may be filled again once P·V of tile i is through too
             // P·V of tile i - 2 is through.  The softmax warps, who wait for P·V of the tile before theirs only when a
             // maximum rose, then never meet a barrier more than one phase behind (a parity cannot tell two apart).
-            if (i >= 2 && !mbar_wait(o_full + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, p.status, 108)) break;
+            if (i >= 2 && !mbar_wait(o_full + 8 * ((i - 2) % 3), ((i - 2) / 3) & 1, abort_flag, p.status, 108)) break;
             // the scores of tile i - 1 have been read: their buffer takes those of tile i + 1
-            if (i >= 1 && !mbar_wait(p_full + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.status, 118)) break;
+            if (i >= 1 && !mbar_wait(p_full + 8 * ((i - 1) % K_SLOTS), ((i - 1) / K_SLOTS) & 1, abort_flag, p.status, 118)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_scores(i + 1);
         }
@@ -296,7 +304,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
         for (int i = 0; i < num_tiles; i++) {
             const int s = i % KV_STAGES;
-            if (!mbar_wait(p_full + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 114)) break;
+            if (!mbar_wait(p_full + 8 * (i % K_SLOTS), (i / K_SLOTS) & 1, abort_flag, p.status, 114)) break;
             if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 109)) break;   // V(i) has landed
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t pd = p_desc0 + (i % K_SLOTS) * K_STEP, vd = v_desc0 + s * V_STEP;
@@ -304,7 +312,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int k = 0; k < KEY_TILE / 16; k++)
                 umma_bf16(tmem_base + O_COL, pd + ((k * 32) >> 4), vd + ((k * (16 * 128)) >> 4), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
             umma_commit(kv_empty + 8 * s);
-            umma_commit(o_full + 8 * (i & 1));
+            umma_commit(o_full + 8 * (i % 3));
         }
     } else if (warp >= 4) {
         // ---- softmax: one thread per query row; O stays in TMEM ------------------------------------
@@ -345,7 +353,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (raise) m = tile_max;
             if (i > 0 && __any_sync(0xffffffffu, raise)) {
                 // the O of the tiles so far is complete, then every row of the warp scales its own O
-                if (!(ok = mbar_wait(o_full + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.status, 116))) break;
+                if (!(ok = mbar_wait(o_full + 8 * ((i - 1) % 3), ((i - 1) / 3) & 1, abort_flag, p.status, 116))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int c = 0; c < D; c += 16) {   // 16 columns at a time: the row's 64 scores are live in registers
@@ -396,9 +404,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full + 8 * (i & 1));
+            mbar_arrive(p_full + 8 * (i % K_SLOTS));
         }
-        if (ok) ok = mbar_wait(o_full + 8 * ((num_tiles - 1) & 1), ((num_tiles - 1) >> 1) & 1, abort_flag, p.status, 117);
+        if (ok) ok = mbar_wait(o_full + 8 * ((num_tiles - 1) % 3), ((num_tiles - 1) / 3) & 1, abort_flag, p.status, 117);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -461,7 +469,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            cudaStream_t stream) {
     constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
     constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (kv_tile >= p_tile ? kv_tile : p_tile) + KV_STAGES * kv_tile +
-                            (2 * KV_STAGES + 7) * 8 + 8;   // tiles, barriers, two words
+                            (2 * KV_STAGES + 9) * 8 + 8;   // tiles, barriers, two words
     auto kernel = attention_prefill_tc_kernel<D>;
     static bool configured = false;
     if (!configured) {

@@ -511,6 +511,32 @@ def test_attention_prefill_tcgen05(nh, nkv, d, window):
     assert torch.allclose(out.double(), ref2, **_tol(dtype))
 
 
+def test_attention_prefill_tcgen05_with_tens_of_thousands_of_ctas():
+    """Eight prompts of 2,048 tokens with 32 heads: 4,096 CTAs of up to 32 key tiles, several times over.  One CTA
+    in tens of thousands once waited for ever on a barrier that had run two phases ahead of a thread that was kept
+    from running; the status word shows such a wait.  The result is compared with the general kernel."""
+    ops = _ops()
+    torch.manual_seed(3)
+    dtype, nh, nkv, d, B, T = torch.bfloat16, 32, 8, 128, 8, 2048
+    keys = [torch.randn(T, nkv, d, device=DEV).to(dtype) for _ in range(B)]
+    vals = [torch.randn(T, nkv, d, device=DEV).to(dtype) for _ in range(B)]
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=9)
+    q = torch.randn(B * T, nh * d, device=DEV).to(dtype)
+    cu = (torch.arange(B + 1, dtype=torch.int32, device=DEV) * T).contiguous()
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    kv = torch.full((B,), T, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    out = torch.empty_like(q)
+    for _ in range(6):
+        ops.attention_prefill_tc(out, q, kp, vp, table, cu, slots, kv, B, T, nh, nkv, d, scale, 0, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    ref = torch.empty_like(q)
+    ops.attention_simt(ref, q, kp, vp, table, cu, slots, kv, B, T, nh, nkv, d, scale)
+    assert torch.allclose(out.float(), ref.float(), **_tol(dtype))
+
+
 def test_attention_decode_tcgen05_more_chunks_than_a_cta_holds():
     """Many long rows: more chunks of 128 keys than the CTAs hold at a time (they go through them in
     rounds), rows beyond 8,192 positions, and one far key that carries all the weight of its row."""
