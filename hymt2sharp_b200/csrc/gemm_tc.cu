@@ -116,19 +116,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
-// A look at a barrier that never suspends the thread.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-
 // The copies of one stage (activations, weights, and for a split weight tile its second half) with, in front of them, a
-// look at the barrier of the stage that comes next: the answer takes a few hundred cycles under load, which pass
+// look (mbarrier.test_wait, which never suspends the thread) at the barrier of the stage that comes next: the answer
+// takes a few hundred cycles under load, which pass
 // while the copies are issued instead of in front of the next ones.  Returns what the look saw.
 __device__ __forceinline__ bool tma_stage_looking_ahead(uint32_t bar, uint32_t bytes, uint32_t a_dst, const CUtensorMap* map_a, int ax,
                                                         int ay, uint32_t b_dst, const CUtensorMap* map_b, int bx, int by,
