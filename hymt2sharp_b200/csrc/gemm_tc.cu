@@ -1105,6 +1105,25 @@ HYMT2_API int hymt2_gemm_tc_plan(int T, int N, int K, int epilogue, long* worksp
     return HYMT2_OK;
 }
 
+// How a product of T tokens onto N features over K would be run (epilogue 0 store, 1 add, 2 SwiGLU, 3 the q/k/v epilogue),
+// on a device of sm_count SMs (0: the current one): out[0] weight rows on the 128-row side (few tokens), [1] the
+// persistent kernel, [2] the tile's width, [3] stages of the ring, [4] splits of K, [5] whether the splits fold as a cluster,
+// [6] tiles, [7] CTAs.  For tests and for reading a profile; nothing is launched.
+HYMT2_API int hymt2_gemm_tc_describe(int T, int N, int K, int epilogue, int sm_count, int* out) {
+    HYMT2_REQUIRE(T > 0 && N > 0 && K > 0 && epilogue >= 0 && epilogue <= 3 && out, "gemm_tc_describe: bad arguments");
+    Plan pl;
+    make_plan(T, N, K, epilogue, sm_count > 0 ? sm_count : sm_count_of_current_device(), &pl);
+    out[0] = pl.swapped ? 1 : 0;
+    out[1] = pl.persistent ? 1 : 0;
+    out[2] = pl.bn;
+    out[3] = pl.stages;
+    out[4] = pl.splits;
+    out[5] = pl.cluster ? 1 : 0;
+    out[6] = pl.tiles;
+    out[7] = pl.persistent ? (pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count) : (int)(pl.grid.x * pl.grid.y * pl.grid.z);
+    return HYMT2_OK;
+}
+
 // C[T,N] (ldc) = epilogue(X[T,K] (lda) · W[N,K]^T (ldw)), X and W bfloat16; for SwiGLU W has 2N rows.
 HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
                             long ldc, int epilogue, float* workspace, long workspace_floats, int* counters,

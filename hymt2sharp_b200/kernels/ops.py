@@ -292,6 +292,18 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
                                         _ptr(status), _stream()), "gemm_tc_rope_kv")
 
 
+def gemm_tc_describe(tokens: int, out_features: int, inner: int, epilogue: int, sm_count: int = 0) -> dict:
+    """How the tensor-core kernel would run this product (nothing is launched; works without a GPU when sm_count
+    is given): orientation, kernel, tile width, ring depth, splits of K and how they fold, tiles and CTAs.
+    epilogue: EPILOGUE_STORE / _ACCUMULATE / _SWIGLU, or 3 for the q/k/v projection with rotation."""
+    out = (ctypes.c_int * 8)()
+    rc = _lib().hymt2_gemm_tc_describe(c_int(tokens), c_int(out_features), c_int(inner), c_int(epilogue), c_int(sm_count), out)
+    if rc != 0:
+        raise KernelError(f"gemm_tc_describe failed ({rc}): {_lib().hymt2_last_error().decode(errors='replace')}")
+    keys = ("swapped", "persistent", "tile_width", "stages", "k_splits", "cluster", "tiles", "ctas")
+    return {k: (bool(v) if k in ("swapped", "persistent", "cluster") else int(v)) for k, v in zip(keys, out)}
+
+
 def gemm_tc_rope_kv_wants_angles(tokens: int, rope_dim: int) -> bool:
     """Whether gemm_tc_rope_kv of this many tokens wants the table of their angles: where tokens are the
     accumulator's rows, a thread owns a whole token and would compute every angle once per head."""

@@ -1,0 +1,76 @@
+"""How the tensor-core matrix product is cut into tiles, splits and waves: decisions of the host code in
+csrc/gemm_tc.cu, asked through `ops.gemm_tc_describe` for a device of 148 SMs.  Nothing is launched, so this runs
+without a GPU; it needs nvcc to build the library and is skipped without it."""
+import pytest
+
+from hymt2sharp_b200.kernels import build
+
+STORE, ADD, SWIGLU, QKV = 0, 1, 2, 3
+SMS = 148
+
+
+@pytest.fixture(scope="module")
+def describe():
+    try:
+        build.find_nvcc()
+    except Exception as err:   # no compiler here: the library cannot be built
+        pytest.skip(f"nvcc is not available: {err}")
+    from hymt2sharp_b200.kernels import ops
+    return lambda T, N, K, epi: ops.gemm_tc_describe(T, N, K, epi, sm_count=SMS)
+
+
+def test_few_tokens_put_the_weight_rows_on_the_128_row_side(describe):
+    for tokens, width in ((1, 16), (16, 16), (17, 32), (33, 64), (64, 64), (65, 128), (128, 128)):
+        plan = describe(tokens, 6144, 2048, SWIGLU)
+        assert plan["swapped"] and not plan["persistent"] and plan["tile_width"] == width
+    assert not describe(129, 6144, 2048, SWIGLU)["swapped"]
+
+
+@pytest.mark.parametrize("N, K, epi", [(6144, 2048, SWIGLU), (2048, 6144, ADD), (2048, 2048, ADD), (3072, 2048, QKV),
+                                       (120818, 2048, STORE), (392, 264, STORE), (8192, 3072, SWIGLU), (4096, 14336, ADD)])
+def test_the_cut_of_k_never_depends_on_the_number_of_tokens(describe, N, K, epi):
+    """Or a sequence's logits would depend on what else is in the batch."""
+    plans = [describe(T, N, K, epi) for T in (1, 2, 8, 16, 17, 40, 64, 100, 128)]
+    assert len({p["k_splits"] for p in plans}) == 1
+    assert all(p["k_splits"] <= 8 for p in plans)           # a portable cluster
+    assert all(p["ctas"] == p["tiles"] * p["k_splits"] for p in plans)
+
+
+def test_a_product_with_few_tiles_is_cut_to_about_one_wave(describe):
+    down = describe(8, 2048, 6144, ADD)      # 16 tiles of 128 features
+    assert down["tiles"] == 16 and down["k_splits"] == 8 and down["cluster"]
+    gate_up = describe(8, 6144, 2048, SWIGLU)   # 48 tiles, wide stages: the splits fold through memory
+    assert gate_up["k_splits"] == 3 and not gate_up["cluster"] and gate_up["ctas"] <= SMS
+    head = describe(8, 120818, 2048, STORE)  # 944 tiles: no cut
+    assert head["k_splits"] == 1 and head["tiles"] == 944
+
+
+def test_prompt_sized_products_fill_whole_waves(describe):
+    # the sizes of the 1.8B model at 2,048 tokens
+    gate_up = describe(2048, 6144, 2048, SWIGLU)
+    assert gate_up["persistent"] and gate_up["tile_width"] == 224 and gate_up["tiles"] == 880 and gate_up["ctas"] == SMS
+    qkv = describe(2048, 3072, 2048, QKV)
+    assert qkv["persistent"] and qkv["tile_width"] == 128          # one head a tile up to a few thousand tokens
+    assert describe(8192, 3072, 2048, QKV)["tile_width"] == 256    # two heads beyond
+    # adding into the residual: 128 x 128 tiles, two CTAs per SM, until there is a 256-wide tile for every SM
+    for K in (2048, 6144):
+        small, large = describe(2048, 2048, K, ADD), describe(4096, 2048, K, ADD)
+        assert not small["persistent"] and small["tile_width"] == 128 and small["ctas"] == 256
+        assert large["persistent"] and large["ctas"] == SMS
+
+
+@pytest.mark.parametrize("T", [129, 300, 512, 1000, 2048, 5000, 16384])
+@pytest.mark.parametrize("N, K, epi", [(6144, 2048, SWIGLU), (3072, 2048, STORE), (3072, 2048, QKV), (896, 256, QKV),
+                                       (8192, 3072, SWIGLU), (777, 264, STORE)])
+def test_the_width_of_a_persistent_tile_is_one_the_kernel_takes(describe, T, N, K, epi):
+    plan = describe(T, N, K, epi)
+    assert plan["persistent"] and 128 <= plan["tile_width"] <= 256
+    step = {SWIGLU: 32, QKV: 128}.get(epi, 16)   # gate and up halves in chunks of 16 columns; whole heads; chunks of 16
+    assert plan["tile_width"] % step == 0
+    out_cols = plan["tile_width"] // 2 if epi == SWIGLU else plan["tile_width"]
+    assert plan["tiles"] == -(-T // 128) * -(-N // out_cols)
+    assert plan["ctas"] == min(plan["tiles"], SMS)
+    assert plan["stages"] >= 4                    # the ring: 224 KB of shared memory
+    # never more waves than the widest tile would need
+    widest = -(-T // 128) * -(-N // (128 if epi == SWIGLU else 256))
+    assert -(-plan["tiles"] // SMS) * plan["tile_width"] <= -(-widest // SMS) * 256 * 1.3
