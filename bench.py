@@ -26,7 +26,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Hy-MT2 1.8B layer sizes
+# the Hy-MT2 1.8B layer sizes, random weights: the configuration that the published benchmark names
 SIZES = dict(num_hidden_layers=32, hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
              intermediate_size=6144, vocab_size=120818, rope_theta=10000.0, rope_alpha=1000.0, rms_norm_eps=1e-5,
              use_qk_norm=True, tie_word_embeddings=True, max_position_embeddings=8192)
