@@ -8,7 +8,9 @@
 // accumulator back with `tcgen05.ld` and run the epilogue.
 //
 // Two orientations:
-//   normal   the 128-row side holds tokens, the BN side holds output features (prefill);
+//   normal   the 128-row side holds tokens, the BN side holds output features (more than 128 tokens): a
+//            persistent kernel with one CTA per SM that walks tiles of a width chosen to fill whole waves
+//            (see gemm_tc_persistent_kernel and make_plan), or 128 x 128 tiles with two CTAs per SM;
 //   swapped  the 128-row side holds output features (weight rows), the BN side holds tokens
 //            (BN = 16..128): a decode step streams every weight tile once at full tile height
 //            whatever the batch is.  With `splits` > 1 the K range is cut over gridDim.z.  The
@@ -20,7 +22,8 @@
 //            itself and a deep ring; partial tiles then go through a global workspace, folded by the
 //            CTA that arrives last at the tile's counter, also in split order.)
 // Epilogues: store, accumulate into float32 C, SwiGLU (silu(gate) * up; W holds N gate rows,
-// then N up rows; src/HyMT2Sharp/Ops.cs:1053).  Rows and K beyond the matrices are zero-filled
+// then N up rows; src/HyMT2Sharp/Ops.cs:1053), and for the fused q/k/v projection with heads of 128 the rotation, the
+// per-head norm and the append to the paged cache (RopeEpilogue).  Rows and K beyond the matrices are zero-filled
 // by TMA and masked in the epilogue, so any T and N are taken; K, lda and ldw must be multiples
 // of 8 elements (TMA's 16-byte rule).
 //
