@@ -147,7 +147,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // Only chunks that hold visible keys are items: warp 2 counts them row by row (a running sum in shared
     // memory), so w = blockIdx.x, + gridDim.x, ... below the total is always a real chunk and every CTA
     // gets the same number of them, give or take one.
-    struct Item { int b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, row0, row1; };
+    struct Item { int b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, first_block, row0, row1; };
     __shared__ Item items[MAX_ITEMS];
     __shared__ int row_first[MAX_ROWS + 1], row_slot[MAX_ROWS], row_len[MAX_ROWS];
     if (warp == 1) {
@@ -218,8 +218,12 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 it.split = it.lo / CHUNK + rem % chunks;
                 it.chunk_begin = it.split * CHUNK;
                 it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
+                // With a window, the chunk's first block may lie wholly below the oldest visible key; the cache has
+                // then handed that block back and its table entry is -1.  Such a block is not loaded at all (its
+                // keys are masked and its rows of V are zeroed in shared memory), and its table entry is not read.
+                it.first_block = it.lo >= it.chunk_begin + BLOCK_KEYS ? 1 : 0;
                 const int* table = p.block_table + (size_t)row_slot[b] * p.table_stride + it.chunk_begin / BLOCK_KEYS;
-                it.row0 = (table[0] * p.nkv + it.kvh) * BLOCK_KEYS;
+                it.row0 = it.first_block == 0 ? (table[0] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
                 it.row1 = it.blocks_here > 1 ? (table[1] * p.nkv + it.kvh) * BLOCK_KEYS : 0;
                 items[threadIdx.x - 64] = it;
             }
@@ -247,7 +251,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                     tma_load_2d(q_of(s) + j * (NQ * 128), &map_q, kq_full + 8 * s, j * 64, it.b * p.nh + it.kvh * g);
                 } else {
                     const int kb = (j - 2) >> 2, x = j & 1;
-                    if (kb >= it.blocks_here) return;
+                    if (kb >= it.blocks_here || kb < it.first_block) return;
                     const int row = kb == 0 ? it.row0 : it.row1;
                     if (((j - 2) & 2) == 0) tma_load_2d(k_of(s) + x * HALF_K + kb * BOX, &map_k, kq_full + 8 * s, x * 64, row);
                     else tma_load_2d(v_of(s) + (kb * 2 + x) * BOX, &map_v, v_full + 8 * s, x * 64, row);
@@ -256,8 +260,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             const int ahead = min(STAGES, n_items);
             if (lane < ahead) {
                 const Item& it = items[lane];
-                mbar_expect_tx(kq_full + 8 * lane, Q_BYTES + it.blocks_here * BOX * 2);
-                mbar_expect_tx(v_full + 8 * lane, it.blocks_here * BOX * 2);
+                mbar_expect_tx(kq_full + 8 * lane, Q_BYTES + (it.blocks_here - it.first_block) * BOX * 2);
+                mbar_expect_tx(v_full + 8 * lane, (it.blocks_here - it.first_block) * BOX * 2);
             }
             __syncwarp();
             const int my_n = lane / 10, my_j = lane % 10;     // three items of ten boxes each
@@ -273,8 +277,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 freed = __shfl_sync(0xffffffffu, freed, 0);
                 if (!freed) break;
                 if (lane == 0) {
-                    mbar_expect_tx(kq_full + 8 * s, Q_BYTES + it.blocks_here * BOX * 2);
-                    mbar_expect_tx(v_full + 8 * s, it.blocks_here * BOX * 2);
+                    mbar_expect_tx(kq_full + 8 * s, Q_BYTES + (it.blocks_here - it.first_block) * BOX * 2);
+                    mbar_expect_tx(v_full + 8 * s, (it.blocks_here - it.first_block) * BOX * 2);
                 }
                 __syncwarp();
                 if (lane < 10) load_box(it, s, lane);
@@ -387,9 +391,10 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                     const uint32_t dst = p_dst + kb * (NQ * 128) + h * 128 + ((((uint32_t)kin >> 3) ^ (h & 7)) << 4) + (kin & 7) * 2;
                     asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&pb)) : "memory");
                 }
-                // rows of V at and past the sequence's length have never been written by this sequence:
-                // their weight is 0, but 0 x (whatever bits lie there) must stay 0
-                if (key >= it.kv_len && kb < it.blocks_here) {
+                // rows of V at and past the sequence's length have never been written by this sequence, and the rows of
+                // a block that was not loaded hold what an earlier chunk left: their weight is 0, but
+                // 0 x (whatever bits lie there) must stay 0
+                if ((key >= it.kv_len || kb < it.first_block) && kb < it.blocks_here) {
                     for (int x = 0; x < 2; x++) {
                         const uint32_t rowp = v_of(s) + (kb * 2 + x) * BOX + kin * 128;
                         if (x == 0 && !mbar_wait(v_full + 8 * s, (uint32_t)((n / STAGES) & 1), abort_flag, p.status, 125)) break;

@@ -36,6 +36,7 @@ struct AttnParams {
     int table_stride, block_tokens, nh, nkv, d, window, tokens_per_tile, heads_per_tile, head_chunks;
     int split_keys, max_splits;
     float scale;
+    int* status;            // may be null; [0] = 2 when a row is longer than max_splits * split_keys covers
 };
 
 template <typename T>
@@ -191,6 +192,13 @@ __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
     const int pos = p.kv_lens[b] - T_b + (t - p.cu_seqlens[b]);
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int s_begin = lo / p.split_keys, s_end = pos / p.split_keys + 1;  // chunks that hold visible keys
+    if (s_end > p.max_splits) {
+        // The row is longer than the chunks the caller made room for: its last keys were never visited and the
+        // partials of chunk max_splits and beyond do not exist.  No truncated softmax is returned: the row's
+        // output stays as it was, and the status word says so.
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, 2);
+        return;
+    }
     const float* ml = p.part_ml + (size_t)row * p.max_splits * 2;
     float M = -INFINITY;
     for (int s = s_begin; s < s_end; s++) M = fmaxf(M, ml[2 * s]);
@@ -211,8 +219,9 @@ __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
 // (part_acc [token, head, split, d], part_ml [token, head, split, (max, sum)]).
 int hymt2_attention_merge_launch(void* out, int dtype, const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
                                  float* part_acc, float* part_ml, int tokens, int nh, int d, int window, int split_keys,
-                                 int max_splits, cudaStream_t stream) {
+                                 int max_splits, cudaStream_t stream, int* status) {
     AttnParams p{};
+    p.status = status;
     p.out = out; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
     p.part_acc = part_acc; p.part_ml = part_ml; p.nh = nh; p.d = d; p.window = window;
     p.split_keys = split_keys; p.max_splits = max_splits;
@@ -232,7 +241,7 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
                                    const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
                                    int batch, int tokens, int max_new_tokens, int nh, int nkv, int d,
                                    float scale, int window, int split_keys, int max_splits,
-                                   float* part_acc, float* part_ml, cudaStream_t stream) {
+                                   float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
     if (tokens == 0 || batch == 0) return HYMT2_OK;
     HYMT2_REQUIRE(batch > 0 && tokens > 0 && nh > 0 && nkv > 0, "attention: bad sizes");
     HYMT2_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -253,6 +262,7 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
     p.head_chunks = (g + p.heads_per_tile - 1) / p.heads_per_tile;
     p.split_keys = split_keys; p.max_splits = split_keys > 0 ? max_splits : 1;
     p.scale = scale;
+    p.status = status;
     const size_t smem = sizeof(float) * ((size_t)ROWS * d + (size_t)KEY_TILE * (d + 1) + (size_t)KEY_TILE * d + ROWS * KEY_TILE);
     dim3 grid((max_new_tokens + p.tokens_per_tile - 1) / p.tokens_per_tile, nkv * p.head_chunks, batch * p.max_splits);
     HYMT2_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "attention: grid too large (batch %d x splits %d)", batch, p.max_splits);
@@ -312,8 +322,9 @@ HYMT2_API int hymt2_attention_decode_noalloc(void* out, const void* q, const voi
                                              const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int rows,
                                              int nh, int nkv,
                                              int d, float scale, int window, int split_keys, int max_splits,
-                                             cudaStream_t stream) {
+                                             int* status, cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(status != nullptr, "attention_decode_noalloc: a status word (one int on the device) is needed");
     HYMT2_REQUIRE(rows > 0, "attention_decode_noalloc: rows %d must be positive", rows);
     HYMT2_REQUIRE(split_keys > 0 && max_splits > 0, "attention_decode_noalloc: split_keys and max_splits must be positive");
     HYMT2_REQUIRE(nh > 0 && d > 0, "attention_decode_noalloc: bad sizes");
@@ -335,5 +346,5 @@ HYMT2_API int hymt2_attention_decode_noalloc(void* out, const void* q, const voi
     float* part_ml = scratch + (size_t)rows * nh * max_splits * d;
     return hymt2_attention_simt(out, q, k_cache, v_cache, dtype, block_table, table_stride, block_tokens, cu_seqlens,
                                 slot_ids, kv_lens, rows, rows, 1, nh, nkv, d, scale, window, split_keys, max_splits,
-                                part_acc, part_ml, stream);
+                                part_acc, part_ml, stream, status);
 }

@@ -22,6 +22,11 @@
 // Limits and rules.
 //   * rows * nh * max_splits * (d + 2) must not exceed HYMT2_NOALLOC_SCRATCH_FLOATS;
 //     a larger request is refused with HYMT2_ERR_ARGUMENT and a message, nothing runs.
+//   * max_splits * split_keys must cover the longest row: the lengths live on the device, so
+//     the host side of this call cannot check it.  The kernels do: a row with
+//     kv_len > max_splits * split_keys is not computed (its row of `out` keeps what it held,
+//     no partial beyond the array is touched) and status[0] is set to 2.  Read the status
+//     word when in doubt; it is only ever written on that fault.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress) with that device current.  Make that first call outside
 //     of any stream capture.
@@ -43,12 +48,14 @@ extern "C" {
 // out, q: [rows, nh * d]; k_cache, v_cache: one layer's planes [block][nkv][block_tokens][d];
 // dtype: 0 = float32, 1 = bfloat16 (q, out and the cache alike); block_table: int32
 // [slot][table_stride]; cu_seqlens: int32 [rows + 1] = 0, 1, ..., rows (row b holds token b);
-// slot_ids, kv_lens: int32 [rows] (slot < 0: the row is skipped); kv_lens counts the new token.  Returns 0, or a negative code with hymt2_last_error() set.
+// slot_ids, kv_lens: int32 [rows] (slot < 0: the row is skipped); kv_lens counts the new token;
+// status: one int32 on the device, zeroed by the caller (see the rules above).  Returns 0, or a
+// negative code with hymt2_last_error() set.
 int hymt2_attention_decode_noalloc(void* out, const void* q, const void* k_cache, const void* v_cache, int dtype,
                                    const int* block_table, int table_stride, int block_tokens,
                                    const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int rows, int nh,
                                    int nkv, int d, float scale, int window, int split_keys, int max_splits,
-                                   cudaStream_t stream);
+                                   int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

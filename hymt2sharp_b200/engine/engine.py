@@ -46,11 +46,14 @@ def require_gpu(device) -> torch.device:
     return device
 
 
-def make_context(cache, entries: list, vocab: int, dtype, device, status, meta_buffer=None):
+def make_context(cache, entries: list, vocab: int, dtype, device, status, meta_buffer=None,
+                 max_positions: int | None = None):
     """Checks the entries, takes the cache blocks that their tokens need (all or nothing) and
     builds the StepContext: packed tokens, each token's batch row and position, the rows'
     offsets, slots and lengths.  Returns (context, wanted rows or None, their count, plan);
-    `plan` goes to cache.end_step once the step has been launched."""
+    `plan` goes to cache.end_step once the step has been launched.  `max_positions`: the longest
+    sequence that the model's position encoding was made for (config.json's
+    max_position_embeddings); a step that would go past it is refused before anything changed."""
     # whole arrays at a time: a prompt of thousands of tokens costs the host microseconds, not one Python step a token
     tokens, token_seq, token_pos, cu, slots, kv_lens, want = [], [], [], [0], [], [], []
     starts, news = [], []
@@ -64,6 +67,9 @@ def make_context(cache, entries: list, vocab: int, dtype, device, status, meta_b
         if n and (int(ids.min()) < 0 or int(ids.max()) >= vocab):
             bad = ids[(ids < 0) | (ids >= vocab)][0]
             raise EngineError(f"token id {int(bad)} is outside the vocabulary of {vocab}")
+        if max_positions is not None and start + n > max_positions:
+            raise EngineError(f"slot {e.slot} would hold {start + n} tokens; the model's max_position_embeddings is "
+                              f"{max_positions}")
         for w in e.want:
             if not (0 <= int(w) < n):
                 raise EngineError(f"wanted place {w} is outside the {n} tokens of the entry")
@@ -117,6 +123,7 @@ class Engine:
             self.status = ops.device_status(self.device)
             self._meta = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.vocab = spec.vocab
+        self.max_positions = spec.max_positions
         self.steps_run = 0
 
     # -- slots ------------------------------------------------------------------
@@ -130,6 +137,18 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forgets the sequence in `slot` from position `length` on; the next step of that slot goes on from
+        there (src/HyMT2Sharp/HunyuanDenseModel.cs:187-240, TruncateCache).  Whole blocks behind the new end go
+        back to the pool.  A layer group with a window may already have handed back blocks that the shorter
+        sequence would need again: that is refused (CacheError), nothing changes."""
+        with torch.cuda.device(self.device):
+            self.cache.truncate(slot, int(length))
+
+    def reset(self, slot: int) -> None:
+        """The slot keeps its place in the batch and starts over as an empty sequence (ResetCache)."""
+        self.truncate(slot, 0)
+
     # -- the step ---------------------------------------------------------------
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Runs one step; returns float32 logits [wanted places, vocab] on the device, in the
@@ -139,7 +158,7 @@ class Engine:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
             ctx, want, num_want, plan = make_context(self.cache, entries, self.vocab, self.dtype, self.device,
-                                                     self.status, self._meta_buffer)
+                                                     self.status, self._meta_buffer, self.max_positions)
             logits = self.model.forward(ctx, want, num_want)
             self.cache.end_step(plan)
         self.steps_run += 1
@@ -152,10 +171,15 @@ class Engine:
 
     def check(self) -> None:
         """Waits for the device and raises if a kernel flagged a fault (a token id outside the
-        embedding table, a bounded wait that gave up)."""
+        embedding table, a bounded wait that gave up).  The engine stays usable: the status word is
+        cleared, and so are the arrival counters that kernels share between launches (a kernel that
+        gave up may have left them half counted, and every kernel relies on finding them at zero);
+        what the faulted step computed is not to be trusted, the cache keeps the tokens it was given."""
         code = int(self.status[0].item())
         if code != 0:
-            self.status.zero_()
+            with torch.cuda.device(self.device):
+                self.status.zero_()
+                ops.reset_counters(self.device)
             raise EngineError(f"a kernel reported device status {code}")
 
     # -- convenience --------------------------------------------------------------

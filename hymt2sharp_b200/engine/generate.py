@@ -219,6 +219,14 @@ def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_tok
     params = [sampling] * len(prompts) if isinstance(sampling, SamplingParams) else list(sampling)
     if len(params) != len(prompts):
         raise ValueError("one SamplingParams for every prompt is needed")
+    limit = getattr(engine, "max_positions", None)
+    if limit is not None:
+        # checked before anything runs, as the reference's callers refuse a prompt that does not fit the context
+        # (src/HyMT2Sharp.Server/ChatCompletionService.cs:123-124); the last sampled token is never fed back
+        for i, p in enumerate(prompts):
+            if len(p) + max(0, max_new_tokens - 1) > limit:
+                raise ValueError(f"request {i}: {len(p)} prompt tokens + {max_new_tokens} new ones go past the model's "
+                                 f"max_position_embeddings of {limit}")
     max_batch = max_batch or engine.cache.max_slots
     capacity = engine.cache.free_tokens()
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, max_batch, capacity, engine.cache.block_tokens)

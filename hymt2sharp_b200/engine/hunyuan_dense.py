@@ -37,7 +37,7 @@ def build_spec(cfg: HunyuanDenseConfig) -> ModelSpec:
     return ModelSpec(
         vocab=cfg.vocab_size, hidden=cfg.hidden_size, embedding="model.embed_tokens.weight", layers=layers,
         final_norm=PartSpec("rmsnorm", dict(dim=cfg.hidden_size, eps=cfg.rms_norm_eps, weight="model.norm.weight")),
-        head=None if cfg.tie_word_embeddings else "lm_head.weight")
+        head=None if cfg.tie_word_embeddings else "lm_head.weight", max_positions=cfg.max_position_embeddings)
 
 
 def tensor_shapes(cfg: HunyuanDenseConfig):

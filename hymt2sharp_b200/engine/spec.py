@@ -28,6 +28,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: str | None                  # checkpoint name of the [vocab, hidden] head; None = the embedding table
     order: list[Run] = field(default_factory=list)
+    max_positions: int | None = None  # the longest sequence the model takes (None: whatever the cache holds)
 
     def __post_init__(self):
         if not self.order:

@@ -57,23 +57,29 @@ def _time(fn, warmup: int, iters: int, graph: bool) -> float:
     return e0.elapsed_time(e1) / calls * 1000.0
 
 
-def gemm(a) -> None:
-    epi = {"store": ops.EPILOGUE_STORE, "accumulate": ops.EPILOGUE_ACCUMULATE, "swiglu": ops.EPILOGUE_SWIGLU}[a.epilogue]
-    rows = 2 * a.out if epi == ops.EPILOGUE_SWIGLU else a.out
-    ws = [(torch.randn(rows, a.inner, device=DEV) / math.sqrt(a.inner)).to(BF) for _ in range(a.copies)]
-    x = torch.randn(a.tokens, a.inner, device=DEV).to(BF)
-    cdt = torch.float32 if (epi == ops.EPILOGUE_ACCUMULATE or a.float_out) else BF
-    out = torch.zeros(a.tokens, a.out, device=DEV, dtype=cdt)
+def measure_gemm(tokens: int, out_features: int, inner: int, epilogue: str = "store", float_out: bool = False,
+                 copies: int = 8, warmup: int = 3, iters: int = 20, graph: bool = True) -> dict:
+    """One tensor-core product alone: microseconds a call, its flops and the bytes of weights it streams."""
+    epi = {"store": ops.EPILOGUE_STORE, "accumulate": ops.EPILOGUE_ACCUMULATE, "swiglu": ops.EPILOGUE_SWIGLU}[epilogue]
+    rows = 2 * out_features if epi == ops.EPILOGUE_SWIGLU else out_features
+    ws = [(torch.randn(rows, inner, device=DEV) / math.sqrt(inner)).to(BF) for _ in range(copies)]
+    x = torch.randn(tokens, inner, device=DEV).to(BF)
+    cdt = torch.float32 if (epi == ops.EPILOGUE_ACCUMULATE or float_out) else BF
+    out = torch.zeros(tokens, out_features, device=DEV, dtype=cdt)
     status = ops.device_status(DEV)
     i = [0]
 
     def fn():
-        ops.gemm_tc(out, x, ws[i[0] % a.copies], epi, status)
+        ops.gemm_tc(out, x, ws[i[0] % copies], epi, status)
         i[0] += 1
-    us = _time(fn, a.warmup, a.iters, a.graph)
-    flops = 2.0 * a.tokens * rows * a.inner
-    print(f"gemm_tc tokens={a.tokens} out={a.out} inner={a.inner} epilogue={a.epilogue}: {us:.1f} us  "
-          f"{flops / us / 1e6:.1f} TFLOP/s  weights {rows * a.inner * 2 / us / 1e3:.0f} GB/s")
+    us = _time(fn, warmup, iters, graph)
+    return {"us": us, "flops": 2.0 * tokens * rows * inner, "bytes": rows * inner * 2.0}
+
+
+def gemm(a) -> None:
+    m = measure_gemm(a.tokens, a.out, a.inner, a.epilogue, a.float_out, a.copies, a.warmup, a.iters, a.graph)
+    print(f"gemm_tc tokens={a.tokens} out={a.out} inner={a.inner} epilogue={a.epilogue}: {m['us']:.1f} us  "
+          f"{m['flops'] / m['us'] / 1e6:.1f} TFLOP/s  weights {m['bytes'] / m['us'] / 1e3:.0f} GB/s")
 
 
 def _cache(batch: int, context: int, nkv: int, d: int):
@@ -84,7 +90,23 @@ def _cache(batch: int, context: int, nkv: int, d: int):
     return kp, vp, table
 
 
+def measure_attention_decode(batch: int, context: int, heads: int, kv_heads: int, head_dim: int = 128, kernel: str = "tc",
+                             copies: int = 8, warmup: int = 3, iters: int = 20, graph: bool = True) -> dict:
+    """The decode attention alone over `batch` sequences of `context` cached tokens: microseconds a call and the
+    bytes of keys and values it has to read."""
+    from types import SimpleNamespace
+    a = SimpleNamespace(batch=batch, context=context, heads=heads, kv_heads=kv_heads, head_dim=head_dim, kernel=kernel,
+                        copies=copies, warmup=warmup, iters=iters, graph=graph)
+    return _attention_decode(a)
+
+
 def attention_decode(a) -> None:
+    m = _attention_decode(a)
+    print(f"attention_decode[{a.kernel}] batch={a.batch} context={a.context} heads={a.heads}/{a.kv_heads} d={a.head_dim}: "
+          f"{m['us']:.1f} us  cache {m['bytes'] / m['us'] / 1e3:.0f} GB/s ({m['bytes'] / 1e6:.1f} MB)")
+
+
+def _attention_decode(a) -> dict:
     B, nh, nkv, d = a.batch, a.heads, a.kv_heads, a.head_dim
     caches = [_cache(B, a.context, nkv, d) for _ in range(a.copies)]
     table = caches[0][2]
@@ -110,12 +132,24 @@ def attention_decode(a) -> None:
         else:
             ops.attention_decode(out, q, kp, vp, table, cu, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, cnt)
     us = _time(fn, a.warmup, a.iters, a.graph)
-    nbytes = B * a.context * nkv * d * 2 * 2
-    print(f"attention_decode[{a.kernel}] batch={B} context={a.context} heads={nh}/{nkv} d={d}: {us:.1f} us  "
-          f"cache {nbytes / us / 1e3:.0f} GB/s ({nbytes / 1e6:.1f} MB)")
+    return {"us": us, "bytes": B * a.context * nkv * d * 2 * 2.0, "flops": 4.0 * B * a.context * nh * d}
+
+
+def measure_attention_prefill(tokens: int, heads: int, kv_heads: int, head_dim: int = 128, batch: int = 1,
+                              warmup: int = 3, iters: int = 20, graph: bool = True) -> dict:
+    """The prompt attention alone over `batch` prompts of `tokens` tokens: microseconds a call and its (causal) flops."""
+    from types import SimpleNamespace
+    return _attention_prefill(SimpleNamespace(tokens=tokens, heads=heads, kv_heads=kv_heads, head_dim=head_dim, batch=batch,
+                                              warmup=warmup, iters=iters, graph=graph))
 
 
 def attention_prefill(a) -> None:
+    m = _attention_prefill(a)
+    print(f"attention_prefill_tc batch={a.batch} tokens={a.tokens} heads={a.heads}/{a.kv_heads} d={a.head_dim}: {m['us']:.1f} us  "
+          f"{m['flops'] / m['us'] / 1e6:.1f} TFLOP/s (causal)")
+
+
+def _attention_prefill(a) -> dict:
     nh, nkv, d, T = a.heads, a.kv_heads, a.head_dim, a.tokens
     kp, vp, table = _cache(a.batch, T, nkv, d)
     q = torch.randn(a.batch * T, nh * d, device=DEV).to(BF)
@@ -126,8 +160,7 @@ def attention_prefill(a) -> None:
     status = ops.device_status(DEV)
     fn = lambda: ops.attention_prefill_tc(out, q, kp, vp, table, cu, slots, kv, a.batch, T, nh, nkv, d, 1 / math.sqrt(d), 0, status)
     us = _time(fn, a.warmup, a.iters, a.graph)
-    flops = 4.0 * nh * d * (T * (T + 1) / 2) * a.batch
-    print(f"attention_prefill_tc batch={a.batch} tokens={T} heads={nh}/{nkv} d={d}: {us:.1f} us  {flops / us / 1e6:.1f} TFLOP/s (causal)")
+    return {"us": us, "flops": 4.0 * nh * d * (T * (T + 1) / 2) * a.batch, "bytes": a.batch * T * (2 * nh + 2 * nkv) * d * 2.0}
 
 
 def small(a) -> None:

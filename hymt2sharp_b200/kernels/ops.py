@@ -164,7 +164,9 @@ _status: dict = {}
 
 def device_status(device) -> torch.Tensor:
     """The int32[4] status word of a device: kernels set [0] when a device-side check fails or a
-    bounded wait gives up (1: token id outside the table; 101-103: a wait of the tensor-core GEMM)."""
+    bounded wait gives up (1: token id outside the table; 2: a sequence longer than the split attention was given
+    room for; 101-105: a wait of the tensor-core GEMM; 108-119: of the prompt attention; 120-129: of the decode
+    attention)."""
     device = torch.device(device)
     key = device.index if device.index is not None else torch.cuda.current_device()
     if key not in _status:
@@ -367,8 +369,13 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                    block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor,
                    kv_lens: torch.Tensor, batch: int, max_new_tokens: int, nh: int, nkv: int, d: int,
                    scale: float, window: int = 0, split_keys: int = 0, max_splits: int = 0,
-                   part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> None:
-    """Causal grouped-query attention of the new tokens over the paged cache (CUDA cores)."""
+                   part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
+                   status: torch.Tensor | None = None) -> None:
+    """Causal grouped-query attention of the new tokens over the paged cache (CUDA cores).  With a split, a row
+    longer than max_splits * split_keys is left as it was and status[0] (the device's status word unless another is
+    given) becomes 2."""
+    if status is None:
+        status = device_status(out.device)
     _need(out, "out", None, 2); _need(q, "q", out.dtype, 2)
     _need(k_plane, "k_plane", out.dtype, 4); _need(v_plane, "v_plane", out.dtype, 4)
     T = out.shape[0]
@@ -389,7 +396,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_
                                        _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(T),
                                        c_int(max_new_tokens), c_int(nh), c_int(nkv), c_int(d), c_float(scale),
                                        c_int(window), c_int(split_keys), c_int(max_splits), _ptr(part_acc),
-                                       _ptr(part_ml), _stream()), "attention_simt", 2 if split_keys > 0 else 1)
+                                       _ptr(part_ml), _stream(), _ptr(status)), "attention_simt", 2 if split_keys > 0 else 1)
 
 
 def attention_decode_tc_scratch(rows: int, nh: int, nkv: int, d: int, max_splits: int) -> tuple[int, int, int]:
@@ -458,6 +465,19 @@ def zeroed_counters(device, n: int) -> torch.Tensor:
     if old is None or old[-1].numel() < n:
         _counters[key] = (old or []) + [torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)]
     return _counters[key][-1]
+
+
+def reset_counters(device) -> None:
+    """Zeroes every arrival counter that kernels of this device share between launches (the split products'
+    and the attention kernels'), on the current stream: after a kernel gave up in mid-count."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    for t in _counters.get(key) or []:
+        t.zero_()
+    ws, cnt, old = _tc_scratch.get(key, (None, None, []))
+    for t in [cnt] + [o for o in old if o.dtype == torch.int32]:
+        if t is not None:
+            t.zero_()
 
 
 def attention_decode(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,

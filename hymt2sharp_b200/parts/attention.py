@@ -30,8 +30,8 @@ class GQAAttention:
                  q_norm: str | None = None, k_norm: str | None = None, window: int | None = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} kv heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim} must be a multiple of 16, at most 256")
+        if head_dim % 8 or head_dim > 256:   # what the general kernels take; the tensor-core kernels take 64 and 128
+            raise ValueError(f"head_dim {head_dim} must be a multiple of 8, at most 256")
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
         self.eps, self.qk_norm, self.window = float(eps), bool(qk_norm), int(window or 0)
         self.names = dict(q=q_proj, k=k_proj, v=v_proj, o=o_proj, qn=q_norm, kn=k_norm)

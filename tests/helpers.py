@@ -50,6 +50,20 @@ CONFIGS = {
                           rope_theta=50000.0, rope_scaling={"type": "dynamic", "alpha": 4.0}, rms_norm_eps=1e-5,
                           use_qk_norm=True, tie_word_embeddings=False, max_position_embeddings=4096),
               seed=4, sigma=0.03, gain_dtype="bfloat16"),
+    # H with a window of 100 positions: the cache hands blocks back while a sequence grows, so the tcgen05
+    # attention kernels meet block tables with -1 entries below the oldest visible key
+    "HW": dict(config=dict(architectures=[ARCH], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=128, intermediate_size=392, vocab_size=777,
+                           rope_theta=50000.0, rope_scaling={"type": "dynamic", "alpha": 4.0}, rms_norm_eps=1e-5,
+                           use_qk_norm=True, tie_word_embeddings=False, sliding_window=100,
+                           max_position_embeddings=4096),
+               seed=5, sigma=0.03, gain_dtype="bfloat16"),
+    # heads of 24: a multiple of 8 that is no multiple of 16, three heads on one kv head, odd sizes all round
+    "S": dict(config=dict(architectures=[ARCH], num_hidden_layers=2, hidden_size=88, num_attention_heads=3,
+                          num_key_value_heads=1, head_dim=24, intermediate_size=136, vocab_size=301,
+                          rope_theta=20000.0, rms_norm_eps=1e-6, use_qk_norm=True,
+                          tie_word_embeddings=True, max_position_embeddings=2048),
+              seed=6, sigma=0.05, gain_dtype="float32"),
 }
 
 # Tolerances, fixed before the kernels were tuned.  32-bit: differences come from the order of

@@ -24,7 +24,7 @@ def _poison(eng):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W", "M", "H"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "M", "H", "HW", "S"])
 def test_long_decoding_from_the_first_token(name, dtype, model_dirs, plain_models):
     """A one-token prompt, then 420 tokens one by one (across block ends and past the length at
     which decode attention starts to split its keys), in a cache whose unwritten rows are NaN."""
@@ -137,6 +137,55 @@ def test_window_edge(dtype, new):
             else:
                 assert o[i].abs().max() < 1.0, f"query at {p} must not see key {hot}"
         assert ((o[-1] - 7.0).abs().max() < 0.05) == visible_from_last
+
+
+def _fast_attention(q, kp, vp, table, L, new, nh, nkv, d, window):
+    """The attention of one sequence through the kernel that the bfloat16 engine picks for it."""
+    from types import SimpleNamespace
+    from hymt2sharp_b200.kernels import fast
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ctx = SimpleNamespace(decode=new == 1, max_kv_len=L, num_tokens=new, num_seqs=1, max_new_tokens=new,
+                          cu_seqlens=i32([0, new]), slot_ids=i32([0]), kv_lens=i32([L]))
+    out = torch.zeros(new, nh * d, dtype=q.dtype, device=DEV)
+    assert fast.try_attention(out, q, kp, vp, table, ctx, nh, nkv, d, 1 / math.sqrt(d), window), "no fast kernel took it"
+    return out.float()
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("L, new", [(900, 1), (900, 130), (300, 300)])
+def test_one_far_key_decides_in_the_tensor_core_kernels(d, L, new):
+    """As above, through the kernels that a bfloat16 engine runs for heads of 64 and 128: the streaming decode
+    kernel, the tcgen05 decode kernel and the tcgen05 prompt kernel."""
+    nh, nkv = 4, 2
+    q, kp, vp, table, _ = _attention_case("bfloat16", L, new, nh, nkv, d, 0, hot_key=5)
+    out = _fast_attention(q, kp, vp, table, L, new, nh, nkv, d, 0)
+    first = L - new
+    assert (out[max(0, 5 - first):] - 7.0).abs().max() < 0.05, "a query lost the far key"
+    if first < 5:
+        assert out[:5 - first].abs().max() < 1.0
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("new", [1, 40, 200])
+@pytest.mark.parametrize("L, window", [(448, 128), (512, 128), (449, 128), (400, 100), (641, 257)])
+def test_window_edge_in_the_tensor_core_kernels(d, new, L, window):
+    """The oldest visible key and the one just outside, with the window's lower end in the second cache block of a
+    128-key chunk (L 448), at a chunk's first key (L 512), one past a 64-key tile's first key (L 449: the newest
+    position opens a tile), and off every boundary."""
+    nh, nkv = 4, 2
+    last = L - 1
+    for hot in (last - window + 1, last - window):
+        q, kp, vp, table, _ = _attention_case("bfloat16", L, new, nh, nkv, d, window, hot_key=hot)
+        # blocks that lie wholly below the oldest key of the FIRST query are handed back by a window cache
+        first_lo = max(0, (L - new) - window + 1)
+        table[0, : first_lo // 64] = -1
+        out = _fast_attention(q, kp, vp, table, L, new, nh, nkv, d, window)
+        for i in range(new):
+            p = L - new + i
+            if p - window + 1 <= hot <= p:
+                assert (out[i] - 7.0).abs().max() < 0.05, f"query at {p} should see key {hot}"
+            else:
+                assert out[i].abs().max() < 1.0, f"query at {p} must not see key {hot}"
 
 
 def test_errors_leave_the_engine_usable(model_dirs, plain_models):

@@ -427,6 +427,46 @@ def test_gemm_tcgen05_epilogues(T, N, K):
     assert status.tolist() == [0, 0, 0, 0]
 
 
+# the shapes of the full-size models' products: few tokens (weight rows on the 128-row side, K cut over clusters or through the
+# global workspace, the vocabulary's last tile of 114 rows) and a prompt's worth (the persistent kernel with its chosen tile width,
+# 128-wide tiles where the product adds into the residual)
+@pytest.mark.parametrize("T, N, K, epilogue, cdt", [
+    (8, 120818, 2048, "store", torch.float32), (1, 120818, 2048, "store", torch.float32), (64, 128167, 4096, "store", torch.float32),
+    (8, 6144, 2048, "swiglu", torch.bfloat16), (64, 6144, 2048, "swiglu", torch.bfloat16), (8, 14336, 4096, "swiglu", torch.bfloat16),
+    (8, 2048, 6144, "add", torch.float32), (8, 2048, 2048, "add", torch.float32), (8, 3072, 2048, "store", torch.bfloat16),
+    (2048, 6144, 2048, "swiglu", torch.bfloat16), (2048, 2048, 2048, "add", torch.float32), (2048, 2048, 6144, "add", torch.float32),
+    (2048, 3072, 2048, "store", torch.bfloat16), (4096, 8192, 3072, "swiglu", torch.bfloat16)])
+def test_gemm_tcgen05_at_full_size_shapes(T, N, K, epilogue, cdt):
+    ops = _ops()
+    torch.manual_seed(N % 1000 + T)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    a = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    rows_w = 2 * N if epilogue == "swiglu" else N
+    w = (torch.randn(rows_w, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    ref = torch.empty(T, rows_w, dtype=torch.float64, device=DEV)
+    for r0 in range(0, rows_w, 16384):   # in pieces: the float64 copy of a whole vocabulary table need not exist
+        ref[:, r0:r0 + 16384] = a.double() @ w[r0:r0 + 16384].double().T
+    if epilogue == "store":
+        out = torch.full((T, N), 7.0, dtype=cdt, device=DEV)
+        ops.gemm_tc(out, a, w, ops.EPILOGUE_STORE, status)
+        want = ref
+    elif epilogue == "add":
+        base = torch.randn(T, N, device=DEV)
+        out = base.clone()
+        ops.gemm_tc(out, a, w, ops.EPILOGUE_ACCUMULATE, status)
+        want = base.double() + ref
+    else:
+        out = torch.empty(T, N, dtype=cdt, device=DEV)
+        ops.gemm_tc(out, a, w, ops.EPILOGUE_SWIGLU, status)
+        g, u = ref[:, :N], ref[:, N:]
+        want = g / (1 + torch.exp(-g)) * u
+    tol = dict(rtol=1e-4, atol=1e-4) if cdt == torch.float32 else _tol(cdt)   # sums of thousands of bfloat16 products
+    err = (out.double() - want).abs()
+    worst = int(err.argmax())
+    assert torch.allclose(out.double(), want, **tol), f"max error {float(err.max()):.3e} at {divmod(worst, N)}"
+    assert status.tolist() == [0, 0, 0, 0]
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_take():
     ops = _ops()
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
@@ -442,8 +482,9 @@ def test_gemm_tcgen05_refuses_what_it_cannot_take():
     assert torch.allclose(out.double(), a.double() @ w.double().T, rtol=2e-5, atol=2e-5)
 
 
+# (32 heads on one kv head is what the tcgen05 decode kernel refuses and this kernel takes over)
 @pytest.mark.parametrize("nh, nkv, d, window", [(16, 4, 128, 0), (8, 2, 64, 0), (6, 2, 64, 300), (5, 5, 128, 0),
-                                                (12, 2, 128, 0), (8, 8, 64, 70)])
+                                                (12, 2, 128, 0), (8, 8, 64, 70), (32, 1, 128, 0), (40, 2, 128, 90)])
 def test_attention_decode_streaming(nh, nkv, d, window):
     """The bfloat16 decode kernel against the float64 reference, lengths around its chunks of 256
     keys and the cache's blocks of 64, a padding row, and a poisoned cache beyond the lengths."""
@@ -473,6 +514,32 @@ def test_attention_decode_streaming(nh, nkv, d, window):
     ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, window, scale) for i in range(rows)])
     assert torch.allclose(out[:7].double(), ref[:7], **_tol(dtype))
     assert (out[7] == 5.0).all()   # the padding row is left alone
+
+
+def test_attention_decode_streaming_with_more_rows_than_the_tensor_core_kernel_takes():
+    """600 sequences in one step: beyond the 512 rows of the tcgen05 decode kernel, the engine's choice
+    (fast.try_attention) must go to the streaming kernel and give every row its own result."""
+    from types import SimpleNamespace
+    from hymt2sharp_b200.kernels import fast
+    torch.manual_seed(9)
+    nh, nkv, d, rows, dtype = 4, 2, 128, 600, torch.bfloat16
+    rng = np.random.default_rng(4)
+    lens = [int(x) for x in rng.integers(1, 300, rows)]
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    q = torch.randn(rows, nh * d, device=DEV).to(dtype)
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=8)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ctx = SimpleNamespace(decode=True, max_kv_len=max(lens), num_tokens=rows, num_seqs=rows, max_new_tokens=1,
+                          cu_seqlens=torch.arange(rows + 1, dtype=torch.int32, device=DEV),
+                          slot_ids=torch.arange(rows, dtype=torch.int32, device=DEV), kv_lens=i32(lens))
+    out = torch.zeros(rows, nh * d, dtype=dtype, device=DEV)
+    before = _ops().launches
+    assert fast.try_attention(out, q, kp, vp, table, ctx, nh, nkv, d, 1 / math.sqrt(d), 0)
+    assert _ops().launches - before == 1
+    for b in range(0, rows, 37):
+        ref = _ref_attention(q[b].view(1, nh, d), keys[b], vals[b], 1, 0, 1 / math.sqrt(d))
+        assert torch.allclose(out[b:b + 1].double(), ref, **_tol(dtype)), f"row {b}"
 
 
 @pytest.mark.parametrize("nh, nkv, d, window", [(4, 2, 128, 0), (8, 2, 64, 0), (3, 1, 128, 100), (6, 6, 64, 37)])

@@ -20,7 +20,7 @@ def _requests(vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W", "M", "H"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "M", "H", "HW", "S"])
 def test_replay_matches_plain(name, dtype, model_dirs, plain_models):
     plain = plain_models(name)
     vocab = plain.cfg.vocab
