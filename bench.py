@@ -1,15 +1,22 @@
 #!/usr/bin/env python3
-"""Benchmark of the library on one B200: decode tokens per second of Hunyuan dense at the
-1.8B layer sizes with random weights (bfloat16), a batch of 8 sequences that each hold a
-2,048-token prompt, plus a 2,048-token prefill, decode at batch 1 and 64, and the decode
-step's fraction of the measured HBM bandwidth.  Prints ONE JSON line.
+"""Benchmark of the library on one B200: decode tokens per second of Hunyuan dense with random
+weights, a prompt-sized prefill, the decode step's fraction of the measured HBM bandwidth, and
+the dominant kernels alone with their own roofline fractions.  Prints ONE JSON line on standard output.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config 1p8b|4b|7b] [--batch B] [--prefill N] [--decode N] [--dtype bf16|fp32] [--reps R]
+                    [--layers L] [--verify-split] [--profile] [--no-points] [--no-kernels] [--no-graph]
 
-A "step" is one decode step of the whole batch.  `value` is timed on the device with CUDA
-events around K steps of the captured decode graph; `e2e` is the same batch through
-Engine.generate (host token ids in and out every step).  The shape of the program follows
-src/HyMT2Sharp.Benchmark/Program.cs:179-241 (warm-up, timed prefill repetitions, timed decode).
+The default is the Hy-MT2 1.8B layer sizes in bfloat16: a batch of 8 sequences that each hold a 2,048-token
+prompt, a 2,048-token prefill, decode at batch 1 and 64.  `--config 4b` and `--config 7b` run the two larger
+families of sizes with their own workloads (16 prompts of 64 to 4,096 tokens and 256 decode steps; 64 prompts of
+16 to 2,048 tokens and 512 steps).  A "step" is one decode step of the whole batch.  `value` is timed on the device
+with CUDA events around K steps of the captured decode graph; `e2e` is the same batch through Engine.generate
+(host token ids in and out every step).  `--verify-split` adds, under `verify`, the comparison of logits between
+the ways of cutting the work, between the precisions and against the plain implementation of the tests
+(src/HyMT2Sharp.Benchmark/Program.cs:124-177); `--profile` adds per-kernel times of an uncaptured prefill and
+decode (:243-261).  The shape of the program follows src/HyMT2Sharp.Benchmark/Program.cs:179-241 (warm-up, timed
+prefill repetitions reported one by one, timed decode including sampling).
 """
 from __future__ import annotations
 
@@ -26,13 +33,25 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# the Hy-MT2 1.8B layer sizes, random weights: the configuration that the published benchmark names
-SIZES = dict(num_hidden_layers=32, hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
-             intermediate_size=6144, vocab_size=120818, rope_theta=10000.0, rope_alpha=1000.0, rms_norm_eps=1e-5,
-             use_qk_norm=True, tie_word_embeddings=True, max_position_embeddings=8192)
-FULL_LAYERS = 32
-PROMPT = 2048
+COMMON = dict(rope_theta=10000.0, rope_alpha=1000.0, rms_norm_eps=1e-5, use_qk_norm=True, head_dim=128,
+              max_position_embeddings=8192)
+CONFIGS = {
+    # the Hy-MT2 1.8B layer sizes: the configuration that the published benchmark names
+    "1p8b": dict(name="hunyuan-dense-1.8B-sizes", seed=2, layers=32,
+                 sizes=dict(COMMON, hidden_size=2048, num_attention_heads=16, num_key_value_heads=4,
+                            intermediate_size=6144, vocab_size=120818, tie_word_embeddings=True),
+                 workload=dict(batch=8, prompt=(2048, 2048), steps=64)),
+    "4b": dict(name="hunyuan-dense-4B-family-sizes", seed=3, layers=32,
+               sizes=dict(COMMON, hidden_size=3072, num_attention_heads=32, num_key_value_heads=8,
+                          intermediate_size=8192, vocab_size=120818, tie_word_embeddings=True),
+               workload=dict(batch=16, prompt=(64, 4096), steps=256)),
+    "7b": dict(name="hunyuan-dense-7B-family-sizes", seed=4, layers=32,
+               sizes=dict(COMMON, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                          intermediate_size=14336, vocab_size=128167, tie_word_embeddings=False),
+               workload=dict(batch=64, prompt=(16, 2048), steps=512)),
+}
 CONTEXT = 8192
+PREFILL_GROUP_TOKENS = 16384   # prompts go in by groups of at most this many tokens: bounded activation memory
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 
@@ -108,36 +127,124 @@ def reference_arm() -> int:
     return 0
 
 
-def make_model(layers: int, seed: int = 2) -> str:
+def make_model(config: str, layers: int) -> str:
+    """A model folder with random weights of the named sizes (N(0, 0.02), the configuration's seed), in a temporary folder."""
     from hymt2sharp_b200.config import HunyuanDenseConfig
     from hymt2sharp_b200.weights import write_random_model
-    data = dict(SIZES, num_hidden_layers=layers, architectures=["HunYuanDenseV1ForCausalLM"],
-                rope_scaling={"type": "dynamic", "alpha": SIZES["rope_alpha"]})
+    spec = CONFIGS[config]
+    data = dict(spec["sizes"], num_hidden_layers=layers, architectures=["HunYuanDenseV1ForCausalLM"],
+                rope_scaling={"type": "dynamic", "alpha": spec["sizes"]["rope_alpha"]})
     data.pop("rope_alpha")
     cfg = HunyuanDenseConfig.from_dict(data)
     folder = tempfile.mkdtemp(prefix="hymt2_bench_model_")
-    write_random_model(folder, cfg, seed, 0.02)
+    write_random_model(folder, cfg, spec["seed"], 0.02)
     return folder
 
 
-def prefill_flops(cfg, tokens: int, wanted_rows: int) -> float:
+def step_flops(cfg, prompt_lens, wanted_rows: int) -> float:
+    """Flops of a step that runs whole prompts of these lengths (products, causal attention, head on the wanted rows)."""
     per_layer = (cfg.q_size + 2 * cfg.kv_size) * cfg.hidden_size + cfg.hidden_size * cfg.q_size \
         + 3 * cfg.intermediate_size * cfg.hidden_size
+    tokens = sum(prompt_lens)
     gemm = 2.0 * tokens * per_layer * cfg.num_hidden_layers
-    attn = 4.0 * cfg.num_attention_heads * cfg.head_dim * (tokens * (tokens + 1) / 2) * cfg.num_hidden_layers
+    attn = sum(4.0 * cfg.num_attention_heads * cfg.head_dim * (n * (n + 1) / 2) for n in prompt_lens) * cfg.num_hidden_layers
     head = 2.0 * wanted_rows * cfg.vocab_size * cfg.hidden_size
     return gemm + attn + head
+
+
+def groups_under_budget(lengths, budget=PREFILL_GROUP_TOKENS):
+    """Index ranges of consecutive prompts whose tokens stay under the budget (a prompt alone may exceed it)."""
+    out, start, used = [], 0, 0
+    for i, n in enumerate(lengths):
+        if i > start and used + n > budget:
+            out.append((start, i))
+            start, used = i, 0
+        used += n
+    out.append((start, len(lengths)))
+    return out
+
+
+def kernel_fractions(cfg, batch: int, prefill_tokens: int, context: int, pk: dict) -> dict:
+    """The dominant kernels alone (captured into a graph, operands rotating so that they come from memory):
+    microseconds, the bytes or flops that the kernel has to move or do, and the fraction of the measured peak
+    (memory bandwidth for the decode kernels, burst tensor throughput for the prompt kernels)."""
+    from hymt2sharp_b200.kernels import microbench as mb
+    H, F, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    big = 2 if V * H * 2 > (1 << 29) else 4
+    runs = {
+        "gate_up_decode": ("hbm", lambda: mb.measure_gemm(batch, F, H, "swiglu", copies=8)),
+        "down_decode": ("hbm", lambda: mb.measure_gemm(batch, H, F, "accumulate", copies=8)),
+        "qkv_decode": ("hbm", lambda: mb.measure_gemm(batch, cfg.q_size + 2 * cfg.kv_size, H, "store", copies=16)),
+        "o_proj_decode": ("hbm", lambda: mb.measure_gemm(batch, H, cfg.q_size, "accumulate", copies=16)),
+        "lm_head_decode": ("hbm", lambda: mb.measure_gemm(batch, V, H, "store", float_out=True, copies=big, iters=8)),
+        "attention_decode": ("hbm", lambda: mb.measure_attention_decode(batch, context, nh, nkv, d, copies=8)),
+        "gate_up_prefill": ("tensor", lambda: mb.measure_gemm(prefill_tokens, F, H, "swiglu", copies=4)),
+        "down_prefill": ("tensor", lambda: mb.measure_gemm(prefill_tokens, H, F, "accumulate", copies=4)),
+        "attention_prefill": ("tensor", lambda: mb.measure_attention_prefill(prefill_tokens, nh, nkv, d)),
+    }
+    out = {}
+    for name, (bound, fn) in runs.items():
+        m = fn()
+        if bound == "hbm":
+            achieved, peak, unit = m["bytes"] / m["us"] / 1e3, pk["hbm_gbs"], "GB/s"
+        else:
+            achieved, peak, unit = m["flops"] / m["us"] / 1e6, pk["bf16_tflops"], "TFLOP/s"
+        out[name] = {"us": round(m["us"], 2), "bound": bound, "achieved": round(achieved, 1), "unit": unit,
+                     "frac": round(achieved / peak, 3)}
+    return out
+
+
+def run_verify(config: str, layers: int) -> dict:
+    """Logits compared between the cuts and the precisions at `layers` layers of the configuration's widths, and the
+    32-bit engine against the plain implementation of the tests at 2 layers."""
+    import numpy as np
+    import torch
+    from hymt2sharp_b200.engine.verify import verify_split
+    vocab = CONFIGS[config]["sizes"]["vocab_size"]
+    rng = np.random.default_rng(11)
+    requests = [rng.integers(0, vocab, n).tolist() for n in (300, 70, 1100)]
+    out = {}
+    folder = make_model(config, layers)
+    try:
+        t0 = time.time()
+        out[f"layers_{layers}"] = verify_split(folder, requests)
+        out[f"layers_{layers}"]["seconds"] = round(time.time() - t0, 1)
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    folder = make_model(config, 2)
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from plain.hunyuan_plain import PlainModel
+        plain = PlainModel(folder)
+        t0 = time.time()
+        res = verify_split(folder, requests, dtypes=("float32",), reference=lambda toks: plain.logits(toks))
+        res["seconds"] = round(time.time() - t0, 1)
+        out["layers_2_against_plain"] = res
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    out["ok"] = all(v["ok"] for v in out.values())
+    torch.cuda.empty_cache()
+    return out
 
 
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=None, help="timed decode steps (default: 64; the workload's own for 4b and 7b)")
+    ap.add_argument("--decode", type=int, default=None, help="the same as --steps (src/HyMT2Sharp.Benchmark --bench-decode)")
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than 32 only where memory or time needs it")
+    ap.add_argument("--config", default="1p8b", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--prefill", type=int, default=2048, help="tokens of the timed prefill (src/HyMT2Sharp.Benchmark --bench-prefill)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--reps", type=int, default=3, help="timed repetitions of the prefill")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has, only where memory or time needs it")
+    ap.add_argument("--verify-split", action="store_true")
+    ap.add_argument("--profile", action="store_true")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the kernels timed alone")
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -145,9 +252,15 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    spec = CONFIGS[args.config]
+    work = spec["workload"]
     warmup = max(3, args.warmup)
-    steps = max(1, args.steps)
+    steps = max(1, args.decode or args.steps or (64 if args.config == "1p8b" else work["steps"]))
+    batch = args.batch or work["batch"]
+    layers = args.layers or spec["layers"]
+    dtype = {"bf16": "bfloat16", "fp32": "float32"}[args.dtype]
 
+    import numpy as np
     import torch
     import hymt2sharp_b200
     from hymt2sharp_b200.engine.decode_session import DecodeSession
@@ -156,51 +269,69 @@ def main() -> int:
     from hymt2sharp_b200.sampling import BatchSampler, GREEDY
 
     pk, pk_source = peaks()
-    folder = make_model(args.layers)
-    point_batches = [] if args.no_points else [1, 64]
-    biggest = max([args.batch] + point_batches)
-    per_seq = -(-(PROMPT + warmup + steps + 8) // 64) * 64
+    verify = run_verify(args.config, layers) if args.verify_split else None
+
+    rng = np.random.default_rng(1234)
+    lo, hi = work["prompt"]
+    uniform = lo == hi
+    vocab = spec["sizes"]["vocab_size"]
+
+    def prompt_lengths(n):
+        return [lo] * n if uniform else [int(x) for x in rng.integers(lo, hi + 1, n)]
+
+    def prompts_of(lengths):
+        return [rng.integers(0, vocab, n).tolist() for n in lengths]
+
+    main_lengths = prompt_lengths(batch)
+    point_batches = [] if (args.no_points or args.config != "1p8b") else [1, 64]
+    reserve = lambda lengths: sum(-(-(n + warmup + steps + 8) // 64) * 64 for n in lengths)
+    capacity = max([reserve(main_lengths), args.prefill + 64] + [reserve([lo] * b) for b in point_batches]) + 4096
+    folder = make_model(args.config, layers)
     try:
-        engine = hymt2sharp_b200.load(folder, dtype="bfloat16", max_tokens=biggest * per_seq + 4096, max_batch=biggest,
+        engine = hymt2sharp_b200.load(folder, dtype=dtype, max_tokens=capacity, max_batch=max([batch] + point_batches),
                                       max_sequence_tokens=CONTEXT)
     finally:
         shutil.rmtree(folder, ignore_errors=True)   # the weights are on the device now; leave nothing in the temporary folder
     cfg = engine.config
-    gen = torch.Generator().manual_seed(1234)
-    rand_prompt = lambda: torch.randint(0, cfg.vocab_size, (PROMPT,), generator=gen).tolist()
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    # ---- prefill of 2,048 tokens: warm-up, then the mean of 3 timed repetitions -----------------
-    prompt = rand_prompt()
+    # ---- prefill of --prefill tokens: warm-up, then the mean of the timed repetitions ----------------------
+    prompt = prompts_of([args.prefill])[0]
     times = []
-    for rep in range(3 + 3):
+    for rep in range(3 + args.reps):
         slot = engine.alloc_slots(1)
         t0, t1 = ev(), ev()
         torch.cuda.synchronize()
         t0.record()
-        engine.step([StepEntry(slot[0], prompt, [PROMPT - 1])])
+        engine.step([StepEntry(slot[0], prompt, [args.prefill - 1])])
         t1.record()
         torch.cuda.synchronize()
         engine.free_slots(slot)
         if rep >= 3:
             times.append(t0.elapsed_time(t1))
     pf_ms = sum(times) / len(times)
-    pf_flops = prefill_flops(cfg, PROMPT, 1)
-    prefill = {"value": PROMPT / pf_ms * 1000.0, "tokens": PROMPT, "ms": pf_ms, "reps_ms": [round(t, 3) for t in times],
-               "frac": pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "peak": pk_source}
+    pf_flops = step_flops(cfg, [args.prefill], 1)
+    prefill = {"value": args.prefill / pf_ms * 1000.0, "tokens": args.prefill, "ms": pf_ms, "reps_ms": [round(t, 3) for t in times],
+               "frac": pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12) if args.dtype == "bf16" else None,
+               "peak": pk_source if args.dtype == "bf16" else "no measured 32-bit peak"}
 
     # ---- decode ----------------------------------------------------------------------------------
-    def decode_run(batch: int, k: int, w: int, sample_clocks: bool):
-        slots = engine.alloc_slots(batch)
-        prompts = [rand_prompt() for _ in range(batch)]
+    def decode_run(lengths: list, k: int, w: int, sample_clocks: bool):
+        n = len(lengths)
+        slots = engine.alloc_slots(n)
+        prompts = prompts_of(lengths)
         firsts = []
-        group = max(1, 16384 // PROMPT)  # prompts go in by groups: bounded activation memory
-        for g0 in range(0, batch, group):
-            entries = [StepEntry(s, p, [PROMPT - 1]) for s, p in zip(slots[g0:g0 + group], prompts[g0:g0 + group])]
+        t0, t1 = ev(), ev()
+        t0.record()
+        for g0, g1 in groups_under_budget(lengths):
+            entries = [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots[g0:g1], prompts[g0:g1])]
             firsts.append(engine.step(entries))
-        sampler = BatchSampler([GREEDY] * batch, engine.device)
+        t1.record()
+        torch.cuda.synchronize()
+        batch_prefill_ms = t0.elapsed_time(t1)
+        sampler = BatchSampler([GREEDY] * n, engine.device)
         first = sampler.sample(torch.cat(firsts), None)
-        session = DecodeSession(engine, slots, sampler, first, PROMPT + w + k + 2, use_graph=not args.no_graph)
+        session = DecodeSession(engine, slots, sampler, first, max(lengths) + w + k + 2, use_graph=not args.no_graph)
         for _ in range(w):
             session.step()
         torch.cuda.synchronize()
@@ -217,53 +348,86 @@ def main() -> int:
         ms = t0.elapsed_time(t1)
         clk = clocks.stop() if sample_clocks else None
         launches = ops.launches - launches0
-        mean_ctx = PROMPT + w + (k + 1) / 2.0
+        mean_tokens = sum(lengths) + n * (w + (k + 1) / 2.0)   # cached tokens that a timed step reads, on average
         engine.check()
         engine.free_slots(slots)
-        return ms, launches, mean_ctx, clk
+        return ms, launches, mean_tokens, clk, batch_prefill_ms
 
-    ms, launches, mean_ctx, clocks = decode_run(args.batch, steps, warmup, True)
+    ms, launches, mean_tokens, clocks, batch_prefill_ms = decode_run(main_lengths, steps, warmup, True)
     ms_per_step = ms / steps
-    value = args.batch * steps / ms * 1000.0
-    step_bytes = engine.model.streamed_weight_bytes() + args.batch * mean_ctx * engine.cache.bytes_per_token() \
-        + args.batch * cfg.hidden_size * 2
+    value = batch * steps / ms * 1000.0
+    step_bytes = engine.model.streamed_weight_bytes() + mean_tokens * engine.cache.bytes_per_token() \
+        + batch * cfg.hidden_size * 2
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / pk["hbm_gbs"], "peak_source": pk_source, "bytes_per_step": int(step_bytes)}
+    if not uniform:
+        # the workload's own prefill: all prompts of the unequal batch, in groups under the token budget
+        flops = step_flops(cfg, main_lengths, batch)
+        prefill["batch"] = {"value": sum(main_lengths) / batch_prefill_ms * 1000.0, "tokens": sum(main_lengths),
+                            "ms": batch_prefill_ms, "groups": len(groups_under_budget(main_lengths)),
+                            "frac": flops / (batch_prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12)
+                            if args.dtype == "bf16" else None, "peak": "sustained"}
 
     points = {}
     for b in point_batches:
         k = max(8, min(steps, 32))
-        pms, _, _, _ = decode_run(b, k, warmup, False)
+        pms, _, _, _, _ = decode_run([lo] * b, k, warmup, False)
         points[f"decode_b{b}"] = b * k / pms * 1000.0
 
     # ---- end to end: Engine.generate, host token ids in and out every step ------------------------
-    prompts = [rand_prompt() for _ in range(args.batch)]
+    prompts = prompts_of(main_lengths)
     # warm-up of the entry point with the same batch shape: the decode graph of that shape is captured here,
     # as it is once in a serving process, not in the timed run
-    engine.generate(prompts, max_new_tokens=4, max_batch=args.batch)
-    out = engine.generate(prompts, max_new_tokens=steps + 1, max_batch=args.batch)
+    engine.generate(prompts, max_new_tokens=4, max_batch=batch)
+    out = engine.generate(prompts, max_new_tokens=steps + 1, max_batch=batch)
     e2e_tokens = out.stats.decode_tokens
     e2e = {"value": e2e_tokens / max(out.stats.decode_ms, 1e-9) * 1000.0, "unit": "tokens/s",
-           "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch,
+           "h2d_bytes_per_step": 4 * batch, "d2h_bytes_per_step": 4 * batch,
            "decode_ms": out.stats.decode_ms, "prefill_ms": out.stats.prefill_ms}
 
+    profile = None
+    if args.profile:
+        prof = engine.generate(prompts[:batch], max_new_tokens=min(steps, 16) + 1, max_batch=batch, profile=True)
+        profile = {phase: {k: round(v, 3) for k, v in t.items()} for phase, t in prof.stats.profile.items()}
+        for phase, t in prof.stats.profile.items():
+            print(ops.profile_line(phase, t), file=sys.stderr)
+
+    kernels = None
+    if not args.no_kernels and args.dtype == "bf16":
+        del engine, out
+        torch.cuda.empty_cache()
+        mean_ctx = int(mean_tokens / batch)
+        kernels = kernel_fractions(cfg, batch, args.prefill, mean_ctx, pk)
+        kernels["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk_source}
+
+    lengths_text = f"{batch} x {lo}" if uniform else f"{batch} lengths uniform in [{lo},{hi}], seed 1234"
     line = {
-        "metric": "decode tok/s at batch 8 (1.8B bf16, 2,048-token prompts); prefill tok/s at 2,048 tokens",
+        "metric": ("decode tok/s at batch 8 (1.8B bf16, 2,048-token prompts); prefill tok/s at 2,048 tokens"
+                   if (args.config, args.dtype, batch, args.prefill) == ("1p8b", "bf16", 8, 2048) else
+                   f"decode tok/s at batch {batch} ({spec['name']}, {args.dtype}, prompts {lengths_text}); "
+                   f"prefill tok/s at {args.prefill} tokens"),
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random-init weights N(0, 0.02) seed 2",
+        "dtype": args.dtype,
+        "data": f"synthetic: seeded uniform-random token ids, random-init weights N(0, 0.02) seed {spec['seed']}",
         "impl": "ours",
-        "config": {"model": "hunyuan-dense-1.8B-sizes", "global_batch": args.batch, "seq_len": PROMPT,
-                   "context": CONTEXT, "parallelism": "single-gpu", "layers": args.layers, "layers_full": FULL_LAYERS,
-                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "rope_alpha": cfg.rope_alpha, "qk_norm": cfg.use_qk_norm, "tied": cfg.tie_word_embeddings,
-                   "cache_block_tokens": engine.cache.block_tokens, "sampling": "greedy on the GPU",
+        "config": {"model": spec["name"], "global_batch": batch, "seq_len": int(sum(main_lengths) / batch),
+                   "prompts": lengths_text, "context": CONTEXT, "parallelism": "single-gpu", "layers": layers,
+                   "layers_full": spec["layers"], "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+                   "vocab": cfg.vocab_size, "rope_alpha": cfg.rope_alpha, "qk_norm": cfg.use_qk_norm,
+                   "tied": cfg.tie_word_embeddings, "sampling": "greedy on the GPU",
                    "l2": "inputs larger than L2: every step streams all weights (GBs) once"},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
         "points": points,
     }
+    if kernels is not None:
+        line["kernels"] = kernels
+    if verify is not None:
+        line["verify"] = verify
+    if profile is not None:
+        line["profile"] = profile
     print(json.dumps(line))
     return 0
 

@@ -11,6 +11,8 @@ so prompts are token ids ("12,7,99" or "12 7 99") and replies are printed as ids
                      the first token comes from the prompt, so a reply has at most N+1 tokens
   --threads N        CPU workers of the reference; accepted, has no meaning on the GPU
   --backend NAME     auto or cuda (cpu, metal and vulkan do not exist here)
+  --profile          per-kernel times of the prefill and of the decode steps (the Benchmark program's switch,
+                     src/HyMT2Sharp.Benchmark/Program.cs:243-261); steps then run uncaptured
 and beyond the reference: --dtype, --temperature, --top-k, --top-p, --min-p,
 --repeat-penalty, --penalty-window, --seed, --stop-ids, --max-context, --max-batch,
 --random CONFIG.json --weights-seed N --sigma S (write random weights into --model first).
@@ -55,6 +57,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--random", metavar="CONFIG.json", help="write random weights for this config into --model")
     ap.add_argument("--weights-seed", type=int, default=0)
     ap.add_argument("--sigma", type=float, default=0.02)
+    ap.add_argument("--profile", action="store_true")
     return ap
 
 
@@ -92,14 +95,16 @@ def main(argv=None) -> int:
     if args.prompt:
         prompts = [system + parse_ids(p) for p in args.prompt]
         out = engine.generate(prompts, max_new_tokens=max_new, sampling=sampling, stop_token_ids=stop,
-                              max_batch=args.max_batch)
+                              max_batch=args.max_batch, profile=args.profile)
         for i, r in enumerate(out.results):
             label = "Assistant" if len(prompts) == 1 else f"Assistant[{i}]"
             print(f"{label}: {','.join(map(str, r.tokens))}  ({r.finish_reason})")
         print(out.stats.line())
+        _print_profile(out.stats)
         return 0
 
-    # prompt loop: each line goes on from the conversation so far; its cache is kept
+    # prompt loop: each line goes on from the conversation so far (the whole conversation is run again as the
+    # next prompt: nothing of a turn's cache is kept once its reply is complete)
     interactive = sys.stdin.isatty()
     if interactive:
         print("\nType token ids.  /reset  /exit")
@@ -123,12 +128,20 @@ def main(argv=None) -> int:
             print("/reset  clear conversation\n/exit   quit")
             continue
         turn = (system if not history else []) + parse_ids(line)
-        out = engine.generate([history + turn], max_new_tokens=max_new, sampling=sampling, stop_token_ids=stop)
+        out = engine.generate([history + turn], max_new_tokens=max_new, sampling=sampling, stop_token_ids=stop,
+                              profile=args.profile)
         r = out.results[0]
         history = history + turn + r.tokens
         print(f"Assistant: {','.join(map(str, r.tokens))}  ({r.finish_reason})")
         print(out.stats.line())
+        _print_profile(out.stats)
     return 0
+
+
+def _print_profile(stats) -> None:
+    from .kernels.ops import profile_line
+    for phase, times in stats.profile.items():
+        print(profile_line(phase, times))
 
 
 if __name__ == "__main__":

@@ -15,15 +15,12 @@
 // cache once per kv head (all heads of the group share it).  The warps that computed a
 // row's last chunk fold all chunks of the row in chunk order, each for its quarter of d.
 // Formulas: src/HyMT2Sharp/Ops.cs:462-532 (the reference's fused decode attention).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tc_common.cuh"
 
 namespace {
 
 constexpr int CHUNK = 128, BLOCK_KEYS = 64, D = 128, NQ = 16;
 constexpr int NUM_THREADS = 352;   // warp 0 TMA, warp 1 MMAs of the scores, warps 2-5 and 6-9: two softmax groups that take turns, warp 10 MMAs of the sums
-constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct DecodeTcParams {
     __nv_bfloat16* out;        // [rows, nh * d]
@@ -37,66 +34,6 @@ struct DecodeTcParams {
     float scale_log2;
     int* status;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023) == 1023 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicExch(status, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_group_bytes) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(mn_group_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) |
-           (2ull << 61);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 constexpr int STAGES = 3;        // chunks whose keys and values are in shared memory or on their way
 constexpr int MAX_ITEMS = 64;    // chunks that one CTA holds in shared memory at a time (one round)
@@ -518,35 +455,14 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
-bool make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace
+
+// The numbers of the kernel's barrier protocol: out[0] stages of K/V in shared memory, [1] pairs of accumulators in
+// tensor memory (one per group of softmax warps).
+HYMT2_API int hymt2_attention_decode_tc_protocol(int* out) {
+    out[0] = STAGES; out[1] = 2;
+    return HYMT2_OK;
+}
 
 // out, q: [rows, nh * 128] bfloat16, one new token per row; k_cache, v_cache: one layer's planes
 // [blocks][nkv][64][128].  max_splits >= ceil(longest kv_len / 128); part_acc holds

@@ -23,14 +23,18 @@
 // over the visible keys), :535-595 (combine).  A query at position p sees keys
 // [max(0, p - window + 1), p].
 // Takes head sizes 64 and 128 and cache blocks of 64 tokens; other shapes stay with the general kernel.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tc_common.cuh"
 
 namespace {
 
 constexpr int Q_ROWS = 128, KEY_TILE = 64, NUM_THREADS = 256, KV_STAGES = 2, K_SLOTS = 3;
-constexpr uint32_t WAIT_LIMIT = 1u << 21;
+// The numbers of the barrier protocol (why these: see the kernel).  hymt2_attention_prefill_tc_protocol hands them to the
+// test that explores every interleaving of the roles, so that the protocol explored is the one compiled here.
+constexpr int P_BARS = K_SLOTS;      // "P of tile i is written": one barrier per K slot, tile mod P_BARS
+constexpr int O_BARS = 3;            // "P·V of tile i is through": tile mod O_BARS
+constexpr int S_BUFFERS = 2;         // score buffers in tensor memory, each with a barrier
+constexpr int STAGE_HOLDERS = 2;     // who must let go of a K/V stage before it is filled again: P·V and the score issuer
+constexpr int NUM_BARS = 2 * KV_STAGES + 1 + O_BARS + S_BUFFERS + P_BARS;
 
 struct PrefillParams {
     __nv_bfloat16* out;        // [T, nh * d]
@@ -44,85 +48,10 @@ struct PrefillParams {
     int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023) == 1023 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicExch(status, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-// MN-major operand tile, 128-byte swizzle: rows (K index) of 64 MN-elements = 128 bytes, 8-row groups
-// 1024 bytes apart (stride offset), the next 64 MN-elements `mn_group_bytes` further (leading offset)
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_group_bytes) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(mn_group_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) |
-           (2ull << 61);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_store16(uint32_t taddr, const float* v) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
@@ -154,8 +83,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // and two CTAs of 112 KB fit an SM.  Barriers and the two words lie behind the tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + BARS_OFFSET);
-    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 9) * 8);
-    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + (2 * KV_STAGES + 9) * 8 + 4);
+    uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(smem_raw + BARS_OFFSET + NUM_BARS * 8);
+    int& abort_s = *reinterpret_cast<int*>(smem_raw + BARS_OFFSET + NUM_BARS * 8 + 4);
 
     // The last query tiles of a prompt walk the most keys: CTAs are numbered by falling query tile, so the long
     // ones start first and the short ones fill the gaps.  When all CTAs fit on the SMs at once (two each), the
@@ -186,7 +115,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * KV_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
     const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
-    const uint32_t s_full = q_full + 32, p_full = q_full + 48;   // s_full: one for even, one for odd tiles; o_full and p_full: three each
+    const uint32_t s_full = o_full + 8 * O_BARS, p_full = s_full + 8 * S_BUFFERS;   // s_full: one for even, one for odd tiles
     // Why these counts.  A parity cannot tell a barrier's phase from the one two later, so no reader may fall two
     // phases behind a barrier, however long its thread is kept from running.  S(j) is only issued once P·V of tile
     // j - 3 is through: with P's barrier of tile j the one of tile j - 3, P(j) cannot be announced before the
@@ -200,14 +129,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (threadIdx.x == 0) {
         for (int s = 0; s < KV_STAGES; s++) {
             mbar_init(kv_full + 8 * s, 1);
-            mbar_init(kv_empty + 8 * s, 2);   // P·V of the tile is through, and the score issuer has seen the copy land
+            mbar_init(kv_empty + 8 * s, STAGE_HOLDERS);   // P·V of the tile is through, and the score issuer has seen the copy land
         }
         mbar_init(q_full, 1);
-        for (int t = 0; t < 2; t++) mbar_init(s_full + 8 * t, 1);
-        for (int t = 0; t < 3; t++) {
-            mbar_init(o_full + 8 * t, 1);
-            mbar_init(p_full + 8 * t, 128);
-        }
+        for (int t = 0; t < S_BUFFERS; t++) mbar_init(s_full + 8 * t, 1);
+        for (int t = 0; t < O_BARS; t++) mbar_init(o_full + 8 * t, 1);
+        for (int t = 0; t < P_BARS; t++) mbar_init(p_full + 8 * t, 128);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -280,9 +207,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_arrive(kv_empty + 8 * (i % KV_STAGES));   // seen: the stage may be filled again once P·V of tile i is through too
             // P·V of tile i - 2 is through.  The softmax warps, who wait for P·V of the tile before theirs only when a
             // maximum rose, then never meet a barrier more than one phase behind (a parity cannot tell two apart).
-            if (i >= 2 && !mbar_wait(o_full + 8 * ((i - 2) % 3), ((i - 2) / 3) & 1, abort_flag, p.status, 108)) break;
+            if (i >= 2 && !mbar_wait(o_full + 8 * ((i - 2) % O_BARS), ((i - 2) / O_BARS) & 1, abort_flag, p.status, 108)) break;
             // the scores of tile i - 1 have been read: their buffer takes those of tile i + 1
-            if (i >= 1 && !mbar_wait(p_full + 8 * ((i - 1) % K_SLOTS), ((i - 1) / K_SLOTS) & 1, abort_flag, p.status, 118)) break;
+            if (i >= 1 && !mbar_wait(p_full + 8 * ((i - 1) % P_BARS), ((i - 1) / P_BARS) & 1, abort_flag, p.status, 118)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_scores(i + 1);
         }
@@ -292,7 +219,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
         for (int i = 0; i < num_tiles; i++) {
             const int s = i % KV_STAGES;
-            if (!mbar_wait(p_full + 8 * (i % K_SLOTS), (i / K_SLOTS) & 1, abort_flag, p.status, 114)) break;
+            if (!mbar_wait(p_full + 8 * (i % P_BARS), (i / P_BARS) & 1, abort_flag, p.status, 114)) break;
             if (!mbar_wait(kv_full + 8 * s, (i / KV_STAGES) & 1, abort_flag, p.status, 109)) break;   // V(i) has landed
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t pd = p_desc0 + (i % K_SLOTS) * K_STEP, vd = v_desc0 + s * V_STEP;
@@ -300,7 +227,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int k = 0; k < KEY_TILE / 16; k++)
                 umma_bf16(tmem_base + O_COL, pd + ((k * 32) >> 4), vd + ((k * (16 * 128)) >> 4), IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
             umma_commit(kv_empty + 8 * s);
-            umma_commit(o_full + 8 * (i % 3));
+            umma_commit(o_full + 8 * (i % O_BARS));
         }
     } else if (warp >= 4) {
         // ---- softmax: one thread per query row; O stays in TMEM ------------------------------------
@@ -341,7 +268,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (raise) m = tile_max;
             if (i > 0 && __any_sync(0xffffffffu, raise)) {
                 // the O of the tiles so far is complete, then every row of the warp scales its own O
-                if (!(ok = mbar_wait(o_full + 8 * ((i - 1) % 3), ((i - 1) / 3) & 1, abort_flag, p.status, 116))) break;
+                if (!(ok = mbar_wait(o_full + 8 * ((i - 1) % O_BARS), ((i - 1) / O_BARS) & 1, abort_flag, p.status, 116))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int c = 0; c < D; c += 16) {   // 16 columns at a time: the row's 64 scores are live in registers
@@ -392,9 +319,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full + 8 * (i % K_SLOTS));
+            mbar_arrive(p_full + 8 * (i % P_BARS));
         }
-        if (ok) ok = mbar_wait(o_full + 8 * ((num_tiles - 1) % 3), ((num_tiles - 1) / 3) & 1, abort_flag, p.status, 117);
+        if (ok) ok = mbar_wait(o_full + 8 * ((num_tiles - 1) % O_BARS), ((num_tiles - 1) / O_BARS) & 1, abort_flag, p.status, 117);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -424,40 +351,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
-bool make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid,
            cudaStream_t stream) {
     constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
     constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (kv_tile >= p_tile ? kv_tile : p_tile) + KV_STAGES * kv_tile +
-                            (2 * KV_STAGES + 9) * 8 + 8;   // tiles, barriers, two words
+                            NUM_BARS * 8 + 8;   // tiles, barriers, two words
     auto kernel = attention_prefill_tc_kernel<D>;
     static bool configured = false;
     if (!configured) {
@@ -471,6 +370,14 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 }
 
 }  // namespace
+
+// The numbers of the kernel's barrier protocol: out[0] stages of the K/V copies, [1] K slots, [2] barriers for "P written",
+// [3] barriers for "P·V through", [4] holders of a stage, [5] score buffers.
+HYMT2_API int hymt2_attention_prefill_tc_protocol(int* out) {
+    static_assert(S_BUFFERS == 2, "the score buffers are addressed by a tile's parity");
+    out[0] = KV_STAGES; out[1] = K_SLOTS; out[2] = P_BARS; out[3] = O_BARS; out[4] = STAGE_HOLDERS; out[5] = S_BUFFERS;
+    return HYMT2_OK;
+}
 
 // out, q: [tokens, nh * d] bfloat16; k_cache, v_cache: one layer's planes [blocks][nkv][64][d] bfloat16.
 HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache,

@@ -1,11 +1,12 @@
-// Token embedding: out[t, :] = float(table[ids[t], :]).  The residual stream
+// Token embedding: out[t, :] = float(table[ids[t], :]) * scale.  The residual stream
 // that it starts is float32 in both precisions.
-// Formula: src/HyMT2Sharp/HunyuanDenseModel.cs:494-537 (row gather, no scale).
+// Formula: src/HyMT2Sharp/HunyuanDenseModel.cs:494-537 (row gather; that model has no scale, so its
+// scale is 1; architectures that multiply their embeddings by a constant give it here).
 #include "common.cuh"
 
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
-                             const int* __restrict__ ids, int hidden, int vocab, int* status) {
+                             const int* __restrict__ ids, int hidden, int vocab, float scale, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -16,15 +17,15 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
         return;
     }
     const T* row = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = scale == 1.0f ? to_float(row[i]) : to_float(row[i]) * scale;
 }
 
 HYMT2_API int hymt2_embed(float* out, const void* table, int table_dtype, const int* ids, int tokens,
-                          int hidden, int vocab, int* status, cudaStream_t stream) {
+                          int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
     if (tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes tokens=%d hidden=%d vocab=%d", tokens, hidden, vocab);
     HYMT2_DISPATCH_DTYPE(table_dtype, T,
-        launch_pdl(embed_kernel<T>, dim3(tokens), dim3(256), 0, stream, out, (const T*)table, ids, hidden, vocab, status));
+        launch_pdl(embed_kernel<T>, dim3(tokens), dim3(256), 0, stream, out, (const T*)table, ids, hidden, vocab, scale, status));
     return hymt2_check_launch("embed");
 }
 

@@ -29,9 +29,7 @@
 //
 // Every wait on an mbarrier is bounded: when it gives up it sets the status word and the abort
 // flag, all roles leave their loops, TMEM is freed and the kernel returns.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tc_common.cuh"
 
 namespace {
 
@@ -43,7 +41,6 @@ __host__ __device__ constexpr int tile_issuers(int bn, bool swapped, int epi) {
 }
 __host__ __device__ constexpr int tile_threads(int bn, bool swapped, int epi) { return tile_issuers(bn, swapped, epi) > 1 ? 224 : 192; }
 constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 2;
-constexpr uint32_t WAIT_LIMIT = 1u << 21;
 constexpr int PERSISTENT_BN = 256;   // tile width of the persistent kernel for many tokens
 
 enum { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE_KV = 3 };
@@ -80,44 +77,9 @@ struct GemmTcParams {
     int* counters;           // [tile] arrivals, zero between launches
     int* status;
     RopeEpilogue rope;       // EPI_ROPE_KV only
+    uint32_t wait_limit;     // tries of a bounded wait in the one-tile kernel (WAIT_LIMIT, less in the debug entry)
+    int withhold_block;      // -1; the debug entry names a k block whose copies the producer does NOT issue
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_plain(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the wait gave up or another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023) == 1023 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicExch(status, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
 
 // The copies of one stage (activations, weights, and for a split weight tile its second half) with, in front of them, a
 // look (mbarrier.test_wait, which never suspends the thread) at the barrier of the stage that comes next: the answer
@@ -144,18 +106,6 @@ __device__ __forceinline__ bool tma_stage_looking_ahead(uint32_t bar, uint32_t b
     return seen != 0;
 }
 
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    // K-major operand, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 // the same with "add to what the accumulator holds" fixed, so that no predicate has to be computed
 __device__ __forceinline__ void umma_bf16_add(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
     asm volatile(
@@ -190,26 +140,14 @@ __device__ __forceinline__ bool umma_block_looking_ahead(uint32_t tmem_d, uint64
         : "memory");
     return seen != 0;
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
 template <int N>
 __device__ __forceinline__ void tmem_load(uint32_t taddr, float* v);
 template <>
-__device__ __forceinline__ void tmem_load<16>(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
+__device__ __forceinline__ void tmem_load<16>(uint32_t taddr, float* v) { tmem_load16(taddr, v); }
 template <>
 __device__ __forceinline__ void tmem_load<32>(uint32_t taddr, float* v) {
-    tmem_load<16>(taddr, v);
-    tmem_load<16>(taddr + 16, v + 16);
+    tmem_load16(taddr, v);
+    tmem_load16(taddr + 16, v + 16);
 }
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -387,26 +325,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (weights_are_a) tma_load_2d(b_dst, &map_b, bar, k, b_row0);
             else tma_load_2d(a_dst, &map_a, bar, k, a_row0);
         };
+        // (p.withhold_block, -1 in every ordinary launch: the debug entry makes the producer announce that block's
+        // bytes and never copy them, so that the wait for them runs out; see hymt2_gemm_tc_debug)
         const int ahead = min(stages, my_blocks);
         for (int i = 0; i < ahead; i++) {   // fresh stages: nothing to wait for
             mbar_expect_tx(full0 + 8 * (i % stages), STAGE_BYTES);
-            load_weights(i);
+            if (kb_begin + i != p.withhold_block) load_weights(i);
         }
         pdl_wait();
-        for (int i = 0; i < ahead; i++) load_activations(i);
+        for (int i = 0; i < ahead; i++)
+            if (kb_begin + i != p.withhold_block) load_activations(i);
         int issued = ahead;
         for (int i = ahead; i < my_blocks; i++) {
             const int s = i % stages;
-            if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, abort_flag, p.status, 101)) break;
+            if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, abort_flag, p.status, 101, p.wait_limit)) break;
             mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            load_weights(i);
-            load_activations(i);
+            if (kb_begin + i != p.withhold_block) {
+                load_weights(i);
+                load_activations(i);
+            }
             issued = i + 1;
         }
         if (*abort_flag) {
             // copies that are in flight must land before the CTA's shared memory goes away
+            const uint32_t tries = p.withhold_block >= 0 ? p.wait_limit : (1u << 16);   // a withheld block never lands
             for (int i = max(0, issued - stages); i < issued; i++)
-                for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full0 + 8 * (i % stages), (i / stages) & 1); t++) {}
+                for (uint32_t t = 0; t < tries && !mbar_try_wait(full0 + 8 * (i % stages), (i / stages) & 1); t++) {}
         }
     } else if ((warp == 1 || (warp >= 6 && warp - 5 < ISSUERS)) && lane == 0) {
         // ---- MMA issuers: warp 1 is issuer 0, warp 6 is issuer 1 ------------------------------------
@@ -416,11 +360,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         constexpr uint64_t K_STEP = (UMMA_K * 2) >> 4, A2_STEP = A_TILE_BYTES >> 4, B_STEP = (NUM_ACC * A_TILE_BYTES) >> 4;
         const int me = warp == 1 ? 0 : warp - 5;
         const uint32_t acc0 = tmem_base + me * BN, acc1 = tmem_base + (ISSUERS + me) * BN;
-        const uint64_t desc0 = smem_desc_sw128(tiles);
+        const uint64_t desc0 = desc_k_major(tiles);
         uint32_t s = 0, phase = 0, any = 0;
         for (int i = 0; i < my_blocks; i++) {
             if ((int)(s % ISSUERS) == me) {
-                if (!mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102)) break;
+                if (!mbar_wait(full0 + 8 * s, phase, abort_flag, p.status, 102, p.wait_limit)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t adesc = desc0 + (uint64_t)s * (uint64_t)(STAGE_BYTES >> 4), bdesc = adesc + B_STEP;
                 umma_bf16(acc0, adesc, bdesc, IDESC, any);
@@ -443,7 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         pdl_wait();   // C, the workspace and the counters may still be in use by the kernel before
         if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();   // wait first, release after
-        bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103) : true;
+        bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103, p.wait_limit) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         TC* C = (TC*)p.C;
         // CH columns of the accumulators from column c on (c counts gate columns, then up columns): the sum over the
@@ -796,7 +740,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (first) pdl_wait();
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: the stage's descriptor is carried along, see gemm_tc_kernel --------------
-        const uint64_t desc0 = smem_desc_sw128(tiles);
+        const uint64_t desc0 = desc_k_major(tiles);
         uint64_t adesc = desc0;
         uint32_t s = 0, phase = 0;
         bool looked = false;   // whether the stage's barrier was already seen complete
@@ -888,7 +832,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive_plain(acc_empty0 + 8 * buf);   // this thread has taken its row out of the accumulator
+            mbar_arrive(acc_empty0 + 8 * buf);   // this thread has taken its row out of the accumulator
         }
     }
 
@@ -903,36 +847,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // --------------------------------------------------------------------------------------------
 // host side
 // --------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
-// A [rows, K] bfloat16 matrix with row stride ld (elements); boxes of 64 x box_rows, 128-byte swizzle,
-// zeros outside the matrix.
-bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int BN, bool SWAPPED, int EPI, typename TC>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kernel = gemm_tc_kernel<BN, SWAPPED, EPI, TC>;
@@ -1098,6 +1012,13 @@ int sm_count_of_current_device() {
 
 }  // namespace
 
+// The numbers of the kernels' barrier protocols: out[0] the most stages of a ring, [1] accumulators of the persistent
+// kernel that alternate, [2] the most MMA issuers of the one-tile kernel, [3] 1: issuer j owns the stages j, j + issuers, ...
+HYMT2_API int hymt2_gemm_tc_protocol(int* out) {
+    out[0] = MAX_STAGES; out[1] = 2; out[2] = tile_issuers(16, true, EPI_STORE); out[3] = 1;
+    return HYMT2_OK;
+}
+
 // Whether the tensor-core kernel takes this problem, and what scratch it wants:
 // workspace_floats of float32 and counters ints (zeroed once; the kernel leaves them zero).
 HYMT2_API int hymt2_gemm_tc_plan(int T, int N, int K, int epilogue, long* workspace_floats, int* counters) {
@@ -1127,10 +1048,10 @@ HYMT2_API int hymt2_gemm_tc_describe(int T, int N, int K, int epilogue, int sm_c
     return HYMT2_OK;
 }
 
-// C[T,N] (ldc) = epilogue(X[T,K] (lda) · W[N,K]^T (ldw)), X and W bfloat16; for SwiGLU W has 2N rows.
-HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
-                            long ldc, int epilogue, float* workspace, long workspace_floats, int* counters,
-                            int num_counters, int* status, cudaStream_t stream) {
+namespace {
+int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw, long ldc,
+                int epilogue, float* workspace, long workspace_floats, int* counters, int num_counters, int* status,
+                cudaStream_t stream, uint32_t wait_limit, int withhold_block) {
     if (T == 0 || N == 0) return HYMT2_OK;
     HYMT2_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
     HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K, lda and ldw must be multiples of 8 (K=%d lda=%ld ldw=%ld)", K, lda, ldw);
@@ -1153,7 +1074,10 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
     GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
-                   RopeEpilogue{}};
+                   RopeEpilogue{}, wait_limit, withhold_block};
+    if (withhold_block >= 0)
+        HYMT2_REQUIRE(pl.swapped && pl.splits == 1, "gemm_tc_debug: only the one-tile kernel without a cut of K can withhold a block "
+                      "(T=%d N=%d K=%d gives swapped=%d splits=%d)", T, N, K, (int)pl.swapped, pl.splits);
     if (pl.swapped) {
         switch (pl.bn) {
             case 16: return dispatch_epilogue<16, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
@@ -1164,6 +1088,31 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
     }
     if (pl.persistent) return launch_persistent(ma, mb, p, pl, epilogue, c_dtype, stream);
     return dispatch_epilogue<128, false>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+}
+}  // namespace
+
+// C[T,N] (ldc) = epilogue(X[T,K] (lda) · W[N,K]^T (ldw)), X and W bfloat16; for SwiGLU W has 2N rows.
+HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
+                            long ldc, int epilogue, float* workspace, long workspace_floats, int* counters,
+                            int num_counters, int* status, cudaStream_t stream) {
+    return run_gemm_tc(C, c_dtype, X, W, T, N, K, lda, ldw, ldc, epilogue, workspace, workspace_floats, counters, num_counters,
+                       status, stream, WAIT_LIMIT, -1);
+}
+
+// The same product with one fault put in on purpose, for the test of the bounded waits: the producer announces
+// the bytes of k block `withhold_block` and never copies them, and every wait gives up after `wait_limit` tries
+// (a few thousand: milliseconds).  The MMA issuer's wait for that block then runs out: it writes 102 into the
+// status word and raises the CTA's abort flag, every role leaves its loop, the producer waits (bounded) for the
+// copies that are in flight, tensor memory is freed, the kernel returns, and the context stays usable.  What the
+// launch wrote into C is not a product.  Only a product of few tokens whose K is not cut is taken (the smallest
+// launch there is): no cluster, no workspace, no counters that a half-finished run could leave set.
+HYMT2_API int hymt2_gemm_tc_debug(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
+                                  long ldc, int epilogue, int* status, cudaStream_t stream, int wait_limit,
+                                  int withhold_block) {
+    HYMT2_REQUIRE(wait_limit > 0 && wait_limit <= (1 << 16), "gemm_tc_debug: wait_limit %d must be in [1, 65536]", wait_limit);
+    HYMT2_REQUIRE(withhold_block >= 0 && withhold_block < (K + BLOCK_K - 1) / BLOCK_K, "gemm_tc_debug: K has no block %d", withhold_block);
+    return run_gemm_tc(C, c_dtype, X, W, T, N, K, lda, ldw, ldc, epilogue, nullptr, 0, nullptr, 0, status, stream,
+                       (uint32_t)wait_limit, withhold_block);
 }
 
 // Whether hymt2_gemm_tc_rope_kv takes a projection of T tokens onto N = (nh + 2 nkv) * 128 features over K.  A few tokens
@@ -1212,7 +1161,8 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
     RopeEpilogue rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, token_seq, token_pos,
                       slot_ids, inv_freq, angles, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
                       gain_dtype == HYMT2_BF16 ? 1 : 0, eps};
-    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, nullptr, nullptr, status, rope};
+    GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, nullptr, nullptr, status, rope,
+                   WAIT_LIMIT, -1};
     if (pl.persistent) {
         const int ctas = pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count;
         return launch_persistent_one<PERSISTENT_BN, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);

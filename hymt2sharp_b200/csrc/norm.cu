@@ -1,12 +1,13 @@
 // Row-wise RMSNorm: y = x * (1 / sqrt(sum(x^2)/dim + eps)) * gain, all in float32
-// (src/HyMT2Sharp/Ops.cs:29-89; scale at :62, product order at :69-72).
+// (src/HyMT2Sharp/Ops.cs:29-89; scale at :62, product order at :69-72).  `out_scale` multiplies the
+// result (1 for this architecture; a model that scales its logits gives the factor to its final norm).
 // `rows_index`, when given, picks the input rows (y[r] = norm(x[rows_index[r]])):
 // the final norm runs only on the rows whose logits are wanted.
 #include "common.cuh"
 
 template <typename TX, typename TW, typename TY>
 __global__ void rmsnorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
-                               const int* __restrict__ rows_index, int dim, float eps) {
+                               const int* __restrict__ rows_index, int dim, float eps, float out_scale) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -20,8 +21,10 @@ __global__ void rmsnorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, con
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
     TY* dst = y + (size_t)r * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x)
-        dst[i] = from_float<TY>(to_float(src[i]) * scale * to_float(gain[i]));
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = to_float(src[i]) * scale * to_float(gain[i]);
+        dst[i] = from_float<TY>(out_scale == 1.0f ? v : v * out_scale);
+    }
 }
 
 // The common case in one pass: float32 rows whose 8 values per thread stay in registers between
@@ -51,10 +54,10 @@ __global__ void rmsnorm_f32_bf16_kernel(__nv_bfloat16* __restrict__ y, const flo
 }
 
 HYMT2_API int hymt2_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, const void* gain, int gain_dtype,
-                            const int* rows_index, int rows, int dim, float eps, cudaStream_t stream) {
+                            const int* rows_index, int rows, int dim, float eps, float out_scale, cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", rows, dim);
-    if (x_dtype == HYMT2_F32 && y_dtype == HYMT2_BF16 && dim % 256 == 0 && dim <= 8192 &&
+    if (out_scale == 1.0f && x_dtype == HYMT2_F32 && y_dtype == HYMT2_BF16 && dim % 256 == 0 && dim <= 8192 &&
         (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
         cudaError_t e;
         if (gain_dtype == HYMT2_BF16)
@@ -69,7 +72,7 @@ HYMT2_API int hymt2_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, co
     const int threads = dim >= 1024 ? 256 : (dim >= 256 ? 128 : 32);
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(y_dtype, TY,
         (launch_pdl(rmsnorm_kernel<TX, TW, TY>, dim3(rows), dim3(threads), 0, stream, (TY*)y, (const TX*)x,
-                    (const TW*)gain, rows_index, dim, eps)))));
+                    (const TW*)gain, rows_index, dim, eps, out_scale)))));
     return hymt2_check_launch("rmsnorm");
 }
 

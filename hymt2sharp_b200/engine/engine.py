@@ -114,7 +114,7 @@ class Engine:
         self.architecture, self.config = load_config(model_dir)
         spec = self.architecture.build_spec(self.config) if spec_override is None else spec_override(self.config)
         self.model = DecoderModel(spec)
-        weights = load_checkpoint(model_dir, self.model.tensors())
+        weights = load_checkpoint(model_dir, self.model.tensors(), spec.ignorable_tensors)
         with torch.cuda.device(self.device):
             self.model.load(weights, self.device, self.dtype)
             self.cache = PagedCache(self.model.groups, self.dtype, self.device, capacity_tokens=max_tokens,

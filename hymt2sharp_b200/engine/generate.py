@@ -32,6 +32,7 @@ class GenerationStats:
     decode_tokens: int = 0      # tokens produced by decode steps
     decode_steps: int = 0
     decode_ms: float = 0.0
+    profile: dict = field(default_factory=dict)   # with profiling on: {"prefill" | "decode": {kernel or product: ms}}
 
     def line(self) -> str:
         """The timing line of src/HyMT2Sharp.Cli/Program.cs:121-126."""
@@ -177,14 +178,26 @@ class EngineStepper:
         self.release(list(self.held))
 
 
-def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None, clock=time.perf_counter) -> None:
+def _book(stats: GenerationStats, phase: str, times: dict) -> None:
+    into = stats.profile.setdefault(phase, {})
+    for k, v in times.items():
+        into[k] = into.get(k, 0.0) + v
+
+
+def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None, clock=time.perf_counter,
+              profiler=None) -> None:
     """Drives one batch to its end through `stepper` (prefill(), decode(rows, tokens),
-    release(rows), close())."""
+    release(rows), close()).  `profiler`: an object with profile_begin() and profile_end() -> {name: ms}
+    (kernels.ops); what it measured is booked under "prefill" and "decode" in stats.profile."""
     try:
         if not state.live:
             return
         t0 = clock()
+        if profiler:
+            profiler.profile_begin()
         tokens = stepper.prefill()
+        if profiler:
+            _book(stats, "prefill", profiler.profile_end())
         stats.prefill_ms += (clock() - t0) * 1000.0
         stats.prefill_tokens += sum(state.prompt_lens)
         rows_before = list(state.live)
@@ -193,6 +206,9 @@ def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None
             on_tokens([(state.request_ids[r], t) for r, t in zip(rows_before, tokens) if state.reasons[r] != "stop"])
         stepper.release(ended)
         t0 = clock()
+        if profiler and state.live:
+            profiler.profile_begin()
+        profiling = bool(profiler and state.live)
         while state.live:
             rows_before = list(state.live)
             tokens = stepper.decode(rows_before, state.last_tokens())
@@ -203,16 +219,21 @@ def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None
                 on_tokens([(state.request_ids[r], t) for r, t in zip(rows_before, tokens)
                            if state.reasons[r] != "stop"])
             stepper.release(ended)
+        if profiling:
+            _book(stats, "decode", profiler.profile_end())
         stats.decode_ms += (clock() - t0) * 1000.0
     finally:
         stepper.close()
 
 
 def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_token_ids=(),
-             max_batch: int | None = None, on_tokens=None, stepper_factory=None) -> GenerationOutput:
+             max_batch: int | None = None, on_tokens=None, stepper_factory=None, profile: bool = False) -> GenerationOutput:
     """Generates for every prompt (a list of token ids).  `sampling` is one SamplingParams for
     all requests or a list with one per request; the default is greedy.  Returns the kept
-    tokens and the finish reason of every request, in the order of `prompts`."""
+    tokens and the finish reason of every request, in the order of `prompts`.  `profile`: every
+    kernel is timed by a pair of CUDA events and booked by name in stats.profile (the counterpart of
+    HunyuanDenseModel.ProfileEnabled, src/HyMT2Sharp/HunyuanDenseModel.cs:48-78); steps then run
+    uncaptured and kernel after kernel, so the total is slower than an unprofiled run."""
     prompts = [list(map(int, p)) for p in prompts]
     if sampling is None:
         sampling = GREEDY
@@ -231,12 +252,17 @@ def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_tok
     capacity = engine.cache.free_tokens()
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, max_batch, capacity, engine.cache.block_tokens)
     factory = stepper_factory or EngineStepper
+    profiler = None
+    if profile:
+        from ..kernels import ops as profiler
+        if stepper_factory is None:
+            factory = lambda *a: EngineStepper(*a, use_graph=False)
     stats = GenerationStats()
     results = [None] * len(prompts)
     for ids in batches:
         state = BatchState(ids, [len(prompts[i]) for i in ids], max_new_tokens, stop_token_ids)
         stepper = factory(engine, [params[i] for i in ids], [prompts[i] for i in ids], max_new_tokens)
-        run_batch(stepper, state, stats, on_tokens)
+        run_batch(stepper, state, stats, on_tokens, profiler=profiler)
         stats.batches += 1
         for i, res in zip(ids, state.results()):
             results[i] = res

@@ -37,7 +37,9 @@ def build_spec(cfg: HunyuanDenseConfig) -> ModelSpec:
     return ModelSpec(
         vocab=cfg.vocab_size, hidden=cfg.hidden_size, embedding="model.embed_tokens.weight", layers=layers,
         final_norm=PartSpec("rmsnorm", dict(dim=cfg.hidden_size, eps=cfg.rms_norm_eps, weight="model.norm.weight")),
-        head=None if cfg.tie_word_embeddings else "lm_head.weight", max_positions=cfg.max_position_embeddings)
+        head=None if cfg.tie_word_embeddings else "lm_head.weight", max_positions=cfg.max_position_embeddings,
+        head_copy="lm_head.weight" if cfg.tie_word_embeddings else None,
+        ignorable_tensors=[r".*\.rotary_emb\.inv_freq"])
 
 
 def tensor_shapes(cfg: HunyuanDenseConfig):

@@ -21,10 +21,10 @@ class DecoderModel:
         self.embedding = None
         self.head = None
         self.groups: list[GroupSpec] = []
-        self.slots: list[MixerSlot] = []
+        self.slots: list[list[MixerSlot]] = []   # per entry of the order: one MixerSlot for each mixer of its block
         self.state_bytes = 0
         # a step can be captured into a CUDA graph only if every part launches kernels and nothing else
-        self.graph_safe = all(getattr(p, "graph_safe", False) for b in self.blocks for p in b.parts())
+        self.graph_safe = all(getattr(b, "graph_safe", False) for b in self.blocks)
         self._plan_memory()
 
     # -- what the checkpoint must hold -----------------------------------------
@@ -36,39 +36,48 @@ class DecoderModel:
         t.update(self.final_norm.tensors())
         if s.head is not None:
             t[s.head] = TensorSpec((s.vocab, s.hidden))
+        elif s.head_copy is not None:
+            t[s.head_copy] = TensorSpec((s.vocab, s.hidden), optional=True, same_as=s.embedding)
         return t
 
     # -- cache planes and state offsets of every run ---------------------------
     def _plan_memory(self) -> None:
+        """Walks the order: every mixer of every run gets its state bytes and, if it keeps keys and values, a
+        plane in the group of its needs (or the plane of the run whose cache it reads).  The blocks answer;
+        the model never looks inside one."""
         keys: list[tuple] = []
         planes: list[int] = []
         specs: list[GroupSpec] = []
         offset = 0
         for i, run in enumerate(self.spec.order):
-            mixer = self.blocks[run.layer].mixer
-            need = mixer.cache_need()
-            slot = MixerSlot()
-            sb = int(mixer.state_bytes())
-            if sb:
-                offset = -(-offset // 16) * 16
-                slot.state_offset, slot.state_bytes = offset, sb
-                offset += sb
-            if need is not None:
-                if run.cache_from is not None:
-                    src = self.slots[run.cache_from]
-                    src_need = self.blocks[self.spec.order[run.cache_from].layer].mixer.cache_need()
-                    if src_need is None or src_need.key() != need.key():
-                        raise ValueError(f"order[{i}] cannot read the cache of entry {run.cache_from}: different needs")
-                    slot.group, slot.plane, slot.writes = src.group, src.plane, False
-                else:
-                    if need.key() not in keys:
-                        keys.append(need.key())
-                        planes.append(0)
-                        specs.append(need)
-                    g = keys.index(need.key())
-                    slot.group, slot.plane = g, planes[g]
-                    planes[g] += 1
-            self.slots.append(slot)
+            block = self.blocks[run.layer]
+            needs, states = list(block.cache_needs()), list(block.state_bytes())
+            if len(needs) != len(states):
+                raise ValueError(f"layer {run.layer}: cache_needs() and state_bytes() must have one entry per mixer")
+            row = []
+            for j, (need, sb) in enumerate(zip(needs, states)):
+                slot = MixerSlot()
+                if sb:
+                    offset = -(-offset // 16) * 16
+                    slot.state_offset, slot.state_bytes = offset, int(sb)
+                    offset += int(sb)
+                if need is not None:
+                    if run.cache_from is not None:
+                        src_needs = list(self.blocks[self.spec.order[run.cache_from].layer].cache_needs())
+                        if j >= len(src_needs) or src_needs[j] is None or src_needs[j].key() != need.key():
+                            raise ValueError(f"order[{i}] cannot read the cache of entry {run.cache_from}: different needs")
+                        src = self.slots[run.cache_from][j]
+                        slot.group, slot.plane, slot.writes = src.group, src.plane, False
+                    else:
+                        if need.key() not in keys:
+                            keys.append(need.key())
+                            planes.append(0)
+                            specs.append(need)
+                        g = keys.index(need.key())
+                        slot.group, slot.plane = g, planes[g]
+                        planes[g] += 1
+                row.append(slot)
+            self.slots.append(row)
         self.groups = [GroupSpec(s.kind, s.kv_heads, s.head_dim, planes[g], s.window) for g, s in enumerate(specs)]
         self.state_bytes = offset
 
@@ -79,7 +88,17 @@ class DecoderModel:
         for b in self.blocks:
             b.load(weights, device, dtype)
         self.final_norm.load(weights, device, dtype)
-        self.head = Linear(self.embedding if s.head is None else compute_form(weights[s.head], device, dtype))
+        self.head = Linear(self.embedding if s.head is None else compute_form(weights[s.head], device, dtype), role="head")
+        if dtype == torch.bfloat16:
+            # a tensor stored in 32-bit stays so; for a MATRIX that means its product runs on the CUDA-core kernel,
+            # many times slower than the tensor cores.  That is a property of the checkpoint worth saying aloud.
+            wide = [name for name, spec in self.tensors().items()
+                    if len(spec.shape) == 2 and name in weights and weights[name].dtype == torch.float32]
+            if wide:
+                import warnings
+                warnings.warn(f"{len(wide)} matrices of the checkpoint are stored in 32-bit (first: {wide[0]}); the bfloat16 "
+                              f"engine keeps them so and computes their products on CUDA cores, not on the tensor cores. "
+                              f"Store them in bfloat16 for full speed.", RuntimeWarning, stacklevel=2)
 
     def streamed_weight_bytes(self) -> int:
         """Bytes of weights that a step reads whatever its tokens are: every layer that runs,
@@ -113,11 +132,13 @@ class DecoderModel:
         of the token rows that `want_rows` names (int32, device)."""
         T = ctx.num_tokens
         residual = torch.empty((T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
-        ops.embed(residual, self.embedding, ctx.tokens, ctx.status)
-        for run, slot in zip(self.spec.order, self.slots):
-            self.blocks[run.layer].forward(residual, ctx, slot)
+        ops.embed(residual, self.embedding, ctx.tokens, ctx.status, self.spec.embed_scale or 1.0)
+        for run, slots in zip(self.spec.order, self.slots):
+            self.blocks[run.layer].forward(residual, ctx, slots)
         ops.join_beside(ctx.device)   # what parts asked into L2 on the side stream
         if num_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=ctx.device)
-        normed = self.final_norm.forward(residual, ctx, ctx.dtype, rows_index=want_rows, rows=num_want)
+        # a model that scales its logits gives the factor to the final norm: (s * norm(x)) W = s * (norm(x) W)
+        scale = {} if self.spec.logit_scale is None else {"scale": float(self.spec.logit_scale)}
+        normed = self.final_norm.forward(residual, ctx, ctx.dtype, rows_index=want_rows, rows=num_want, **scale)
         return self.head(normed, out_dtype=torch.float32)

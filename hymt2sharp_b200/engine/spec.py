@@ -29,6 +29,11 @@ class ModelSpec:
     head: str | None                  # checkpoint name of the [vocab, hidden] head; None = the embedding table
     order: list[Run] = field(default_factory=list)
     max_positions: int | None = None  # the longest sequence the model takes (None: whatever the cache holds)
+    embed_scale: float | None = None  # the embedding rows are multiplied by this (None: as they are)
+    logit_scale: float | None = None  # the logits are multiplied by this (None: as they are)
+    # regular expressions of tensor names that checkpoints of this architecture may hold and the model does not read
+    ignorable_tensors: list[str] = field(default_factory=list)
+    head_copy: str | None = None      # with a tied head: the name under which a checkpoint may store the head once more
 
     def __post_init__(self):
         if not self.order:

@@ -15,6 +15,34 @@ def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: in
     return True
 
 
+def try_project_rope_kv(x, weight, epilogue, ctx, planes, cache_dtype, block_table, q_gain, k_gain, eps, nh, nkv, d):
+    """The fused q/k/v projection whose epilogue rotates, norms and appends to the cache (tcgen05, heads of 128,
+    rotate-half pairs): returns q [T, nh * d], or None when that kernel does not take the operands and the caller
+    goes the two-kernel way.  `planes` = (k_plane, v_plane), or (None, None) for a run that writes no keys."""
+    from . import ops
+    if epilogue.pairing != "half" or x.dtype != torch.bfloat16:
+        return None
+    if not ops.gemm_tc_rope_kv_supported(x, weight, nh, nkv, d, cache_dtype, epilogue.rope_dim):
+        return None
+    T = x.shape[0]
+    q = torch.empty((T, nh * d), dtype=x.dtype, device=x.device)
+    angles = None
+    if ops.gemm_tc_rope_kv_wants_angles(T, epilogue.rope_dim):
+        # a prompt's worth of tokens: their angles once per step and table, not once per head and layer
+        key = ("rotary angles", epilogue.inv_freq.data_ptr())
+        angles = ctx.shared.get(key)
+        if angles is None:
+            angles = ctx.shared[key] = ops.rope_angles(ctx.token_pos[:T], epilogue.inv_freq)
+    ops.tag = "qkv+rope"
+    try:
+        ops.gemm_tc_rope_kv(x, weight, q, planes[0], planes[1], block_table, ctx.cache.block_tokens, ctx.token_seq,
+                            ctx.token_pos, ctx.slot_ids, epilogue.inv_freq, epilogue.rope_dim, q_gain, k_gain, eps, nh, nkv,
+                            ops.device_status(x.device), angles=angles)
+    finally:
+        ops.tag = None
+    return q
+
+
 DECODE_CHUNK_KEYS = 256     # keys per partial of the streaming decode kernel, a constant of the kernel
 DECODE_TC_MAX_ROWS = 512       # sequences that one launch of the tcgen05 decode kernel takes
 DECODE_TC_CHUNK_KEYS = 128  # keys per partial of the tensor-core decode kernel

@@ -41,13 +41,50 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
 
 launches = 0  # kernels of this library launched (or captured into a graph) so far
 
+# The profiling switch (the counterpart of HunyuanDenseModel.ProfileEnabled and its tick counters,
+# src/HyMT2Sharp/HunyuanDenseModel.cs:48-78): between profile_begin() and profile_end() every launch on the current
+# stream is followed by a CUDA event, and the time between two events is booked under the launch's name, or under
+# `tag` where a caller set one (a Linear names the product it is: "qkv", "o_proj", ...).  Kernels then run one after
+# the other (an event between two launches keeps the second from starting early), so the sum is more than an
+# unprofiled step takes; the shares are what it is for.  Not for captured steps.
+tag: str | None = None
+_profile: list | None = None
 
-def _check(rc: int, what: str, kernels: int = 1) -> None:
+
+def profile_begin() -> None:
+    global _profile
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    _profile = [(None, e)]
+
+
+def profile_end() -> dict:
+    """{name: milliseconds} of everything launched since profile_begin(), in the order of first appearance."""
+    global _profile
+    events, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    out: dict = {}
+    for (_, before), (name, after) in zip(events, events[1:]):
+        out[name] = out.get(name, 0.0) + before.elapsed_time(after)
+    return out
+
+
+def profile_line(phase: str, times: dict) -> str:
+    """One line in the manner of src/HyMT2Sharp.Benchmark/Program.cs:243-261."""
+    body = " ".join(f"{k}={v:.2f}ms" for k, v in times.items())
+    return f"profile {phase}: {body} accounted={sum(times.values()):.2f}ms"
+
+
+def _check(rc: int, what: str, kernels: int = 1, timed: bool = True) -> None:
     global launches
     launches += kernels
     if rc != 0:
         msg = _lib().hymt2_last_error().decode(errors="replace")
         raise KernelError(f"{what} failed ({rc}): {msg}")
+    if _profile is not None and timed and kernels > 0:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        _profile.append((tag or what, e))
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:
@@ -62,14 +99,14 @@ def _need(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:
 
 
 # ---------------------------------------------------------------------------
-def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t] = float32(table[ids[t]]); out is [T, hidden] float32."""
+def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = float32(table[ids[t]]) * scale; out is [T, hidden] float32."""
     _need(out, "out", torch.float32, 2); _need(table, "table", None, 2); _need(ids, "ids", torch.int32, 1)
     T, H = out.shape
     if table.shape[1] != H or ids.shape[0] < T:
         raise KernelError(f"embed: shapes out {tuple(out.shape)} table {tuple(table.shape)} ids {tuple(ids.shape)}")
     _check(_lib().hymt2_embed(_ptr(out), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), c_int(T),
-                              c_int(H), c_int(table.shape[0]), _ptr(status), _stream()), "embed")
+                              c_int(H), c_int(table.shape[0]), c_float(scale), _ptr(status), _stream()), "embed")
 
 
 def advance_decode(token_pos: torch.Tensor, kv_lens: torch.Tensor, slot_ids: torch.Tensor) -> None:
@@ -100,7 +137,7 @@ def prefetch_beside(t: torch.Tensor) -> None:
     event.record(main)
     side.wait_event(event)
     with torch.cuda.stream(side):
-        _check(_lib().hymt2_l2_prefetch(_ptr(t), c_long(nbytes), _stream()), "l2_prefetch")
+        _check(_lib().hymt2_l2_prefetch(_ptr(t), c_long(nbytes), _stream()), "l2_prefetch", timed=False)
     _side[key][2] = True
 
 
@@ -115,8 +152,8 @@ def join_beside(device) -> None:
 
 
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float,
-            rows_index: torch.Tensor | None = None) -> None:
-    """out[r] = rmsnorm(x[rows_index[r]] or x[r]) * gain, computed in float32."""
+            rows_index: torch.Tensor | None = None, out_scale: float = 1.0) -> None:
+    """out[r] = rmsnorm(x[rows_index[r]] or x[r]) * gain * out_scale, computed in float32."""
     _need(out, "out", None, 2); _need(x, "x", None, 2); _need(gain, "gain", None, 1)
     rows, dim = out.shape
     if x.shape[1] != dim or gain.shape[0] != dim:
@@ -129,7 +166,7 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float,
         raise KernelError("rmsnorm: x has fewer rows than out")
     _check(_lib().hymt2_rmsnorm(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(x), c_int(dtype_code(x.dtype)),
                                 _ptr(gain), c_int(dtype_code(gain.dtype)), _ptr(rows_index), c_int(rows),
-                                c_int(dim), c_float(eps), _stream()), "rmsnorm")
+                                c_int(dim), c_float(eps), c_float(out_scale), _stream()), "rmsnorm")
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
@@ -229,6 +266,20 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, 
                                 c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream()), "gemm_tc")
 
 
+def gemm_tc_debug(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor,
+                  wait_limit: int, withhold_block: int) -> None:
+    """gemm_tc with a fault put in on purpose: the copies of k block `withhold_block` are announced and never made,
+    and every wait gives up after `wait_limit` tries.  The kernel must set status[0] = 102, free what it holds and
+    return; `out` is then not a product.  Only products of few tokens whose K is not cut are taken."""
+    T, N = out.shape
+    K = a.shape[1]
+    if a.shape[0] != T or w.shape != (N, K) or not gemm_tc_supported(out, a, w, epilogue):
+        raise KernelError("gemm_tc_debug: operands are not taken")
+    _check(_lib().hymt2_gemm_tc_debug(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(T), c_int(N), c_int(K),
+                                      c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)), c_int(epilogue),
+                                      _ptr(status), _stream(), c_int(wait_limit), c_int(withhold_block)), "gemm_tc_debug")
+
+
 def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: int, d: int, cache_dtype, rope_dim: int) -> bool:
     """Whether the fused projection + rotation + cache append takes these operands: bfloat16, head_dim 128, and
     either few enough tokens that the product is cut over K among clusters (any even rope_dim), or more than 128
@@ -304,6 +355,18 @@ def gemm_tc_describe(tokens: int, out_features: int, inner: int, epilogue: int, 
         raise KernelError(f"gemm_tc_describe failed ({rc}): {_lib().hymt2_last_error().decode(errors='replace')}")
     keys = ("swapped", "persistent", "tile_width", "stages", "k_splits", "cluster", "tiles", "ctas")
     return {k: (bool(v) if k in ("swapped", "persistent", "cluster") else int(v)) for k, v in zip(keys, out)}
+
+
+def protocol_numbers() -> dict:
+    """The numbers that the barrier protocols of the tcgen05 kernels are built on, as compiled (stages, slots, barriers
+    per purpose, issuers): what an exploration of the protocols has to be run with.  Works without a GPU."""
+    def ask(fn, names):
+        out = (ctypes.c_int * 8)()
+        getattr(_lib(), fn)(out)
+        return dict(zip(names, out))
+    return {"prefill": ask("hymt2_attention_prefill_tc_protocol", ("kv_stages", "k_slots", "p_bars", "o_bars", "stage_holders", "s_buffers")),
+            "decode": ask("hymt2_attention_decode_tc_protocol", ("stages", "accumulators")),
+            "gemm": ask("hymt2_gemm_tc_protocol", ("max_stages", "accumulators", "issuers", "issuers_own_stages"))}
 
 
 def gemm_tc_rope_kv_wants_angles(tokens: int, rope_dim: int) -> bool:

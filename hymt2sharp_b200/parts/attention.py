@@ -16,7 +16,7 @@ import torch
 from ..cache.allocator import GroupSpec
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import MixerSlot, PartSpec, build_part, register_part
+from .base import MixerSlot, PartSpec, RotaryEpilogue, build_part, register_part
 from .linear import Linear, compute_form
 
 SPLIT_KEYS = 256  # decode: keys per partial, a constant so that the cut depends on nothing else
@@ -61,8 +61,8 @@ class GQAAttention:
     def load(self, weights, device, dtype):
         n = self.names
         fused = torch.cat([weights[n["q"]], weights[n["k"]], weights[n["v"]]], dim=0)
-        self.qkv = Linear(compute_form(fused, device, dtype))
-        self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE)
+        self.qkv = Linear(compute_form(fused, device, dtype), role="qkv")
+        self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="o_proj")
         if self.qk_norm:
             self.q_gain = compute_form(weights[n["qn"]], device, dtype)
             self.k_gain = compute_form(weights[n["kn"]], device, dtype)
@@ -73,36 +73,27 @@ class GQAAttention:
 
     # -- the step ---------------------------------------------------------------
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot) -> None:
+        from ..kernels import fast
         T = ctx.num_tokens
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim
-        table = self.position.rotary_table() if self.position is not None else None
-        inv_freq, rope_dim = table if table is not None else (None, 0)
+        # the position encoding in the form that the appending kernels take, or None: it rotates q and k itself
+        epilogue = self.position.kernel_epilogue(ctx) if self.position is not None else RotaryEpilogue.none()
         k_plane, v_plane = ctx.cache.plane(slot.group, slot.plane)
         block_table = ctx.cache.tables[slot.group]
-        fused = (table is not None or self.position is None) and x.shape[0] == T and \
-            ops.gemm_tc_rope_kv_supported(x, self.qkv.weight, nh, nkv, d, k_plane.dtype, rope_dim)
-        if fused:
-            # projection, rotation, norm and cache append are one kernel
-            q = torch.empty((T, nh * d), dtype=x.dtype, device=x.device)
-            angles = None
-            if ops.gemm_tc_rope_kv_wants_angles(T, rope_dim):
-                # a prompt's worth of tokens: their angles once per step, not once per head and layer
-                key = ("rotary angles", inv_freq.data_ptr())
-                angles = ctx.shared.get(key)
-                if angles is None:
-                    angles = ctx.shared[key] = ops.rope_angles(ctx.token_pos[:T], inv_freq)
-            ops.gemm_tc_rope_kv(x, self.qkv.weight, q, k_plane if slot.writes else None, v_plane if slot.writes else None,
-                                block_table, ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids, inv_freq,
-                                rope_dim, self.q_gain, self.k_gain, self.eps, nh, nkv, ops.device_status(x.device),
-                                angles=angles)
-        else:
+        planes = (k_plane, v_plane) if slot.writes else (None, None)
+        q = None
+        if epilogue is not None and x.shape[0] == T:
+            # projection, rotation, norm and cache append as one kernel, where the kernels have one for the shape
+            q = fast.try_project_rope_kv(x, self.qkv.weight, epilogue, ctx, planes, k_plane.dtype, block_table,
+                                         self.q_gain, self.k_gain, self.eps, nh, nkv, d)
+        if q is None:
             qkv = self.qkv(x)
-            if table is None and self.position is not None:
+            if epilogue is None:
                 self.position.apply(qkv, ctx, nh, nkv, d)
+                epilogue = RotaryEpilogue.none()
             q = torch.empty((T, nh * d), dtype=qkv.dtype, device=qkv.device)
-            ops.rope_kv(qkv, q, k_plane if slot.writes else None, v_plane if slot.writes else None, block_table,
-                        ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids, inv_freq, rope_dim,
-                        self.q_gain, self.k_gain, self.eps, nh, nkv, d)
+            ops.rope_kv(qkv, q, planes[0], planes[1], block_table, ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos,
+                        ctx.slot_ids, epilogue.inv_freq, epilogue.rope_dim, self.q_gain, self.k_gain, self.eps, nh, nkv, d)
         out = torch.empty((T, nh * d), dtype=q.dtype, device=q.device)
         self.attend(out, q, k_plane, v_plane, block_table, ctx)
         if ctx.decode and ctx.weights_ahead is not None:

@@ -14,17 +14,23 @@ Interfaces (duck-typed, see the classes in this package for examples):
   norm
       forward(x [rows, dim], ctx, out_dtype, rows_index=None) -> [rows, dim]
   position encoding
-      rotary_table() -> (inv_freq float32 [rope_dim/2], rope_dim) or None
-      apply(qkv, ctx, heads, kv_heads, head_dim) -> None   (in place; used when rotary_table() is None)
+      kernel_epilogue(ctx) -> RotaryEpilogue or None
+          what the kernels that append k and v can do on the way (rotate-half pairs by a table of
+          frequencies); None: the encoding has no such form and rotates q and k itself in `apply`
+      apply(qkv, ctx, heads, kv_heads, head_dim) -> None   (in place; used when kernel_epilogue() is None)
   mixer
       cache_need() -> GroupSpec or None      (planes is filled in by the model)
       state_bytes() -> int                   (fixed-size state per sequence)
+      graph_safe: bool                       (its forward launches kernels on the current stream and nothing else)
       forward(x [T, hidden], residual float32 [T, hidden], ctx, slot: MixerSlot) -> None
           adds its output to `residual`
   feed-forward
       forward(x [T, hidden], residual float32 [T, hidden], ctx) -> None
-  block
-      forward(residual, ctx, slot: MixerSlot) -> None
+  block  (it may hold any number of mixers, none included; the model asks the block, never its parts)
+      cache_needs() -> [GroupSpec or None]   one entry per mixer it holds, in a fixed order
+      state_bytes() -> [int]                 one entry per mixer, same order
+      graph_safe: bool                       every part it holds is graph_safe
+      forward(residual, ctx, slots: [MixerSlot]) -> None     slots[i] belongs to the i-th mixer
 
 New kinds are added with `register_part(category, kind, factory)`; a model
 spec names parts by (category, kind) and gives the factory's parameters.
@@ -59,6 +65,19 @@ def build_part(category: str, spec: "PartSpec"):
 class PartSpec:
     kind: str
     params: dict = field(default_factory=dict)
+
+
+@dataclass
+class RotaryEpilogue:
+    """A position encoding in the form that the kernels take which rotate q and k while they append k and v to the
+    cache: dims i and i + rope_dim/2 are a pair, rotated by position * inv_freq[i]; dims from rope_dim on stay."""
+    inv_freq: torch.Tensor | None     # float32 [rope_dim / 2] on the device; None with rope_dim 0
+    rope_dim: int
+    pairing: str = "half"             # the only pairing the kernels know; anything else is refused by them
+
+    @staticmethod
+    def none() -> "RotaryEpilogue":
+        return RotaryEpilogue(None, 0)
 
 
 @dataclass

@@ -16,6 +16,17 @@ class PreNormBlock:
     def parts(self):
         return (self.norm1, self.mixer, self.norm2, self.feed_forward)
 
+    # -- what the model asks a block (never its parts): one entry per mixer it holds ---------------
+    def cache_needs(self) -> list:
+        return [self.mixer.cache_need()]
+
+    def state_bytes(self) -> list:
+        return [int(self.mixer.state_bytes())]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts())
+
     def tensors(self):
         t = {}
         for p in self.parts():
@@ -26,11 +37,11 @@ class PreNormBlock:
         for p in self.parts():
             p.load(weights, device, dtype)
 
-    def forward(self, residual, ctx, slot) -> None:
+    def forward(self, residual, ctx, slots) -> None:
         x = self.norm1.forward(residual, ctx, ctx.dtype)
         # what the feed-forward streams first, for a mixer whose last kernel can ask for it ahead of time
         ctx.weights_ahead = getattr(self.feed_forward, "first_weights", lambda: None)()
-        self.mixer.forward(x, residual, ctx, slot)
+        self.mixer.forward(x, residual, ctx, slots[0])
         ctx.weights_ahead = None
         x = self.norm2.forward(residual, ctx, ctx.dtype)
         self.feed_forward.forward(x, residual, ctx)

@@ -19,9 +19,10 @@ def compute_form(t: torch.Tensor, device, dtype: torch.dtype) -> torch.Tensor:
 class Linear:
     """y = epilogue(x @ W^T) with W [out, in]; for the SwiGLU epilogue W is [2*out, in]."""
 
-    def __init__(self, weight: torch.Tensor, epilogue: int = ops.EPILOGUE_STORE):
+    def __init__(self, weight: torch.Tensor, epilogue: int = ops.EPILOGUE_STORE, role: str | None = None):
         self.weight = weight
         self.epilogue = epilogue
+        self.role = role   # what a profile books this product under
         rows = weight.shape[0]
         self.out_features = rows // 2 if epilogue == ops.EPILOGUE_SWIGLU else rows
         self.in_features = weight.shape[1]
@@ -29,7 +30,11 @@ class Linear:
     def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None):
         if out is None:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
-        matmul(out, x, self.weight, self.epilogue)
+        ops.tag = self.role
+        try:
+            matmul(out, x, self.weight, self.epilogue)
+        finally:
+            ops.tag = None
         return out
 
 

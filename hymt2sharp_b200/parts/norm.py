@@ -24,10 +24,10 @@ class RMSNorm:
         self.gain = compute_form(weights[self.weight_name], device, dtype)
 
     def forward(self, x: torch.Tensor, ctx, out_dtype: torch.dtype, rows_index: torch.Tensor | None = None,
-                rows: int | None = None) -> torch.Tensor:
+                rows: int | None = None, scale: float = 1.0) -> torch.Tensor:
         n = rows if rows is not None else (rows_index.shape[0] if rows_index is not None else x.shape[0])
         out = torch.empty((n, self.dim), dtype=out_dtype, device=x.device)
-        ops.rmsnorm(out, x, self.gain, self.eps, rows_index)
+        ops.rmsnorm(out, x, self.gain, self.eps, rows_index, scale)
         return out
 
 

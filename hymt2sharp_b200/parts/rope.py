@@ -15,7 +15,7 @@ import math
 import numpy as np
 import torch
 
-from .base import register_part
+from .base import RotaryEpilogue, register_part
 
 
 _TABLES: dict = {}   # (device, the frequencies' bytes) -> their tensor on the device
@@ -46,8 +46,9 @@ class NeoXRotary:
             _TABLES[key] = torch.from_numpy(self._host).to(device)
         self.inv_freq = _TABLES[key]
 
-    def rotary_table(self):
-        return self.inv_freq, self.rope_dim
+    def kernel_epilogue(self, ctx) -> RotaryEpilogue:
+        """Rotate-half pairs by a table of frequencies: exactly what the appending kernels do on the way."""
+        return RotaryEpilogue(self.inv_freq if self.rope_dim else None, self.rope_dim)
 
     def apply(self, qkv, ctx, heads, kv_heads, head_dim):
         raise NotImplementedError("NeoXRotary is applied by the fused rotation kernel")

@@ -27,8 +27,8 @@ class SwiGLU:
     def load(self, weights, device, dtype):
         n = self.names
         stacked = torch.cat([weights[n["g"]], weights[n["u"]]], dim=0)
-        self.gate_up = Linear(compute_form(stacked, device, dtype), ops.EPILOGUE_SWIGLU)
-        self.down = Linear(compute_form(weights[n["d"]], device, dtype), ops.EPILOGUE_ACCUMULATE)
+        self.gate_up = Linear(compute_form(stacked, device, dtype), ops.EPILOGUE_SWIGLU, role="gate_up")
+        self.down = Linear(compute_form(weights[n["d"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="down")
 
     def first_weights(self):
         """The weights that this part's first kernel streams."""

@@ -134,7 +134,6 @@ def test_device_side_on_cpu_tensors():
     cache.free_slots([slots[0]])
     again = cache.alloc_slots(1)
     assert again == [slots[0]] and int(cache.state[again[0]].sum()) == 0  # zeroed when handed out
-    cache.begin_step([(more[0], 64 * 20)]) if False else None
     with pytest.raises(CacheFull):
         cache.begin_step([(more[0], 64 * 13)])
     cache.begin_step([(more[0], 64 * 9)])  # more columns than the table had

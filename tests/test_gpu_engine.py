@@ -237,3 +237,40 @@ def test_the_fast_kernels_are_what_a_bfloat16_step_of_full_size_heads_runs(model
     assert ops.gemm_tc_rope_kv_supported(torch.empty(1, 256, dtype=torch.bfloat16, device=DEV),
                                          eng.model.blocks[0].mixer.qkv.weight, 4, 2, 128, q.dtype, 128)
     eng.check()
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_engine_goes_on(model_dirs, plain_models):
+    """One tensor-core product is launched with a fault put in: the producer never copies one k block, so the MMA
+    issuer's wait for it gives up after a few thousand tries.  The kernel must say so in the status word (102), let
+    every role leave, free its tensor memory and return; Engine.check() raises and clears; the next step is right."""
+    from hymt2sharp_b200.engine.engine import EngineError, StepEntry
+    from hymt2sharp_b200.kernels import ops
+    plain = plain_models("H")
+    eng = _engine(model_dirs, "H", "bfloat16")
+    slot = eng.alloc_slots(1)[0]
+    toks = helpers.random_tokens(plain.cfg.vocab, 90, 31)
+    first = eng.step([StepEntry(slot, toks[:60], [59])]).cpu().numpy()
+    eng.check()
+
+    a = torch.randn(8, 128, device=DEV).to(torch.bfloat16)
+    w = torch.randn(256, 128, device=DEV).to(torch.bfloat16)
+    out = torch.zeros(8, 256, device=DEV)
+    plan = ops.gemm_tc_describe(8, 256, 128, ops.EPILOGUE_STORE)
+    assert plan["swapped"] and plan["k_splits"] == 1 and plan["ctas"] == 2      # the smallest launch there is
+    ops.gemm_tc_debug(out, a, w, ops.EPILOGUE_STORE, eng.status, wait_limit=4096, withhold_block=1)
+    torch.cuda.synchronize()                                                    # the kernel came back
+    assert int(eng.status[0].item()) == 102
+    with pytest.raises(EngineError, match="102"):
+        eng.check()
+    assert int(eng.status[0].item()) == 0
+    # the same product without the fault, then the engine's next steps
+    ops.gemm_tc(out, a, w, ops.EPILOGUE_STORE, eng.status)
+    assert torch.allclose(out.double(), a.double() @ w.double().T, rtol=2e-2, atol=2e-2)
+    rest = torch.cat([eng.step([StepEntry(slot, toks[60:80], list(range(20)))])] +
+                     [eng.step([StepEntry(slot, [t], [0])]) for t in toks[80:]]).cpu().numpy()
+    eng.check()
+    ref = plain.logits(toks).numpy()
+    helpers.assert_close(np.concatenate([first, rest]), ref[59:], "bfloat16", "after a wait that ran out")
+    with pytest.raises(ops.KernelError):        # a product whose K is cut over CTAs is not offered with a fault
+        ops.gemm_tc_debug(torch.zeros(8, 2048, device=DEV), torch.zeros(8, 2048, device=DEV, dtype=torch.bfloat16),
+                          torch.zeros(2048, 2048, device=DEV, dtype=torch.bfloat16), ops.EPILOGUE_STORE, eng.status, 4096, 1)

@@ -133,7 +133,7 @@ def test_block_part_equals_the_plain_layer(model_dirs, plain_models):
     ref = pm.layer(h, 1, torch.arange(90))
     ctx, plan = _context(cache, [(slot_id, 90)], torch.float32)
     residual = h.clone().to(DEV)
-    block.forward(residual, ctx, MixerSlot(group=0, plane=0))
+    block.forward(residual, ctx, [MixerSlot(group=0, plane=0)])
     assert torch.allclose(residual.cpu(), ref, atol=1e-5, rtol=1e-5)
 
 
@@ -178,7 +178,7 @@ def test_order_names_a_layer_twice_and_shares_a_cache(model_dirs, plain_models, 
         return spec
 
     eng2 = Engine(folder, dtype="float32", max_tokens=256, spec_override=shared)
-    assert eng2.model.groups[0].planes == 2 and not eng2.model.slots[2].writes
+    assert eng2.model.groups[0].planes == 2 and not eng2.model.slots[2][0].writes
     slot = eng2.alloc_slots(1)[0]
     whole = eng2.step([StepEntry(slot, toks, list(range(100)))]).cpu().numpy()
     eng2.free_slots([slot])

@@ -102,7 +102,7 @@ def test_toy_mixer_with_state(tmp_path):
 
     eng = Engine(str(tmp_path), dtype="float32", max_tokens=512)
     assert eng.model.state_bytes == 80 + 80 and len(eng.model.groups) == 1 and eng.model.groups[0].planes == 1
-    assert [s.state_bytes for s in eng.model.slots] == [80, 0, 80]
+    assert [s[0].state_bytes for s in eng.model.slots] == [80, 0, 80]
     toks = [helpers.random_tokens(97, n, 3 + n) for n in (40, 9)]
 
     def run(cuts):

@@ -1,9 +1,11 @@
-"""Two more toy parts, defined here and registered without any change to the library: a
+"""More toy parts, defined here and registered without any change to the library: a
 feed-forward with routing (every token goes to the one of a few small experts that a router
-picks) and another position encoding (neighbouring pairs are rotated, and with other
-frequencies than the library's).  A model alternates them with the library's own parts layer
-by layer; the engine's logits are compared with a plain whole-sequence computation written
-here, for the whole prompt, token by token, and in a batch of two.  Not a model of anyone's."""
+picks), another position encoding (neighbouring pairs are rotated, and with other
+frequencies than the library's), and a block that holds TWO mixers side by side (attention
+with its cache and a running sum with state of its own).  A model alternates them with the
+library's own parts layer by layer; the engine's logits are compared with a plain
+whole-sequence computation written here, for the whole prompt, token by token, and in a batch
+of two.  Not a model of anyone's."""
 import json
 import math
 
@@ -64,8 +66,8 @@ class NeighbourPairRotary:
         half = self.head_dim // 2
         self.freq = (self.base ** (-torch.arange(half, dtype=torch.float64) / half)).float().to(device)
 
-    def rotary_table(self):
-        return None
+    def kernel_epilogue(self, ctx):
+        return None   # no kernel rotates neighbouring pairs: `apply` does it
 
     def apply(self, qkv, ctx, heads, kv_heads, head_dim):
         T = ctx.num_tokens
@@ -203,3 +205,131 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
     eng.model.blocks[1].mixer.position.load(None, DEV, torch.float32)
     moved = run([(37, 12)])
     assert np.abs(moved[0] - whole[0]).max() > 1e-3
+
+
+class ParallelMixersBlock:
+    """h += attention(norm1(h)) + decayed_sum(norm1(h)); h += feed_forward(norm2(h)): two mixers in one block, one
+    with keys and values in the cache, one with a fixed-size state.  The model learns both needs from the block."""
+
+    def __init__(self, norm1, attention, running, norm2, feed_forward):
+        from hymt2sharp_b200.parts import build_part
+        self.norm1, self.norm2 = build_part("norm", norm1), build_part("norm", norm2)
+        self.attention, self.running = build_part("mixer", attention), build_part("mixer", running)
+        self.feed_forward = build_part("feed_forward", feed_forward)
+        self.graph_safe = False   # the running sum is plain torch on the host's lists
+
+    def _parts(self):
+        return (self.norm1, self.attention, self.running, self.norm2, self.feed_forward)
+
+    def tensors(self):
+        t = {}
+        for p in self._parts():
+            t.update(p.tensors())
+        return t
+
+    def load(self, weights, device, dtype):
+        for p in self._parts():
+            p.load(weights, device, dtype)
+
+    def cache_needs(self):
+        return [self.attention.cache_need(), self.running.cache_need()]
+
+    def state_bytes(self):
+        return [self.attention.state_bytes(), self.running.state_bytes()]
+
+    def forward(self, residual, ctx, slots):
+        x = self.norm1.forward(residual, ctx, ctx.dtype)   # both mixers read the same normed input
+        self.attention.forward(x, residual, ctx, slots[0])
+        self.running.forward(x, residual, ctx, slots[1])
+        self.feed_forward.forward(self.norm2.forward(residual, ctx, ctx.dtype), residual, ctx)
+
+
+def test_a_block_with_two_mixers(tmp_path):
+    from hymt2sharp_b200.config import register_architecture
+    from hymt2sharp_b200.engine.engine import Engine, StepEntry
+    from hymt2sharp_b200.engine.model import DecoderModel
+    from hymt2sharp_b200.engine.spec import ModelSpec
+    from hymt2sharp_b200.parts import PartSpec, register_part
+    from hymt2sharp_b200.weights import write_safetensors
+    from test_gpu_toy_mixer import DecaySumMixer
+
+    register_part("mixer", "toy_decay_sum", DecaySumMixer)
+    register_part("block", "toy_parallel_mixers", ParallelMixersBlock)
+    H, W, V, DECAY = 48, 12, 61, 0.8
+
+    def spec(cfg=None):
+        layers = []
+        for l in range(3):
+            p = f"l{l}."
+            norm = lambda n: PartSpec("rmsnorm", dict(dim=H, eps=EPS, weight=p + n))
+            attn = PartSpec("gqa_attention", dict(hidden=H, heads=2, kv_heads=1, head_dim=24, eps=EPS, qk_norm=False,
+                                                  position=None, q_proj=p + "q", k_proj=p + "k", v_proj=p + "v", o_proj=p + "o"))
+            ffn = PartSpec("swiglu", dict(hidden=H, intermediate=56, gate_proj=p + "g", up_proj=p + "u", down_proj=p + "d"))
+            if l == 1:   # the middle layer is one of the library's own blocks
+                layers.append(PartSpec("pre_norm", dict(norm1=norm("n1"), mixer=attn, norm2=norm("n2"), feed_forward=ffn)))
+            else:
+                run = PartSpec("toy_decay_sum", dict(hidden=H, width=W, decay=DECAY, proj=p + "proj", out=p + "out"))
+                layers.append(PartSpec("toy_parallel_mixers", dict(norm1=norm("n1"), attention=attn, running=run,
+                                                                   norm2=norm("n2"), feed_forward=ffn)))
+        # the embedding rows are scaled and so are the logits: both are plain numbers of the spec
+        return ModelSpec(V, H, "emb", layers, PartSpec("rmsnorm", dict(dim=H, eps=EPS, weight="norm")), head=None,
+                         embed_scale=3.0, logit_scale=0.25)
+
+    class Cfg:
+        architecture = "ToyTwoMixersForCausalLM"
+
+        @classmethod
+        def from_dict(cls, data, source="config.json"):
+            return cls()
+
+    register_architecture(Cfg.architecture, Cfg, spec, lambda cfg: DecoderModel(spec()).tensors())
+    (tmp_path / "config.json").write_text(json.dumps(dict(architectures=[Cfg.architecture])))
+    gen = torch.Generator().manual_seed(9)
+    tensors = {}
+    for name, ts in DecoderModel(spec()).tensors().items():
+        t = torch.randn(ts.shape, generator=gen) / math.sqrt(ts.shape[-1])
+        tensors[name] = ((1.0 + 0.1 * t) if ts.init == "gain" else t).to(torch.bfloat16)
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    w = {n: t.float() for n, t in tensors.items()}
+
+    eng = Engine(str(tmp_path), dtype="float32", max_tokens=512)
+    m = eng.model
+    assert not m.graph_safe and len(m.groups) == 1 and m.groups[0].planes == 3     # three attention mixers, one group
+    assert [[s.state_bytes for s in row] for row in m.slots] == [[0, 4 * W], [0], [0, 4 * W]]
+    assert m.state_bytes == 2 * 4 * W
+
+    def plain(tokens):
+        T = len(tokens)
+        h = w["emb"][torch.tensor(tokens)] * 3.0
+        for l in range(3):
+            p = f"l{l}."
+            x = rms_norm(h, w[p + "n1"], EPS)
+            q, k, v = ((x @ w[p + n].T).reshape(T, -1, 24) for n in "qkv")
+            add = causal_attention(q, k, v) @ w[p + "o"].T
+            if l != 1:
+                u, state = x @ w[p + "proj"].T, torch.zeros(W)
+                for t in range(T):
+                    state = DECAY * state + u[t]
+                    add[t] += state @ w[p + "out"].T
+            h = h + add
+            x = rms_norm(h, w[p + "n2"], EPS)
+            h = h + swiglu(x @ w[p + "g"].T, x @ w[p + "u"].T) @ w[p + "d"].T
+        return (0.25 * rms_norm(h, w["norm"], EPS) @ w["emb"].T).numpy()
+
+    toks = [helpers.random_tokens(V, 50, 1), helpers.random_tokens(V, 9, 2)]
+    for cuts in ([(50, 9)], [(20, 3), (1, 1), (1, 1), (28, 4)]):
+        slots = eng.alloc_slots(2)
+        rows, pos = [[], []], [0, 0]
+        for step in cuts:
+            entries = [StepEntry(slots[i], toks[i][pos[i]:pos[i] + n], list(range(n))) for i, n in enumerate(step) if n]
+            out = eng.step(entries).cpu()
+            o = 0
+            for i, n in enumerate(step):
+                rows[i].append(out[o:o + n]); o += n; pos[i] += n
+        eng.free_slots(slots)
+        for i in range(2):
+            helpers.assert_close(torch.cat(rows[i]).numpy(), plain(toks[i]), "float32", f"two mixers, cut {cuts[0]}, sequence {i}")
+    # generation goes the eager way for a model that says it is not safe to capture
+    out = eng.generate([toks[1]], max_new_tokens=4)
+    assert len(out.results[0].tokens) == 4
+    eng.check()

@@ -15,8 +15,16 @@ wait for whom, and that can be enumerated.  The roles, as in the kernel:
 
 Copies land and products complete at any later time (products of one issuer in order).  A first version with two
 barriers for P, two for O and the stage held by P·V alone met the never-ending wait on the device; the exploration
-finds it in that version within milliseconds, and finds none in the kernel's."""
+finds it in that version within milliseconds, and finds none in the kernel's.
+
+The numbers that the little programs are built from (stages, K slots, barriers per purpose, holders of a stage,
+accumulators, issuers) are not written here: they come out of the compiled kernels (ops.protocol_numbers, which
+returns the .cu files' own constants), so a change of one of them in a kernel changes what is explored."""
 import pytest
+
+from hymt2sharp_b200.kernels import ops
+
+NUMBERS = ops.protocol_numbers()
 
 
 def explore(roles, sizes, arrivals_needed=None):
@@ -87,17 +95,19 @@ def explore(roles, sizes, arrivals_needed=None):
     return None
 
 
-def prefill(tiles, p_bars, o_bars, stage_holders):
+def prefill(tiles, p_bars, o_bars, stage_holders, kv_stages=None):
+    kv = kv_stages or NUMBERS["prefill"]["kv_stages"]
+    assert NUMBERS["prefill"]["s_buffers"] == 2     # the score buffers go by a tile's parity, here as in the kernel
     producer = [("copy", "q", 0)]
     for i in range(tiles):
-        if i >= 2:
-            producer.append(("wait", "stage_free", i % 2, i // 2 - 1))
-        producer.append(("copy", "copied", i % 2))
+        if i >= kv:
+            producer.append(("wait", "stage_free", i % kv, i // kv - 1))
+        producer.append(("copy", "copied", i % kv))
     scores = [("wait", "q", 0, 0), ("issue", "S", [("s_done", 0)])]
     for i in range(tiles - 1):
-        scores.append(("wait", "copied", i % 2, i // 2))
+        scores.append(("wait", "copied", i % kv, i // kv))
         if stage_holders == 2:
-            scores.append(("arrive", "stage_free", i % 2))
+            scores.append(("arrive", "stage_free", i % kv))
         if i >= 2:
             scores.append(("wait", "o_done", (i - 2) % o_bars, (i - 2) // o_bars))
         if i >= 1:
@@ -106,24 +116,26 @@ def prefill(tiles, p_bars, o_bars, stage_holders):
     weighted = []
     for i in range(tiles):
         weighted.append(("wait", "p_written", i % p_bars, i // p_bars))
-        weighted.append(("wait", "copied", i % 2, i // 2))
-        weighted.append(("issue", "PV", [("stage_free", i % 2), ("o_done", i % o_bars)]))
+        weighted.append(("wait", "copied", i % kv, i // kv))
+        weighted.append(("issue", "PV", [("stage_free", i % kv), ("o_done", i % o_bars)]))
     softmax = []
     for i in range(tiles):
         softmax.append(("wait", "s_done", i & 1, i >> 1))
         if i > 0:
             softmax.append(("wait or not", "o_done", (i - 1) % o_bars, (i - 1) // o_bars))
         if i == tiles - 1:
-            softmax.append(("wait or not", "copied", i % 2, i // 2))
+            softmax.append(("wait or not", "copied", i % kv, i // kv))
         softmax.append(("arrive", "p_written", i % p_bars))
     softmax.append(("wait", "o_done", (tiles - 1) % o_bars, (tiles - 1) // o_bars))
-    sizes = {"q": 1, "copied": 2, "stage_free": 2, "s_done": 2, "o_done": o_bars, "p_written": p_bars}
+    sizes = {"q": 1, "copied": kv, "stage_free": kv, "s_done": 2, "o_done": o_bars, "p_written": p_bars}
     return explore((producer, scores, weighted, softmax), sizes, {"stage_free": stage_holders})
 
 
 @pytest.mark.parametrize("tiles", [1, 2, 3, 4, 5, 8, 13, 32])
 def test_no_interleaving_of_the_kernels_protocol_goes_wrong(tiles):
-    assert prefill(tiles, p_bars=3, o_bars=3, stage_holders=2) is None
+    n = NUMBERS["prefill"]     # as compiled: 2 stages, 3 barriers for P (one per K slot), 3 for O, 2 holders of a stage
+    assert n["p_bars"] == n["k_slots"]
+    assert prefill(tiles, p_bars=n["p_bars"], o_bars=n["o_bars"], stage_holders=n["stage_holders"]) is None
 
 
 @pytest.mark.parametrize("p_bars, o_bars, stage_holders", [(2, 2, 1), (2, 3, 2), (3, 2, 2), (3, 3, 1)])
@@ -142,7 +154,8 @@ def test_each_of_the_three_measures_is_needed(p_bars, o_bars, stage_holders):
 #   softmax groups group g takes the items n = g, g + 2, ...: wait S(n), sometimes wait V(n) (rows to clear), announce P(n),
 #                  wait O(n), free the accumulators
 def decode(items):
-    stages = 3
+    stages = NUMBERS["decode"]["stages"]
+    assert NUMBERS["decode"]["accumulators"] == 2   # two groups of softmax warps take turns, here as in the kernel
     producer, scores, weighted, groups = [], [], [], ([], [])
     for n in range(items):
         s, t = n % stages, n & 1
@@ -192,8 +205,10 @@ def persistent_gemm(tiles, k_blocks, stages):
     return explore((producer, issuer, epilogue), {"full": stages, "empty": stages, "acc_full": 2, "acc_empty": 2})
 
 
-@pytest.mark.parametrize("tiles, k_blocks, stages", [(1, 1, 4), (3, 2, 4), (5, 3, 2), (6, 4, 5), (4, 9, 4)])
+@pytest.mark.parametrize("tiles, k_blocks, stages", [(1, 1, 4), (3, 2, 4), (5, 3, 2), (6, 4, 5), (4, 9, 4),
+                                                     (3, 10, NUMBERS["gemm"]["max_stages"])])
 def test_no_interleaving_of_the_persistent_products_protocol_goes_wrong(tiles, k_blocks, stages):
+    assert NUMBERS["gemm"]["accumulators"] == 2 and 2 <= stages <= NUMBERS["gemm"]["max_stages"]
     assert persistent_gemm(tiles, k_blocks, stages) is None
 
 
@@ -215,8 +230,10 @@ def tile_gemm(blocks, stages, issuers, own):
     return explore((producer, *takers), {"full": stages, "empty": stages})
 
 
-@pytest.mark.parametrize("blocks, stages, issuers", [(32, 5, 2), (12, 6, 2), (20, 3, 2), (7, 2, 2), (18, 4, 1)])
+@pytest.mark.parametrize("blocks, stages", [(32, 5), (12, 6), (20, 3), (7, 2), (18, 4), (40, NUMBERS["gemm"]["max_stages"])])
+@pytest.mark.parametrize("issuers", sorted({1, NUMBERS["gemm"]["issuers"]}))
 def test_issuers_that_own_their_stages_never_misread_a_barrier(blocks, stages, issuers):
+    assert NUMBERS["gemm"]["issuers_own_stages"] == 1
     assert tile_gemm(blocks, stages, issuers, own=True) is None
 
 

@@ -13,10 +13,12 @@ def test_rotary_frequencies_and_their_sharing():
     c, d = NeoXRotary(128, 128, 5e6), NeoXRotary(128, 64, 10000.0)
     for part in (a, b, c, d):
         part.load({}, "cpu", torch.float32)
-    table, rope_dim = a.rotary_table()
+    epi = a.kernel_epilogue(None)
+    table, rope_dim = epi.inv_freq, epi.rope_dim
+    assert epi.pairing == "half"
     assert rope_dim == 128 and table.dtype == torch.float32 and table.shape == (64,)
     want = [1.0 / math.pow(10000.0, i / 64) for i in range(64)]
     assert torch.allclose(table.double(), torch.tensor(want, dtype=torch.float64), rtol=1e-6)
-    assert b.rotary_table()[0].data_ptr() == table.data_ptr()
-    assert c.rotary_table()[0].data_ptr() != table.data_ptr()
-    assert d.rotary_table()[0].data_ptr() != table.data_ptr() and d.rotary_table()[0].shape == (32,)
+    assert b.kernel_epilogue(None).inv_freq.data_ptr() == table.data_ptr()
+    assert c.kernel_epilogue(None).inv_freq.data_ptr() != table.data_ptr()
+    assert d.kernel_epilogue(None).inv_freq.data_ptr() != table.data_ptr() and d.kernel_epilogue(None).inv_freq.shape == (32,)

@@ -113,3 +113,45 @@ def test_sharded_checkpoint(model_dirs, tmp_path):
     (tmp_path / "config.json").write_text(open(os.path.join(folder, "config.json")).read())
     w = load_checkpoint(str(tmp_path), _expected(str(tmp_path)))
     assert all(torch.equal(w[n], src.tensor(n)) for n in names)
+
+
+def test_harmless_extra_tensors_are_reported_not_refused(model_dirs, tmp_path):
+    """A folder that the reference would run (it looks its tensors up by name) may hold a recomputed rotary buffer
+    and, with a tied head, the head once more under its own name: both are left unread with a warning.  A head copy
+    with OTHER values, and any other extra tensor, stay errors."""
+    from hymt2sharp_b200.engine.hunyuan_dense import build_spec
+    folder = model_dirs("A")   # tie_word_embeddings is set
+    arch, cfg = load_config(folder)
+    src = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = {n: src.tensor(n).clone() for n in src.names()}
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    (tmp_path / "config.json").write_text(open(os.path.join(folder, "config.json")).read())
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    ignorable = build_spec(cfg).ignorable_tensors
+    with pytest.warns(RuntimeWarning, match="not read") as rec:
+        w = load_checkpoint(str(tmp_path), _expected(str(tmp_path)), ignorable)
+    assert "inv_freq" in str(rec[0].message) and "lm_head.weight (a copy of model.embed_tokens.weight)" in str(rec[0].message)
+    assert "lm_head.weight" not in w and set(w) == set(src.names())
+    with pytest.raises(WeightError) as e:     # without the architecture's say-so the buffer is unexpected
+        load_checkpoint(str(tmp_path), _expected(str(tmp_path)))
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    tensors["lm_head.weight"][3, 5] += 1.0
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    with pytest.raises(WeightError, match="holds other values"):
+        load_checkpoint(str(tmp_path), _expected(str(tmp_path)), ignorable)
+
+
+def test_index_that_names_the_wrong_shard(model_dirs, tmp_path):
+    folder = model_dirs("A")
+    src = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    names = src.names()
+    shards = {"a.safetensors": names[:5], "b.safetensors": names[5:]}
+    for fn, ns in shards.items():
+        write_safetensors(str(tmp_path / fn), {n: src.tensor(n) for n in ns})
+    weight_map = {n: fn for fn, ns in shards.items() for n in ns}
+    weight_map[names[0]] = "b.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    (tmp_path / "config.json").write_text(open(os.path.join(folder, "config.json")).read())
+    with pytest.raises(WeightError, match="which does not hold it"):
+        load_checkpoint(str(tmp_path), _expected(str(tmp_path)))
