@@ -218,7 +218,7 @@ def run_verify(config: str, layers: int) -> dict:
         from plain.hunyuan_plain import PlainModel
         plain = PlainModel(folder)
         t0 = time.time()
-        res = verify_split(folder, requests, dtypes=("float32",), reference=lambda toks: plain.logits(toks))
+        res = verify_split(folder, requests, reference=lambda toks: plain.logits(toks))
         res["seconds"] = round(time.time() - t0, 1)
         out["layers_2_against_plain"] = res
     finally:
@@ -383,7 +383,8 @@ def main() -> int:
     out = engine.generate(prompts, max_new_tokens=steps + 1, max_batch=batch)
     e2e_tokens = out.stats.decode_tokens
     e2e = {"value": e2e_tokens / max(out.stats.decode_ms, 1e-9) * 1000.0, "unit": "tokens/s",
-           "h2d_bytes_per_step": 4 * batch, "d2h_bytes_per_step": 4 * batch,
+           # every step: which rows run (slot and row number of each, int32) from pinned memory; the sampled tokens back
+           "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 4 * batch,
            "decode_ms": out.stats.decode_ms, "prefill_ms": out.stats.prefill_ms}
 
     profile = None

@@ -136,5 +136,10 @@ class PagedCache:
 
     def _send_row(self, slot: int, groups, lo: int, hi: int) -> None:
         for g in groups:
-            # a copy from pageable memory is staged before it returns: the host row may change right after
-            self.tables[g][slot, lo:hi].copy_(torch.from_numpy(self.host_tables[g][slot, lo:hi].copy()))
+            # through pinned memory and without waiting: a copy from pageable memory makes the host wait for all the work
+            # that the stream still holds (steps that were launched ahead).  The pinned piece is a copy of the row as it
+            # is now (the host row may change right after) and goes back to torch's pool once the transfer has run.
+            src = torch.from_numpy(self.host_tables[g][slot, lo:hi].copy())
+            if self.device.type == "cuda":
+                src = src.pin_memory()
+            self.tables[g][slot, lo:hi].copy_(src, non_blocking=True)

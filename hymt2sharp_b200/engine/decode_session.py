@@ -32,14 +32,19 @@ class DecodeSlot:
         dev = engine.device
         B = rows
         self.rows, self.max_total_len = rows, max_total_len
-        # one buffer, fixed offsets: tokens | token_seq | token_pos | cu_seqlens | slot_ids | kv_lens | want
-        self.meta = torch.zeros(7 * B + 1, dtype=torch.int32, device=dev)
-        o = [0, B, 2 * B, 3 * B, 4 * B + 1, 5 * B + 1, 6 * B + 1, 7 * B + 1]
-        v = [self.meta[o[i]:o[i + 1]] for i in range(7)]
-        self.tokens, self.token_seq, self.token_pos, self.cu, self.slot_ids, self.kv_lens, self.want = v
-        self.row_map = torch.zeros(B, dtype=torch.int32, device=dev)
+        # one buffer, fixed offsets: tokens | token_seq | token_pos | cu_seqlens | slot_ids | row_map | kv_lens | want
+        # (slot_ids and row_map lie side by side: together they say which rows run, and go to the device in one copy)
+        self.meta = torch.zeros(8 * B + 1, dtype=torch.int32, device=dev)
+        o = [0, B, 2 * B, 3 * B, 4 * B + 1, 5 * B + 1, 6 * B + 1, 7 * B + 1, 8 * B + 1]
+        v = [self.meta[o[i]:o[i + 1]] for i in range(8)]
+        self.tokens, self.token_seq, self.token_pos, self.cu, self.slot_ids, self.row_map, self.kv_lens, self.want = v
+        self.rows_running = self.meta[o[4]:o[6]]
         self.host_in = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.host_out = torch.zeros(B, dtype=torch.int32).pin_memory()
+        # for steps that are launched ahead of the host: two sets of pinned buffers and events that take turns
+        self.host_running = [torch.zeros(2 * B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.host_tokens = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.copied = [torch.cuda.Event() for _ in range(2)]
         self.sampler_tensors = None
         self.argmax_scratch = None
         self.graph = None
@@ -74,12 +79,11 @@ class DecodeSession:
         with torch.cuda.device(engine.device):
             self.buf = decode_slot(engine, B, max_total_len, sampler)
             self.max_total_len = self.buf.max_total_len
+            row_map = [r if alive else -1 for r, alive in enumerate(self.live)]
             host = np.concatenate([np.zeros(B), np.arange(B), np.asarray(lens), np.arange(B + 1), np.asarray(dev_slots),
-                                   np.asarray(lens) + 1, np.arange(B)]).astype(np.int32)
+                                   np.asarray(row_map), np.asarray(lens) + 1, np.arange(B)]).astype(np.int32)
             self.buf.meta.copy_(torch.from_numpy(host))
             self.buf.tokens.copy_(first_tokens.to(torch.int32))
-            self.buf.row_map.copy_(torch.tensor([r if alive else -1 for r, alive in enumerate(self.live)],
-                                                dtype=torch.int32))
             if self.buf.sampler_tensors is None:   # the first batch of this shape lends its tensors to the slot
                 self.buf.sampler_tensors = sampler.tensors()
                 self.buf.argmax_scratch = sampler.ensure_argmax_scratch(B, engine.vocab)
@@ -184,6 +188,29 @@ class DecodeSession:
         b.host_out.copy_(b.tokens, non_blocking=True)
         torch.cuda.current_stream(self.engine.device).synchronize()
         return b.host_out.tolist()
+
+    def step_async(self) -> int:
+        """The step for a caller that does not want to wait for it: which rows still run goes to the device from pinned
+        memory, the step runs on the tokens that the step before left on the device, and the sampled tokens start their
+        way to pinned host memory.  Returns a ticket for wait().  At most two steps may be in flight."""
+        b = self.buf
+        k = self.steps & 1
+        running = b.host_running[k].numpy()
+        for r, alive in enumerate(self.live):
+            running[r] = self.slots[r] if alive else -1
+            running[self.rows + r] = r if alive else -1
+        with torch.cuda.device(self.engine.device):
+            b.rows_running.copy_(b.host_running[k], non_blocking=True)
+            self.step()
+            b.host_tokens[k].copy_(b.tokens, non_blocking=True)
+            b.copied[k].record()
+        return k
+
+    def wait(self, ticket: int) -> list:
+        """The tokens that the step of this ticket sampled, one for every row of the batch (rows that do not run keep
+        what they held)."""
+        self.buf.copied[ticket].synchronize()
+        return self.buf.host_tokens[ticket].tolist()
 
     def _capture(self) -> None:
         # one eager step first (it also sets up what kernels set up at their first launch), then

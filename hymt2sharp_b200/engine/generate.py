@@ -166,6 +166,24 @@ class EngineStepper:
         out = self.session.step_host(dict(zip(rows, tokens)))
         return [out[r] for r in rows]
 
+    # -- the same without a wait in every step: launch(rows) starts a step and the copy of its tokens to the host,
+    #    collect() waits for the OLDEST step that was launched and not yet collected -------------------------------
+    def launch(self, rows: list) -> None:
+        """One more token for the batch rows `rows`, whose last tokens are already on the device (the step before left
+        them there).  What goes to the device from pinned host memory is which rows still run; nothing is waited for."""
+        if self.session is None:
+            from .decode_session import DecodeSession
+            longest = max(len(p) for p in self.prompts) + self.max_new_tokens
+            self.session = DecodeSession(self.engine, self.slots, self.sampler, self._first, longest, self.use_graph,
+                                         live_rows=set(self.held))
+        self._flying = getattr(self, "_flying", [])
+        self._flying.append((list(rows), self.session.step_async()))
+
+    def collect(self) -> list:
+        rows, ticket = self._flying.pop(0)
+        out = self.session.wait(ticket)
+        return [out[r] for r in rows]
+
     def release(self, rows: list) -> None:
         rows = [r for r in rows if r in self.held]
         self.held.difference_update(rows)
@@ -209,6 +227,8 @@ def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None
         if profiler and state.live:
             profiler.profile_begin()
         profiling = bool(profiler and state.live)
+        if hasattr(stepper, "launch") and not profiling:
+            _decode_ahead(stepper, state, stats, on_tokens)
         while state.live:
             rows_before = list(state.live)
             tokens = stepper.decode(rows_before, state.last_tokens())
@@ -224,6 +244,41 @@ def run_batch(stepper, state: BatchState, stats: GenerationStats, on_tokens=None
         stats.decode_ms += (clock() - t0) * 1000.0
     finally:
         stepper.close()
+
+
+def _decode_ahead(stepper, state: BatchState, stats: GenerationStats, on_tokens) -> None:
+    """The decode loop with one step in flight beyond the one whose tokens the host is looking at: step n + 1 is
+    launched before step n's tokens are waited for, so the device never idles while the host decides.  The price: a
+    sequence that sampled a stop token in step n has already run in step n + 1; that extra token is dropped here, and
+    the row leaves with the launch after.  A sequence that reaches its token limit leaves without that lag (the limit
+    needs no token to be seen).  The tokens and reasons are those of the loop that waits every step."""
+    produced = {r: len(state.outputs[r]) for r in state.live}     # tokens launched so far for each row, the prompt's first included
+    running = list(state.live)                                     # rows that the next launch takes
+    flying: list = []                                              # rows of the launches that are not collected yet, oldest first
+    gone: set = set()                                              # rows that were released already
+    while running or flying:
+        if running:
+            stepper.launch(running)
+            flying.append(list(running))
+            for r in running:
+                produced[r] += 1
+            at_limit = [r for r in running if produced[r] >= state.max_new_tokens]
+            running = [r for r in running if produced[r] < state.max_new_tokens]
+            stepper.release(at_limit)           # their last token is on its way; they take no further step
+            gone.update(at_limit)
+        if len(flying) > 1 or not running:
+            rows, tokens = flying.pop(0), stepper.collect()
+            by_row = dict(zip(rows, tokens))
+            live_before = list(state.live)      # rows that had not ended by the tokens of the steps before
+            go_on, ended = state.accept([by_row[r] for r in live_before])
+            stats.decode_steps += 1
+            stats.decode_tokens += len(live_before)
+            if on_tokens:
+                on_tokens([(state.request_ids[r], by_row[r]) for r in live_before if state.reasons[r] != "stop"])
+            stopped = [r for r in ended if r in running]
+            running = [r for r in running if r not in stopped]
+            stepper.release([r for r in ended if r not in gone])
+            gone.update(ended)
 
 
 def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_token_ids=(),

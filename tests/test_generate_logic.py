@@ -96,3 +96,51 @@ def test_plan_batches():
     with pytest.raises(ValueError):
         plan_batches([0], 1, 8, 64 * 4, 64)
     assert plan_batches([], 5, 8, 640, 64) == []
+
+
+class AheadStepper(ScriptedStepper):
+    """A stepper that can run a step ahead of the host: launch() starts a step, collect() hands over the oldest one's tokens."""
+
+    def __init__(self, scripts):
+        super().__init__(scripts)
+        self.flying = []
+        self.most_in_flight = 0
+
+    def launch(self, rows):
+        self.calls.append(("launch", list(rows)))
+        self.flying.append(self._next(rows))
+        self.most_in_flight = max(self.most_in_flight, len(self.flying))
+
+    def collect(self):
+        self.calls.append(("collect",))
+        return self.flying.pop(0)
+
+
+def test_a_step_ahead_gives_the_same_tokens_and_reasons():
+    """With a step in flight beyond the one the host looks at, a stop token is seen one launch late: the extra token is
+    dropped, the row leaves with the next launch; a row at its limit leaves at once.  Results are those of the waiting loop."""
+    scripts = [[5, 6, 99, 41, 42], [7, 99, 43, 44, 45], [8, 9, 10, 11, 12]]
+    waiting, ahead = ScriptedStepper(scripts), AheadStepper(scripts)
+    results, streams = [], []
+    for stepper in (waiting, ahead):
+        state = BatchState(["a", "b", "c"], [3, 4, 5], max_new_tokens=4, stop_token_ids=[99])
+        stats = GenerationStats()
+        seen = []
+        run_batch(stepper, state, stats, on_tokens=seen.extend, clock=lambda: 0.0)
+        results.append([(r.tokens, r.finish_reason) for r in state.results()])
+        streams.append(seen)
+        assert stats.decode_steps == 3 and stats.decode_tokens == 6 and stepper.closed
+    assert results[0] == results[1] == [([5, 6], "stop"), ([7], "stop"), ([8, 9, 10, 11], "length")]
+    assert streams[0] == streams[1]
+    # b's stop (sampled by launch 1) is seen after launch 2, which therefore still has b; c reaches its limit with launch 3
+    assert ahead.calls == [("prefill", [0, 1, 2]), ("launch", [0, 1, 2]), ("launch", [0, 1, 2]), ("collect",),
+                           ("launch", [0, 2]), ("collect",), ("collect",)]
+    assert ahead.most_in_flight == 2 and sorted(ahead.released) == [0, 1, 2]
+
+
+def test_a_step_ahead_with_a_limit_of_two_and_an_immediate_stop():
+    ahead = AheadStepper([[1, 2, 3], [99, 5, 6], [4, 99, 7]])
+    state = BatchState([0, 1, 2], [1, 1, 1], max_new_tokens=2, stop_token_ids={99})
+    run_batch(ahead, state, GenerationStats())
+    assert [(r.tokens, r.finish_reason) for r in state.results()] == [([1, 2], "length"), ([], "stop"), ([4], "stop")]
+    assert ahead.calls == [("prefill", [0, 1, 2]), ("launch", [0, 2]), ("collect",)]   # one launch: both rows are at their limit
