@@ -65,6 +65,33 @@ struct RopeEpilogue {
     float eps;
 };
 
+// An RMSNorm (src/HyMT2Sharp/Ops.cs:29-89) folded into the products around it.  The row scale r = 1/sqrt(mean(x^2) + eps) of the
+// norm commutes with the product that follows it: (r * (x * gain)) W^T = r * ((x * gain) W^T).  So a product that ADDS into the
+// residual (the only place where a residual row changes) can leave bf16(x * gain) and the row's sum of squares behind,
+// and the product after it multiplies its sums by r: no kernel of its own reads the row again.  The sums of squares are
+// partial, one per token and tile of output features of the producing launch; the consumer adds them in tile order.
+struct NormSide {
+    // producer (EPI_ACCUMULATE): null, or where bf16(C_new * gain) goes ([T, N] contiguous), with the gain and the partial sums
+    __nv_bfloat16* out;
+    const void* gain;
+    int gain_bf16;
+    float* ss_out;           // [T][ss_out_tiles]
+    int ss_out_tiles;
+    // consumer: null, or the partial sums of the activations' rows ([T][ss_in_tiles]), the width of a row and the norm's eps
+    const float* ss_in;
+    int ss_in_tiles, ss_width;
+    float ss_eps;
+};
+
+__device__ __forceinline__ float norm_row_scale(const NormSide& ns, int t) {
+    float ss = 0.f;
+    for (int m = 0; m < ns.ss_in_tiles; m++) ss += ns.ss_in[(size_t)t * ns.ss_in_tiles + m];
+    return 1.0f / sqrtf(ss / (float)ns.ss_width + ns.ss_eps);
+}
+__device__ __forceinline__ float norm_gain_at(const NormSide& ns, int n) {
+    return ns.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)ns.gain)[n]) : ((const float*)ns.gain)[n];
+}
+
 struct GemmTcParams {
     void* C;
     long ldc;
@@ -79,6 +106,7 @@ struct GemmTcParams {
     RopeEpilogue rope;       // EPI_ROPE_KV only
     uint32_t wait_limit;     // tries of a bounded wait in the one-tile kernel (WAIT_LIMIT, less in the debug entry)
     int withhold_block;      // -1; the debug entry names a k block whose copies the producer does NOT issue
+    NormSide norm;
 };
 
 // The copies of one stage (activations, weights, and for a split weight tile its second half) with, in front of them, a
@@ -179,7 +207,7 @@ __device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const float* v
 // over all 128 (rope_dim 128) or none (0), RMSNorm over the head where the model has it, then q to its tensor, k and v
 // to the token's row of the paged cache.  Every thread of the warp comes along (the tensor-memory accesses are
 // warp-wide); `active` says whether the token exists.
-__device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int head, bool active, const RopeEpilogue& rp) {
+__device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int head, bool active, const RopeEpilogue& rp, float row_scale) {
     const bool is_q = head < rp.nh, is_k = !is_q && head < rp.nh + rp.nkv;
     int pos = 0, slot = -1;
     if (active) {
@@ -204,7 +232,7 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
 #pragma unroll
     for (int c = 0; c < TILE_M; c += 16) tmem_load<16>(head_at + c, v + c);
 #pragma unroll
-    for (int i = 0; i < TILE_M; i++) v[i] = bf16_round(v[i]);      // what the projection would have stored
+    for (int i = 0; i < TILE_M; i++) v[i] = bf16_round(v[i] * row_scale);      // what the projection would have stored
     if (rotate) {
         const float4* angles = reinterpret_cast<const float4*>(rp.angles) + (size_t)(active ? t : 0) * (HALF / 2);
 #pragma unroll
@@ -267,6 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (EPI != EPI_ROPE_KV) pdl_launch_dependents();
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
+    __shared__ float scale_s[SWAPPED ? BN : 1], norm_red_s[4];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
@@ -387,6 +416,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         pdl_wait();   // C, the workspace and the counters may still be in use by the kernel before
         if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();   // wait first, release after
+        if (SWAPPED && EPI != EPI_ACCUMULATE && p.norm.ss_in) {
+            // the row scale of the norm in front of this product, for the tile's tokens (see NormSide)
+            const int tl = threadIdx.x - 64;
+            if (tl < BN) scale_s[tl] = b_row0 + tl < p.T ? norm_row_scale(p.norm, b_row0 + tl) : 0.f;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        const bool scaled = SWAPPED && EPI != EPI_ACCUMULATE && p.norm.ss_in != nullptr;
+        float ss_acc = 0.f;   // normal orientation, producer of a norm: this thread's token row, summed over the tile's features
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103, p.wait_limit) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         TC* C = (TC*)p.C;
@@ -425,9 +462,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int t = b_row0 + c + j;              // token
                     if (t >= p.T) break;
                     TC* dst = C + (size_t)t * p.ldc + n;
-                    if (EPI == EPI_STORE) *dst = from_float<TC>(g[j]);
+                    const float r = scaled ? scale_s[c + j] : 1.0f;
+                    if (EPI == EPI_STORE) *dst = from_float<TC>(g[j] * r);
                     else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[j] + g[j]);
-                    else *dst = from_float<TC>(silu_mul(g[j], u[j]));
+                    else *dst = from_float<TC>(silu_mul(g[j] * r, u[j] * r));
                 }
             } else {
                 const int m = a_row0 + row;                    // token
@@ -450,8 +488,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 if (EPI == EPI_ACCUMULATE) {
                                     const float4 old = d4[q];
                                     v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                                    o[4 * q] = v.x; o[4 * q + 1] = v.y; o[4 * q + 2] = v.z; o[4 * q + 3] = v.w;
                                 }
                                 d4[q] = v;
+                            }
+                            if (EPI == EPI_ACCUMULATE && p.norm.out) {   // the new residual values, times the gain, as the next product's input
+                                __nv_bfloat162 h[4];
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    const float a = o[2 * q], b = o[2 * q + 1];
+                                    ss_acc = fmaf(a, a, ss_acc); ss_acc = fmaf(b, b, ss_acc);
+                                    h[q] = __floats2bfloat162_rn(a * norm_gain_at(p.norm, n0 + j8 + 2 * q), b * norm_gain_at(p.norm, n0 + j8 + 2 * q + 1));
+                                }
+                                *reinterpret_cast<uint4*>(p.norm.out + (size_t)m * p.N + n0 + j8) = *reinterpret_cast<uint4*>(h);
                             }
                         } else {
                             uint4* d4 = reinterpret_cast<uint4*>(dst + j8);
@@ -470,7 +519,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             if (n0 + j8 + j >= p.N) break;
-                            dst[j8 + j] = from_float<TC>(EPI == EPI_ACCUMULATE ? to_float(dst[j8 + j]) + o[j] : o[j]);
+                            const float v = EPI == EPI_ACCUMULATE ? to_float(dst[j8 + j]) + o[j] : o[j];
+                            dst[j8 + j] = from_float<TC>(v);
+                            if (EPI == EPI_ACCUMULATE && p.norm.out) {
+                                ss_acc = fmaf(v, v, ss_acc);
+                                p.norm.out[(size_t)m * p.N + n0 + j8 + j] = __float2bfloat16_rn(v * norm_gain_at(p.norm, n0 + j8 + j));
+                            }
                         }
                     }
                 }
@@ -488,6 +542,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     emit(c, g, u);
                 }
+                // a norm's producer in the normal orientation: this thread's token, this tile's features
+                if (!SWAPPED && EPI == EPI_ACCUMULATE && p.norm.out && a_row0 + row < p.T)
+                    p.norm.ss_out[(size_t)(a_row0 + row) * p.norm.ss_out_tiles + blockIdx.y] = ss_acc;
             }
         } else if (SWAPPED && p.cluster) {
             // partial tile -> this CTA's shared memory (the stage ring is free now), [column][row].  After the
@@ -525,6 +582,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float g = 0.f, u = 0.f;
 #pragma unroll
                     for (int r = 0; r < MAX_RANKS; r++) { g += pg[r]; u += pu[r]; }
+                    if (scaled) { g *= scale_s[c]; u *= scale_s[c]; }
                     if constexpr (EPI == EPI_ROPE_KV) {
                         // this tile is head blockIdx.x of token b_row0 + c, this thread its value d = row
                         const RopeEpilogue& rp = p.rope;
@@ -572,6 +630,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             else if (write_kv) rp.k_cache[cache_at] = __float2bfloat16_rn(y);
                             asm volatile("bar.sync 1, 128;" ::: "memory");   // the next column trades through the same words
                         }
+                    } else if (EPI == EPI_ACCUMULATE && p.norm.out) {
+                        // the residual's new value, and for the norm that follows: bf16(value * gain) and the sum of squares
+                        // of this token over the tile's 128 features
+                        float v = 0.f;
+                        if (n < p.N) {
+                            TC* dst = C + (size_t)(b_row0 + c) * p.ldc + n;
+                            v = to_float(*dst) + g;
+                            *dst = from_float<TC>(v);
+                            p.norm.out[(size_t)(b_row0 + c) * p.N + n] = __float2bfloat16_rn(v * norm_gain_at(p.norm, n));
+                        }
+                        const float sq = warp_sum(v * v);
+                        if (lane == 0) norm_red_s[quarter] = sq;
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (threadIdx.x == 64)
+                            p.norm.ss_out[(size_t)(b_row0 + c) * p.norm.ss_out_tiles + blockIdx.x] = (norm_red_s[0] + norm_red_s[1]) + (norm_red_s[2] + norm_red_s[3]);
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
                     } else if (n < p.N) {
                         TC* dst = C + (size_t)(b_row0 + c) * p.ldc + n;
                         if (EPI == EPI_STORE) *dst = from_float<TC>(g);
@@ -781,13 +855,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
             const int m = a_row0 + row;
+            // a norm folded into this product (see NormSide): the row scale of this thread's token, or its sum of squares
+            const float row_scale = (EPI != EPI_ACCUMULATE && p.norm.ss_in && m < p.T) ? norm_row_scale(p.norm, m) : 1.0f;
+            float ss_acc = 0.f;
             if constexpr (EPI == EPI_ROPE_KV) {
                 // the tile holds BN / 128 heads of 128 tokens: this thread's token, head after head
                 const int heads = p.rope.nh + 2 * p.rope.nkv;
 #pragma unroll 1
                 for (int h = 0; h < bn / TILE_M; h++) {
                     const int head = b_row0 / TILE_M + h;
-                    if (head < heads) rope_head_from_tmem(lane_addr + h * TILE_M, m, head, m < p.T, p.rope);
+                    if (head < heads) rope_head_from_tmem(lane_addr + h * TILE_M, m, head, m < p.T, p.rope, row_scale);
                 }
             } else
 #pragma unroll 1
@@ -803,7 +880,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 for (int j8 = 0; j8 < 16; j8 += 8) {
                     float o[8];
 #pragma unroll
-                    for (int q = 0; q < 8; q++) o[q] = EPI == EPI_SWIGLU ? silu_mul(g[j8 + q], u[j8 + q]) : g[j8 + q];
+                    for (int q = 0; q < 8; q++)
+                        o[q] = EPI == EPI_SWIGLU ? silu_mul(g[j8 + q] * row_scale, u[j8 + q] * row_scale)
+                             : EPI == EPI_STORE ? g[j8 + q] * row_scale : g[j8 + q];
                     if (vec) {
                         if constexpr (sizeof(TC) == 4) {
                             float4* d4 = reinterpret_cast<float4*>(dst + j8);
@@ -813,8 +892,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                                 if (EPI == EPI_ACCUMULATE) {
                                     const float4 old = d4[q];
                                     v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                                    o[4 * q] = v.x; o[4 * q + 1] = v.y; o[4 * q + 2] = v.z; o[4 * q + 3] = v.w;
                                 }
                                 d4[q] = v;
+                            }
+                            if (EPI == EPI_ACCUMULATE && p.norm.out) {
+                                __nv_bfloat162 h[4];
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    const float a = o[2 * q], b = o[2 * q + 1];
+                                    ss_acc = fmaf(a, a, ss_acc); ss_acc = fmaf(b, b, ss_acc);
+                                    h[q] = __floats2bfloat162_rn(a * norm_gain_at(p.norm, n0 + j8 + 2 * q), b * norm_gain_at(p.norm, n0 + j8 + 2 * q + 1));
+                                }
+                                *reinterpret_cast<uint4*>(p.norm.out + (size_t)m * p.N + n0 + j8) = *reinterpret_cast<uint4*>(h);
                             }
                         } else {
                             __nv_bfloat162 h[4];
@@ -826,11 +916,17 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll
                         for (int q = 0; q < 8; q++) {
                             if (n0 + j8 + q >= p.N) break;
-                            dst[j8 + q] = from_float<TC>(EPI == EPI_ACCUMULATE ? to_float(dst[j8 + q]) + o[q] : o[q]);
+                            const float v = EPI == EPI_ACCUMULATE ? to_float(dst[j8 + q]) + o[q] : o[q];
+                            dst[j8 + q] = from_float<TC>(v);
+                            if (EPI == EPI_ACCUMULATE && p.norm.out) {
+                                ss_acc = fmaf(v, v, ss_acc);
+                                p.norm.out[(size_t)m * p.N + n0 + j8 + q] = __float2bfloat16_rn(v * norm_gain_at(p.norm, n0 + j8 + q));
+                            }
                         }
                     }
                 }
             }
+            if (EPI == EPI_ACCUMULATE && p.norm.out && m < p.T) p.norm.ss_out[(size_t)m * p.norm.ss_out_tiles + tile / tiles_m] = ss_acc;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(acc_empty0 + 8 * buf);   // this thread has taken its row out of the accumulator
         }
@@ -1049,9 +1145,17 @@ HYMT2_API int hymt2_gemm_tc_describe(int T, int N, int K, int epilogue, int sm_c
 }
 
 namespace {
+// How many partial sums of squares per token a product that adds into the residual leaves behind for the norm after it:
+// one per tile of output features (0: this plan cannot, and the norm runs as a kernel of its own).
+int norm_out_tiles(const Plan& pl, int epilogue) {
+    if (epilogue != EPI_ACCUMULATE) return 0;
+    if (pl.swapped) return (pl.splits > 1 && pl.cluster) ? (int)pl.grid.x : 0;   // the cluster's fold holds (token, tile) whole
+    return (int)pl.grid.y;                                                        // a thread owns a token's row of the tile
+}
+
 int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw, long ldc,
                 int epilogue, float* workspace, long workspace_floats, int* counters, int num_counters, int* status,
-                cudaStream_t stream, uint32_t wait_limit, int withhold_block) {
+                cudaStream_t stream, uint32_t wait_limit, int withhold_block, NormSide norm = NormSide{}) {
     if (T == 0 || N == 0) return HYMT2_OK;
     HYMT2_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
     HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K, lda and ldw must be multiples of 8 (K=%d lda=%ld ldw=%ld)", K, lda, ldw);
@@ -1073,8 +1177,14 @@ int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N
         ok = make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, w_rows, K, ldw, epilogue == EPI_SWIGLU ? pl.bn / 2 : pl.bn);
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
+    if (norm.out) {
+        HYMT2_REQUIRE(c_dtype == HYMT2_F32 && norm_out_tiles(pl, epilogue) > 0 && norm.gain && norm.ss_out && N % 8 == 0 &&
+                      (uintptr_t)norm.out % 16 == 0, "gemm_tc: this product (T=%d N=%d K=%d epilogue %d) cannot leave a norm's input behind", T, N, K, epilogue);
+        norm.ss_out_tiles = norm_out_tiles(pl, epilogue);
+    }
+    if (norm.ss_in) HYMT2_REQUIRE(epilogue != EPI_ACCUMULATE && norm.ss_in_tiles > 0 && norm.ss_width > 0, "gemm_tc: bad row-scale arguments");
     GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
-                   RopeEpilogue{}, wait_limit, withhold_block};
+                   RopeEpilogue{}, wait_limit, withhold_block, norm};
     if (withhold_block >= 0)
         HYMT2_REQUIRE(pl.swapped && pl.splits == 1, "gemm_tc_debug: only the one-tile kernel without a cut of K can withhold a block "
                       "(T=%d N=%d K=%d gives swapped=%d splits=%d)", T, N, K, (int)pl.swapped, pl.splits);
@@ -1097,6 +1207,28 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
                             int num_counters, int* status, cudaStream_t stream) {
     return run_gemm_tc(C, c_dtype, X, W, T, N, K, lda, ldw, ldc, epilogue, workspace, workspace_floats, counters, num_counters,
                        status, stream, WAIT_LIMIT, -1);
+}
+
+// hymt2_gemm_tc with an RMSNorm folded in (see NormSide).  As a consumer (ss_in): the activations X are bf16(x * gain) and the sums
+// are multiplied by 1/sqrt(sum_tiles ss_in[t] / ss_width + ss_eps) (store and SwiGLU epilogues).  As a producer (norm_out, accumulate
+// epilogue into float32): bf16(C_new * gain) goes to norm_out [T, N] and the partial sums of squares to ss_out [T][tiles], tiles as
+// hymt2_gemm_tc_norm_tiles says (0: not offered for this shape).
+HYMT2_API int hymt2_gemm_tc_norm_tiles(int T, int N, int K, int epilogue) {
+    if (T <= 0 || N <= 0 || K <= 0 || N % 8) return 0;
+    Plan pl;
+    make_plan(T, N, K, epilogue, sm_count_of_current_device(), &pl);
+    return norm_out_tiles(pl, epilogue);
+}
+
+HYMT2_API int hymt2_gemm_tc_norm(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,
+                                 long ldc, int epilogue, float* workspace, long workspace_floats, int* counters,
+                                 int num_counters, int* status, cudaStream_t stream, const float* ss_in, int ss_in_tiles,
+                                 int ss_width, float ss_eps, void* norm_out, const void* norm_gain, int norm_gain_dtype,
+                                 float* ss_out) {
+    HYMT2_REQUIRE(!norm_out || norm_gain_dtype == HYMT2_BF16 || norm_gain_dtype == HYMT2_F32, "gemm_tc_norm: the gain must be bfloat16 or float32");
+    NormSide ns{(__nv_bfloat16*)norm_out, norm_gain, norm_gain_dtype == HYMT2_BF16 ? 1 : 0, ss_out, 0, ss_in, ss_in_tiles, ss_width, ss_eps};
+    return run_gemm_tc(C, c_dtype, X, W, T, N, K, lda, ldw, ldc, epilogue, workspace, workspace_floats, counters, num_counters,
+                       status, stream, WAIT_LIMIT, -1, ns);
 }
 
 // The same product with one fault put in on purpose, for the test of the bounded waits: the producer announces
@@ -1137,9 +1269,11 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
                                     void* v_cache, const int* block_table, int table_stride, int block_tokens,
                                     const int* token_seq, const int* token_pos, const int* slot_ids, const float* inv_freq,
                                     const float* angles, int rope_dim, const void* q_gain, const void* k_gain, int gain_dtype,
-                                    float eps, int nh, int nkv, int write_kv, int* status, cudaStream_t stream) {
+                                    float eps, int nh, int nkv, int write_kv, int* status, cudaStream_t stream,
+                                    const float* ss_in, int ss_in_tiles, int ss_width, float ss_eps) {
     if (T == 0) return HYMT2_OK;
     const int N = (nh + 2 * nkv) * TILE_M;
+    HYMT2_REQUIRE(!ss_in || (ss_in_tiles > 0 && ss_width > 0), "gemm_tc_rope_kv: bad row-scale arguments");
     HYMT2_REQUIRE(T > 0 && nh > 0 && nkv > 0 && K > 0, "gemm_tc_rope_kv: bad sizes T=%d nh=%d nkv=%d K=%d", T, nh, nkv, K);
     HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_rope_kv: K, lda and ldw must be multiples of 8");
     HYMT2_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc_rope_kv: operands must be 16-byte aligned");
@@ -1162,7 +1296,7 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
                       slot_ids, inv_freq, angles, q_gain, k_gain, table_stride, block_tokens, nh, nkv, rope_dim, write_kv,
                       gain_dtype == HYMT2_BF16 ? 1 : 0, eps};
     GemmTcParams p{nullptr, 0, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, nullptr, nullptr, status, rope,
-                   WAIT_LIMIT, -1};
+                   WAIT_LIMIT, -1, NormSide{nullptr, nullptr, 0, nullptr, 0, ss_in, ss_in_tiles, ss_width, ss_eps}};
     if (pl.persistent) {
         const int ctas = pl.tiles < pl.sm_count ? pl.tiles : pl.sm_count;
         return launch_persistent_one<PERSISTENT_BN, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);

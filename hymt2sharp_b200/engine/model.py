@@ -133,8 +133,13 @@ class DecoderModel:
         T = ctx.num_tokens
         residual = torch.empty((T, self.spec.hidden), dtype=torch.float32, device=ctx.device)
         ops.embed(residual, self.embedding, ctx.tokens, ctx.status, self.spec.embed_scale or 1.0)
-        for run, slots in zip(self.spec.order, self.slots):
+        order = self.spec.order
+        for i, (run, slots) in enumerate(zip(order, self.slots)):
+            # the first norm of the block that runs next, for a block whose last product can prepare it (parts.base.Prenormed)
+            nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            ctx.next_first_norm = getattr(nxt, "first_norm", lambda: None)() if nxt is not None else None
             self.blocks[run.layer].forward(residual, ctx, slots)
+        ctx.next_first_norm = ctx.prenormed = None
         ops.join_beside(ctx.device)   # what parts asked into L2 on the side stream
         if num_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=ctx.device)

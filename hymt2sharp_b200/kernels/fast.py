@@ -6,16 +6,37 @@ from __future__ import annotations
 import torch
 
 
-def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int) -> bool:
-    """bfloat16 operands with 16-byte aligned rows go to the tcgen05 kernel; anything else is refused."""
+def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int, row_scale: tuple | None = None) -> bool:
+    """bfloat16 operands with 16-byte aligned rows go to the tcgen05 kernel; anything else is refused.  `row_scale`: see
+    ops.gemm_tc (the activations are a norm's input times its gain; the row scale is applied to the sums)."""
     from . import ops
     if not ops.gemm_tc_supported(out, x, w, epilogue):
         return False
-    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device))
+    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device), row_scale=row_scale)
     return True
 
 
-def try_project_rope_kv(x, weight, epilogue, ctx, planes, cache_dtype, block_table, q_gain, k_gain, eps, nh, nkv, d):
+def try_matmul_then_norm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, gain: torch.Tensor):
+    """out += x @ w^T on the tcgen05 kernel, which also leaves behind what the RMSNorm after it needs: returns
+    (bf16(out_new * gain) [T, N], partial sums of squares [T, tiles]); or None (nothing ran) where the kernel or this
+    shape's plan cannot do that."""
+    from . import ops
+    T, N = out.shape
+    if gain.dtype not in (torch.bfloat16, torch.float32) or out.dtype != torch.float32 or not out.is_contiguous() or N % 8:
+        return None
+    if not ops.gemm_tc_supported(out, x, w, ops.EPILOGUE_ACCUMULATE):
+        return None
+    tiles = ops.gemm_tc_norm_tiles(T, N, x.shape[1], ops.EPILOGUE_ACCUMULATE)
+    if tiles == 0:
+        return None
+    normed = torch.empty((T, N), dtype=torch.bfloat16, device=out.device)
+    ss = torch.empty((T, tiles), dtype=torch.float32, device=out.device)
+    ops.gemm_tc(out, x, w, ops.EPILOGUE_ACCUMULATE, ops.device_status(out.device), norm_after=(normed, gain, ss))
+    return normed, ss
+
+
+def try_project_rope_kv(x, weight, epilogue, ctx, planes, cache_dtype, block_table, q_gain, k_gain, eps, nh, nkv, d,
+                        row_scale: tuple | None = None):
     """The fused q/k/v projection whose epilogue rotates, norms and appends to the cache (tcgen05, heads of 128,
     rotate-half pairs): returns q [T, nh * d], or None when that kernel does not take the operands and the caller
     goes the two-kernel way.  `planes` = (k_plane, v_plane), or (None, None) for a run that writes no keys."""
@@ -37,7 +58,7 @@ def try_project_rope_kv(x, weight, epilogue, ctx, planes, cache_dtype, block_tab
     try:
         ops.gemm_tc_rope_kv(x, weight, q, planes[0], planes[1], block_table, ctx.cache.block_tokens, ctx.token_seq,
                             ctx.token_pos, ctx.slot_ids, epilogue.inv_freq, epilogue.rope_dim, q_gain, k_gain, eps, nh, nkv,
-                            ops.device_status(x.device), angles=angles)
+                            ops.device_status(x.device), angles=angles, row_scale=row_scale)
     finally:
         ops.tag = None
     return q

@@ -245,9 +245,21 @@ def gemm_tc_supported(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
     return out.dtype == torch.bfloat16
 
 
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor) -> None:
+def gemm_tc_norm_tiles(tokens: int, out_features: int, inner: int, epilogue: int) -> int:
+    """How many partial sums of squares per token gemm_tc leaves behind when it is asked to prepare the norm that follows it
+    (`norm_after`); 0: this shape's plan cannot, and the norm runs as a kernel of its own."""
+    return int(_lib().hymt2_gemm_tc_norm_tiles(c_int(tokens), c_int(out_features), c_int(inner), c_int(epilogue)))
+
+
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor,
+            row_scale: tuple | None = None, norm_after: tuple | None = None) -> None:
     """out[T, N] = epilogue(a[T, K] @ w[N, K]^T) on the tcgen05 tensor cores (bfloat16 operands,
-    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows."""
+    float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows.
+
+    An RMSNorm can be folded into the products around it.  `row_scale` = (ss [T, tiles] float32, width, eps): `a` holds
+    bf16(x * gain) and the sums are multiplied by 1 / sqrt(sum(ss[t]) / width + eps) (store and SwiGLU epilogues).
+    `norm_after` = (normed [T, N] bfloat16, gain [N], ss [T, gemm_tc_norm_tiles(...)] float32), accumulate epilogue only:
+    bf16(out_new * gain) and the partial sums of squares of the new rows are written for the product that comes next."""
     T, N = out.shape
     K = a.shape[1]
     rows_w = 2 * N if epilogue == EPILOGUE_SWIGLU else N
@@ -260,10 +272,26 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, 
     ws = cnt = None
     if floats.value:
         ws, cnt = _tc_workspace(out.device, floats.value, counters.value)
-    _check(_lib().hymt2_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(T), c_int(N), c_int(K),
-                                c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)), c_int(epilogue),
-                                _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(cnt),
-                                c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream()), "gemm_tc")
+    ss_in = normed = gain = ss_out = None
+    tiles_in, width, eps = 0, 0, 0.0
+    if row_scale is not None:
+        ss_in, width, eps = row_scale
+        _need(ss_in, "row_scale sums", torch.float32, 2)
+        if ss_in.shape[0] < T or epilogue == EPILOGUE_ACCUMULATE:
+            raise KernelError("gemm_tc: row_scale needs sums for every token and a store or SwiGLU epilogue")
+        tiles_in = ss_in.shape[1]
+    if norm_after is not None:
+        normed, gain, ss_out = norm_after
+        tiles = gemm_tc_norm_tiles(T, N, K, epilogue)
+        _need(normed, "normed", torch.bfloat16, 2); _need(gain, "gain", None, 1); _need(ss_out, "ss_out", torch.float32, 2)
+        if tiles == 0 or normed.shape != (T, N) or gain.shape[0] != N or ss_out.shape != (T, tiles) or out.dtype != torch.float32:
+            raise KernelError(f"gemm_tc: norm_after does not fit T={T} N={N} K={K} epilogue {epilogue} (tiles {tiles})")
+    _check(_lib().hymt2_gemm_tc_norm(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(T), c_int(N), c_int(K),
+                                     c_long(a.stride(0)), c_long(w.stride(0)), c_long(out.stride(0)), c_int(epilogue),
+                                     _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(cnt),
+                                     c_int(cnt.numel() if cnt is not None else 0), _ptr(status), _stream(),
+                                     _ptr(ss_in), c_int(tiles_in), c_int(width), c_float(eps), _ptr(normed), _ptr(gain),
+                                     c_int(dtype_code(gain.dtype) if gain is not None else F32), _ptr(ss_out)), "gemm_tc")
 
 
 def gemm_tc_debug(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor,
@@ -298,11 +326,13 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
                     v_plane: torch.Tensor | None, block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor,
                     token_pos: torch.Tensor, slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int,
                     q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float, nh: int, nkv: int,
-                    status: torch.Tensor, angles: torch.Tensor | None = None) -> None:
+                    status: torch.Tensor, angles: torch.Tensor | None = None, row_scale: tuple | None = None) -> None:
     """q_out[T, nh*128] = rotation and per-head norm of the query part of x @ w^T; the key part, rotated and
     normed, and the value part go to the rows of the cache planes that (slot, position) of every token name
     (k_plane None: nothing is written).  One tcgen05 kernel; head_dim 128; see rope_kv for the arguments.
-    `angles`: what rope_angles(token_pos, inv_freq) gave, where gemm_tc_rope_kv_wants_angles says so."""
+    `angles`: what rope_angles(token_pos, inv_freq) gave, where gemm_tc_rope_kv_wants_angles says so.
+    `row_scale` = (ss [T, tiles] float32, width, eps): x holds bf16(h * gain) of an RMSNorm whose row scale is applied to the
+    projection's sums here (see gemm_tc)."""
     d = 128
     T = x.shape[0]
     if gemm_tc_rope_kv_wants_angles(T, rope_dim):
@@ -342,7 +372,9 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
                                         c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq), _ptr(token_pos),
                                         _ptr(slot_ids), _ptr(inv_freq), _ptr(angles), c_int(rope_dim), _ptr(q_gain), _ptr(k_gain),
                                         c_int(gain_dtype), c_float(eps), c_int(nh), c_int(nkv), c_int(1 if write else 0),
-                                        _ptr(status), _stream()), "gemm_tc_rope_kv")
+                                        _ptr(status), _stream(), _ptr(row_scale[0] if row_scale else None),
+                                        c_int(row_scale[0].shape[1] if row_scale else 0), c_int(row_scale[1] if row_scale else 0),
+                                        c_float(row_scale[2] if row_scale else 0.0)), "gemm_tc_rope_kv")
 
 
 def gemm_tc_describe(tokens: int, out_features: int, inner: int, epilogue: int, sm_count: int = 0) -> dict:

@@ -16,7 +16,7 @@ import torch
 from ..cache.allocator import GroupSpec
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import MixerSlot, PartSpec, RotaryEpilogue, build_part, register_part
+from .base import MixerSlot, PartSpec, Prenormed, RotaryEpilogue, build_part, register_part
 from .linear import Linear, compute_form
 
 SPLIT_KEYS = 256  # decode: keys per partial, a constant so that the cut depends on nothing else
@@ -24,6 +24,7 @@ SPLIT_KEYS = 256  # decode: keys per partial, a constant so that the cut depends
 
 class GQAAttention:
     graph_safe = True  # its forward only launches kernels on the current stream
+    takes_prenormed = True  # x may be a parts.base.Prenormed: the projection applies the norm's row scale itself
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, eps: float, qk_norm: bool,
                  position: PartSpec | None, q_proj: str, k_proj: str, v_proj: str, o_proj: str,
@@ -82,12 +83,14 @@ class GQAAttention:
         block_table = ctx.cache.tables[slot.group]
         planes = (k_plane, v_plane) if slot.writes else (None, None)
         q = None
+        pre = x if isinstance(x, Prenormed) else None
         if epilogue is not None and x.shape[0] == T:
             # projection, rotation, norm and cache append as one kernel, where the kernels have one for the shape
-            q = fast.try_project_rope_kv(x, self.qkv.weight, epilogue, ctx, planes, k_plane.dtype, block_table,
-                                         self.q_gain, self.k_gain, self.eps, nh, nkv, d)
+            q = fast.try_project_rope_kv(pre.normed if pre else x, self.qkv.weight, epilogue, ctx, planes, k_plane.dtype,
+                                         block_table, self.q_gain, self.k_gain, self.eps, nh, nkv, d,
+                                         row_scale=pre.row_scale() if pre else None)
         if q is None:
-            qkv = self.qkv(x)
+            qkv = self.qkv(x, ctx=ctx)
             if epilogue is None:
                 self.position.apply(qkv, ctx, nh, nkv, d)
                 epilogue = RotaryEpilogue.none()
@@ -101,7 +104,7 @@ class GQAAttention:
             # the memory idle; the request starts once the attention is through (not earlier: its last loads and
             # the folding of its partials are sensitive to traffic)
             ops.prefetch_beside(ctx.weights_ahead)
-        self.out(out, out=residual)
+        self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
 
     def attend(self, out, q, k_plane, v_plane, block_table, ctx) -> None:
         from ..kernels import fast

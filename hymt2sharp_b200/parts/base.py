@@ -81,6 +81,38 @@ class RotaryEpilogue:
 
 
 @dataclass
+class Prenormed:
+    """An RMSNorm's output in two pieces, left behind by the product that last changed the residual rows: `normed` =
+    bf16(x * gain) [T, dim] and `ss` = partial sums of squares of x's rows [T, tiles].  The product that consumes it applies
+    the row scale 1 / sqrt(sum(ss) / dim + eps) to its own sums (kernels.ops.gemm_tc, `row_scale`), so the norm never runs
+    as a kernel.  Only parts that say `takes_prenormed = True` are handed one; `materialize()` gives the plain tensor."""
+    normed: torch.Tensor
+    ss: torch.Tensor
+    dim: int
+    eps: float
+    source: torch.Tensor          # the residual rows it was made from
+    norm: object                  # the norm part it stands for
+
+    @property
+    def shape(self):
+        return self.normed.shape
+
+    @property
+    def dtype(self):
+        return self.normed.dtype
+
+    @property
+    def device(self):
+        return self.normed.device
+
+    def row_scale(self) -> tuple:
+        return (self.ss, self.dim, self.eps)
+
+    def materialize(self, ctx) -> torch.Tensor:
+        return self.norm.forward(self.source, ctx, self.normed.dtype, fresh=True)
+
+
+@dataclass
 class MixerSlot:
     """Where one run of a mixer keeps what it remembers."""
     group: int | None = None      # cache group of its keys and values
@@ -121,6 +153,13 @@ class StepContext:
     # what parts worked out from the step's tokens and other parts of the same kind can use again, by key: the
     # angles of a rotary table, say, are the same in every layer that rotates by that table
     shared: dict = field(default_factory=dict)
+    # An RMSNorm can be folded into the products around it (see Prenormed).  Whoever arranges the parts names the norm that
+    # will be applied next to the residual rows (`norm_ahead`: set by a block around its mixer and its feed-forward; the
+    # model names `next_first_norm`, the first norm of the block after this one); a part whose last product adds into the
+    # residual may then leave a Prenormed in `prenormed`, and that norm hands it on instead of running.
+    norm_ahead: object = None
+    next_first_norm: object = None
+    prenormed: object = None
 
     @property
     def decode(self) -> bool:

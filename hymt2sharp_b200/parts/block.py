@@ -3,7 +3,7 @@
 float32; the normed activations have the engine's compute type."""
 from __future__ import annotations
 
-from .base import PartSpec, build_part, register_part
+from .base import PartSpec, Prenormed, build_part, register_part
 
 
 class PreNormBlock:
@@ -37,14 +37,27 @@ class PreNormBlock:
         for p in self.parts():
             p.load(weights, device, dtype)
 
+    def first_norm(self):
+        """The norm that this block applies to the residual first, if the part behind it can take a norm's output in
+        two pieces (parts.base.Prenormed): the block before may then prepare it in its last product."""
+        return self.norm1 if getattr(self.mixer, "takes_prenormed", False) else None
+
     def forward(self, residual, ctx, slots) -> None:
-        x = self.norm1.forward(residual, ctx, ctx.dtype)
+        x = self.norm1.forward(residual, ctx, ctx.dtype)      # what the block before left behind, or the norm's own kernel
+        if isinstance(x, Prenormed) and not getattr(self.mixer, "takes_prenormed", False):
+            x = x.materialize(ctx)
         # what the feed-forward streams first, for a mixer whose last kernel can ask for it ahead of time
         ctx.weights_ahead = getattr(self.feed_forward, "first_weights", lambda: None)()
+        # the norm that comes next, for a mixer whose last product can prepare it
+        ctx.norm_ahead = self.norm2 if getattr(self.feed_forward, "takes_prenormed", False) else None
         self.mixer.forward(x, residual, ctx, slots[0])
-        ctx.weights_ahead = None
+        ctx.weights_ahead = ctx.norm_ahead = None
         x = self.norm2.forward(residual, ctx, ctx.dtype)
+        if isinstance(x, Prenormed) and not getattr(self.feed_forward, "takes_prenormed", False):
+            x = x.materialize(ctx)
+        ctx.norm_ahead = ctx.next_first_norm
         self.feed_forward.forward(x, residual, ctx)
+        ctx.norm_ahead = None
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -14,6 +14,7 @@ from .linear import Linear, compute_form
 
 class SwiGLU:
     graph_safe = True  # its forward only launches kernels on the current stream
+    takes_prenormed = True  # x may be a parts.base.Prenormed: the gate/up product applies the norm's row scale itself
 
     def __init__(self, hidden: int, intermediate: int, gate_proj: str, up_proj: str, down_proj: str):
         self.hidden, self.intermediate = int(hidden), int(intermediate)
@@ -34,9 +35,9 @@ class SwiGLU:
         """The weights that this part's first kernel streams."""
         return self.gate_up.weight if self.gate_up is not None else None
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
-        act = self.gate_up(x)
-        self.down(act, out=residual)
+    def forward(self, x, residual: torch.Tensor, ctx) -> None:
+        act = self.gate_up(x, ctx=ctx)
+        self.down.add_then_norm(act, residual, getattr(ctx, "norm_ahead", None), ctx)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -220,10 +220,10 @@ def test_no_device_means_a_loud_error(monkeypatch):
 
 
 def test_the_fast_kernels_are_what_a_bfloat16_step_of_full_size_heads_runs(model_dirs):
-    """With heads of 128 a bfloat16 decode step is, per layer: norm, the projection that also rotates and
-    appends to the cache, attention, the request for the next weights, output projection, norm, gate/up, down.
-    A silent fall to the general kernels would show as more launches (a rotation kernel, a split attention
-    with its merge)."""
+    """With heads of 128 a bfloat16 decode step is, per layer: the projection that also rotates and appends to the
+    cache, attention, the request for the next weights, output projection, gate/up, down; the norms are folded into
+    the products around them, all but the very first.  A silent fall to the general kernels would show as more
+    launches (a norm, a rotation kernel, a split attention with its merge)."""
     from hymt2sharp_b200.engine.engine import StepEntry
     from hymt2sharp_b200.kernels import ops
     eng = _engine(model_dirs, "H", "bfloat16")
@@ -232,7 +232,7 @@ def test_the_fast_kernels_are_what_a_bfloat16_step_of_full_size_heads_runs(model
     before = ops.launches
     eng.step([StepEntry(slot, [5], [0])])
     layers = eng.config.num_hidden_layers
-    assert ops.launches - before == 1 + 8 * layers + 2   # embedding; the layers; final norm and head
+    assert ops.launches - before == 1 + 1 + 6 * layers + 2   # embedding; the first norm; the layers; final norm and head
     q = torch.empty(1, 4 * 128, dtype=torch.bfloat16, device=DEV)
     assert ops.gemm_tc_rope_kv_supported(torch.empty(1, 256, dtype=torch.bfloat16, device=DEV),
                                          eng.model.blocks[0].mixer.qkv.weight, 4, 2, 128, q.dtype, 128)

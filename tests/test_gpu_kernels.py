@@ -467,6 +467,61 @@ def test_gemm_tcgen05_at_full_size_shapes(T, N, K, epilogue, cdt):
     assert status.tolist() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("T, H, K_in, F, gain_dtype", [
+    (8, 2048, 2048, 6144, torch.bfloat16),      # decode: the cluster's fold leaves the norm's input; gate/up through the workspace takes it
+    (1, 256, 512, 392, torch.float32),          # one token, few tiles, 32-bit gain
+    (40, 1000, 520, 520, torch.bfloat16),       # a last tile of features that is not full
+    (300, 256, 512, 392, torch.bfloat16),       # a prompt: tiles of 128 x 128 leave it, the persistent kernel takes it
+    (2048, 2048, 6144, 6144, torch.bfloat16),   # the full-size prompt
+    (4500, 2048, 2048, 1024, torch.bfloat16)])  # many tokens: the persistent kernel leaves it too
+def test_gemm_tcgen05_with_a_norm_folded_in(T, H, K_in, F, gain_dtype):
+    """residual += a @ w^T leaves bf16(residual * gain) and the rows' sums of squares behind; the next product (SwiGLU or
+    store) applies the row scale 1/rms to its sums.  Against the same products with the norm as a kernel of its own."""
+    ops = _ops()
+    torch.manual_seed(T + H)
+    bf = torch.bfloat16
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    a = torch.randn(T, K_in, device=DEV).to(bf)
+    w = (torch.randn(H, K_in, device=DEV) / math.sqrt(K_in)).to(bf)
+    wgu = (torch.randn(2 * F, H, device=DEV) / math.sqrt(H)).to(bf)
+    gain = (1 + 0.1 * torch.randn(H, device=DEV)).to(gain_dtype)
+    res0 = torch.randn(T, H, device=DEV)
+    eps = 1e-5
+    # the norm as a kernel of its own
+    res_ref = res0.clone()
+    ops.gemm_tc(res_ref, a, w, ops.EPILOGUE_ACCUMULATE, status)
+    x_ref = torch.empty(T, H, dtype=bf, device=DEV)
+    ops.rmsnorm(x_ref, res_ref, gain, eps)
+    act_ref = torch.empty(T, F, dtype=bf, device=DEV)
+    ops.gemm_tc(act_ref, x_ref, wgu, ops.EPILOGUE_SWIGLU, status)
+    plain_ref = torch.empty(T, F, device=DEV)
+    ops.gemm_tc(plain_ref, x_ref, wgu[:F], ops.EPILOGUE_STORE, status)
+    # folded
+    tiles = ops.gemm_tc_norm_tiles(T, H, K_in, ops.EPILOGUE_ACCUMULATE)
+    assert tiles > 0
+    res = res0.clone()
+    normed = torch.full((T, H), 7.0, dtype=bf, device=DEV)
+    ss = torch.full((T, tiles), -1.0, device=DEV)
+    ops.gemm_tc(res, a, w, ops.EPILOGUE_ACCUMULATE, status, norm_after=(normed, gain, ss))
+    assert torch.equal(res, res_ref)                                             # the residual itself is what it was
+    assert torch.equal(normed, (res * gain.float()).to(bf))                      # its rows times the gain, rounded once
+    assert torch.allclose(ss.sum(1).double(), res.double().pow(2).sum(1), rtol=1e-5)
+    act = torch.empty(T, F, dtype=bf, device=DEV)
+    ops.gemm_tc(act, normed, wgu, ops.EPILOGUE_SWIGLU, status, row_scale=(ss, H, eps))
+    plain = torch.empty(T, F, device=DEV)
+    ops.gemm_tc(plain, normed, wgu[:F], ops.EPILOGUE_STORE, status, row_scale=(ss, H, eps))
+    for got, ref, what in ((act, act_ref, "swiglu"), (plain, plain_ref, "store")):
+        diff = (got.float() - ref.float()).abs()
+        # the two ways round the activations at different places (x * gain against x * r * gain) and, for SwiGLU, round two
+        # factors of the result: independent bfloat16 roundings (2^-9 relative each) of every input and output element
+        rms = float(diff.pow(2).mean().sqrt()) / float(ref.float().pow(2).mean().sqrt())
+        assert float(diff.max()) <= 3e-2 * float(ref.float().abs().max()), what
+        assert rms <= 8e-3, (what, rms)
+    assert status.tolist() == [0, 0, 0, 0]
+    # what cannot leave a norm's input says so: a product that does not add, and one whose K is folded through the workspace
+    assert ops.gemm_tc_norm_tiles(8, 6144, 2048, ops.EPILOGUE_SWIGLU) == 0
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_take():
     ops = _ops()
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
