@@ -267,7 +267,7 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
 }
 
 template <int BN, bool SWAPPED, int EPI, typename TC>
-__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), 1)
+__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), SWAPPED ? 1 : 2)   // tokens as rows: two CTAs share an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
     constexpr int NUM_ACC = (SWAPPED && EPI == EPI_SWIGLU) ? 2 : 1;   // accumulators = A tiles per stage
     constexpr bool SPLIT_B = !SWAPPED && EPI == EPI_SWIGLU;           // B tile = gate rows, then up rows
@@ -424,6 +424,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const bool scaled = SWAPPED && EPI != EPI_ACCUMULATE && p.norm.ss_in != nullptr;
         float ss_acc = 0.f;   // normal orientation, producer of a norm: this thread's token row, summed over the tile's features
+
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103, p.wait_limit) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         TC* C = (TC*)p.C;
@@ -467,6 +468,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[j] + g[j]);
                     else *dst = from_float<TC>(silu_mul(g[j] * r, u[j] * r));
                 }
+            } else if constexpr (!SWAPPED && EPI == EPI_ACCUMULATE && sizeof(TC) == 4) {
+                // Adding into the float32 residual, tokens as rows.  A thread holds 32 columns of ITS token's row; touching C
+                // that way, every load and store of a warp would hit 32 different 128-byte lines (32 rows, 8 KB apart), and
+                // the memory pipe, one line a cycle, made this epilogue as long as the tile's MMAs.  So the warp turns its
+                // 32 x 32 piece around through shared memory (the stage ring is free: every MMA of the tile is complete):
+                // then a lane owns a COLUMN, and a warp's access is one whole line of one token's row.
+                static_assert(CH == 32, "a warp turns 32 x 32 pieces around");
+                float* piece = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw))) + quarter * (32 * 33);
+#pragma unroll
+                for (int j = 0; j < 32; j++) piece[lane * 33 + j] = g[j];
+                __syncwarp();
+                const int n = b_row0 + c + lane;               // this lane's output feature
+                const bool n_ok = n < p.N;
+                const float gn = (p.norm.out && n_ok) ? norm_gain_at(p.norm, n) : 0.f;
+                const int m0 = a_row0 + quarter * 32;
+#pragma unroll
+                for (int r0 = 0; r0 < 32; r0 += 16) {          // sixteen tokens at a time: their loads are in flight together
+                    float oldv[16];
+#pragma unroll
+                    for (int r = 0; r < 16; r++) oldv[r] = (n_ok && m0 + r0 + r < p.T) ? C[(size_t)(m0 + r0 + r) * p.ldc + n] : 0.f;
+#pragma unroll
+                    for (int r = 0; r < 16; r++) {
+                        float v = 0.f;
+                        if (n_ok && m0 + r0 + r < p.T) {
+                            v = oldv[r] + piece[(r0 + r) * 33 + lane];
+                            C[(size_t)(m0 + r0 + r) * p.ldc + n] = v;
+                            if (p.norm.out) p.norm.out[(size_t)(m0 + r0 + r) * p.N + n] = __float2bfloat16_rn(v * gn);
+                        }
+                        if (p.norm.out) piece[(r0 + r) * 33 + lane] = v;   // back, for the row's sum of squares
+                    }
+                }
+                __syncwarp();
+                if (p.norm.out) {   // the thread is its token's row again
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float v = piece[lane * 33 + j];
+                        ss_acc = fmaf(v, v, ss_acc);
+                    }
+                }
+                __syncwarp();
             } else {
                 const int m = a_row0 + row;                    // token
                 if (m >= p.T) return;
