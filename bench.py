@@ -4,7 +4,7 @@ weights, a prompt-sized prefill, the decode step's fraction of the measured HBM 
 the dominant kernels alone with their own roofline fractions.  Prints ONE JSON line on standard output.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config 1p8b|4b|7b] [--batch B] [--prefill N] [--decode N] [--dtype bf16|fp32] [--reps R]
+                    [--config 1p8b|4b|7b|tinyA|tinyB] [--batch B] [--prefill N] [--decode N] [--dtype bf16|fp32] [--reps R]
                     [--layers L] [--verify-split] [--profile] [--no-points] [--no-kernels] [--no-graph]
 
 The default is the Hy-MT2 1.8B layer sizes in bfloat16: a batch of 8 sequences that each hold a 2,048-token
@@ -50,6 +50,17 @@ CONFIGS = {
                           intermediate_size=14336, vocab_size=128167, tie_word_embeddings=False),
                workload=dict(batch=64, prompt=(16, 2048), steps=512)),
 }
+# the two tiny configurations of the tests' workloads (head sizes 16 and 32: every kernel is the general CUDA-core one)
+CONFIGS["tinyA"] = dict(name="hunyuan-dense-tiny-A", seed=0, layers=2,
+                        sizes=dict(hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=160,
+                                   vocab_size=256, rope_theta=10000.0, rope_alpha=1.0, rms_norm_eps=1e-5, use_qk_norm=True,
+                                   tie_word_embeddings=True, max_position_embeddings=8192),
+                        workload=dict(batch=3, lengths=[5, 9, 1], steps=8))
+CONFIGS["tinyB"] = dict(name="hunyuan-dense-tiny-B", seed=1, layers=3,
+                        sizes=dict(hidden_size=96, num_attention_heads=6, num_key_value_heads=1, head_dim=32, intermediate_size=224,
+                                   vocab_size=509, rope_theta=1e6, rope_alpha=1000.0, rms_norm_eps=1e-6, use_qk_norm=False,
+                                   tie_word_embeddings=False, max_position_embeddings=8192),
+                        workload=dict(batch=4, lengths=[17, 3, 11, 6], steps=12))
 CONTEXT = 8192
 PREFILL_GROUP_TOKENS = 16384   # prompts go in by groups of at most this many tokens: bounded activation memory
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
@@ -272,11 +283,14 @@ def main() -> int:
     verify = run_verify(args.config, layers) if args.verify_split else None
 
     rng = np.random.default_rng(1234)
-    lo, hi = work["prompt"]
-    uniform = lo == hi
+    fixed = work.get("lengths")
+    lo, hi = work["prompt"] if fixed is None else (min(fixed), max(fixed))
+    uniform = lo == hi and fixed is None
     vocab = spec["sizes"]["vocab_size"]
 
     def prompt_lengths(n):
+        if fixed is not None:
+            return [fixed[i % len(fixed)] for i in range(n)]
         return [lo] * n if uniform else [int(x) for x in rng.integers(lo, hi + 1, n)]
 
     def prompts_of(lengths):
@@ -395,14 +409,15 @@ def main() -> int:
             print(ops.profile_line(phase, t), file=sys.stderr)
 
     kernels = None
-    if not args.no_kernels and args.dtype == "bf16":
+    if not args.no_kernels and args.dtype == "bf16" and not args.config.startswith("tiny"):
         del engine, out
         torch.cuda.empty_cache()
         mean_ctx = int(mean_tokens / batch)
         kernels = kernel_fractions(cfg, batch, args.prefill, mean_ctx, pk)
         kernels["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk_source}
 
-    lengths_text = f"{batch} x {lo}" if uniform else f"{batch} lengths uniform in [{lo},{hi}], seed 1234"
+    lengths_text = f"{batch} x {lo}" if uniform else f"lengths {main_lengths}" if fixed is not None else \
+        f"{batch} lengths uniform in [{lo},{hi}], seed 1234"
     line = {
         "metric": ("decode tok/s at batch 8 (1.8B bf16, 2,048-token prompts); prefill tok/s at 2,048 tokens"
                    if (args.config, args.dtype, batch, args.prefill) == ("1p8b", "bf16", 8, 2048) else
@@ -419,7 +434,8 @@ def main() -> int:
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
                    "vocab": cfg.vocab_size, "rope_alpha": cfg.rope_alpha, "qk_norm": cfg.use_qk_norm,
                    "tied": cfg.tie_word_embeddings, "sampling": "greedy on the GPU",
-                   "l2": "inputs larger than L2: every step streams all weights (GBs) once"},
+                   "l2": "inputs larger than L2: every step streams all weights (GBs) once" if step_bytes > 2 * 126e6 else
+                         "model smaller than L2, nothing flushed: a tiny configuration times launches, not memory"},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
         "points": points,
     }
