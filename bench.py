@@ -14,8 +14,8 @@ families of sizes with their own workloads (16 prompts of 64 to 4,096 tokens and
 with CUDA events around K steps of the captured decode graph; `e2e` is the same batch through Engine.generate
 (host token ids in and out every step).  `--verify-split` adds, under `verify`, the comparison of logits between
 the ways of cutting the work, between the precisions and against the plain implementation of the tests
-(src/HyMT2Sharp.Benchmark/Program.cs:124-177); `--profile` adds per-kernel times of an uncaptured prefill and
-decode (:243-261).  The shape of the program follows src/HyMT2Sharp.Benchmark/Program.cs:179-241 (warm-up, timed
+(src/HyMT2Sharp.Benchmark/Program.cs:124-177); `--profile` adds per-kernel times of a prefill and of
+decode steps, kernel after kernel (:243-261).  The shape of the program follows src/HyMT2Sharp.Benchmark/Program.cs:179-241 (warm-up, timed
 prefill repetitions reported one by one, timed decode including sampling).
 """
 from __future__ import annotations

@@ -12,7 +12,7 @@ so prompts are token ids ("12,7,99" or "12 7 99") and replies are printed as ids
   --threads N        CPU workers of the reference; accepted, has no meaning on the GPU
   --backend NAME     auto or cuda (cpu, metal and vulkan do not exist here)
   --profile          per-kernel times of the prefill and of the decode steps (the Benchmark program's switch,
-                     src/HyMT2Sharp.Benchmark/Program.cs:243-261); steps then run uncaptured
+                     src/HyMT2Sharp.Benchmark/Program.cs:243-261); kernels then run one after the other
 and beyond the reference: --dtype, --temperature, --top-k, --top-p, --min-p,
 --repeat-penalty, --penalty-window, --seed, --stop-ids, --max-context, --max-batch,
 --random CONFIG.json --weights-seed N --sigma S (write random weights into --model first).

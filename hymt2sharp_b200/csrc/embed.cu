@@ -67,3 +67,18 @@ HYMT2_API int hymt2_l2_prefetch(const void* ptr, long bytes, cudaStream_t stream
     l2_prefetch_kernel<<<blocks, 32, 0, stream>>>((const uint8_t*)ptr, bytes);
     return hymt2_check_launch("l2_prefetch");
 }
+
+// The device's clock (nanoseconds of %globaltimer) into out[0]: launched between the kernels of a captured step while
+// kernels are being timed, since a graph can hold this where the host cannot look.  Launched without programmatic
+// overlap, so a stamp is taken when everything in front of it on the stream is complete.
+__global__ void stamp_kernel(unsigned long long* out) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    *out = t;
+}
+
+HYMT2_API int hymt2_stamp(unsigned long long* out, cudaStream_t stream) {
+    HYMT2_REQUIRE(out != nullptr, "stamp: no place to write");
+    stamp_kernel<<<1, 1, 0, stream>>>(out);
+    return hymt2_check_launch("stamp");
+}

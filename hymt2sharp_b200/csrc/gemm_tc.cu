@@ -266,6 +266,10 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
     }
 }
 
+// sincosf, not inlined: its slow path for large arguments is long, and an epilogue that rotates several columns would
+// carry a copy for each
+__device__ __noinline__ void sincos_once(float angle, float* sn, float* cs) { sincosf(angle, sn, cs); }
+
 template <int BN, bool SWAPPED, int EPI, typename TC>
 __global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), SWAPPED ? 1 : 2)   // tokens as rows: two CTAs share an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
@@ -295,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (EPI != EPI_ROPE_KV) pdl_launch_dependents();
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
-    __shared__ float scale_s[SWAPPED ? BN : 1], norm_red_s[4];
+    __shared__ float scale_s[SWAPPED ? BN : 1], norm_red_s[16];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
@@ -424,10 +428,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const bool scaled = SWAPPED && EPI != EPI_ACCUMULATE && p.norm.ss_in != nullptr;
         float ss_acc = 0.f;   // normal orientation, producer of a norm: this thread's token row, summed over the tile's features
+        TC* C = (TC*)p.C;
+        // The cluster's fold: this CTA's share of the token columns that exist in the tile.  Where the fold adds into C,
+        // the old values of the first batch of columns are asked for now, under the MMAs.
+        constexpr int MAX_RANKS = 8;                           // a portable cluster
+        constexpr int FOLD_COLS = BN <= 16 ? 2 : 4;            // columns whose partials are in flight together
+        int c_begin = 0, c_end = 0;
+        float old_first[FOLD_COLS] = {};
+        if (SWAPPED && p.cluster && p.splits > 1) {
+            const int cols = min(BN, p.T - b_row0);
+            const int share = (cols + p.splits - 1) / p.splits;
+            c_begin = (int)blockIdx.z * share;
+            c_end = min(cols, c_begin + share);
+            if (EPI == EPI_ACCUMULATE && a_row0 + row < p.N) {
+#pragma unroll
+                for (int q = 0; q < FOLD_COLS; q++)
+                    if (c_begin + q < c_end) old_first[q] = to_float(C[(size_t)(b_row0 + c_begin + q) * p.ldc + a_row0 + row]);
+            }
+        }
 
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103, p.wait_limit) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        TC* C = (TC*)p.C;
         // CH columns of the accumulators from column c on (c counts gate columns, then up columns): the sum over the
         // issuers that had a k block, in issuer order (issuer 1 has one as soon as there are two blocks and two stages)
         const int used = min(ISSUERS, min(my_blocks, stages));
@@ -607,91 +628,142 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             cluster_sync_all();
             {
-                constexpr int MAX_RANKS = 8;                       // a portable cluster
-                const int cols = min(BN, p.T - b_row0);            // token columns that exist in this tile
-                const int share = (cols + p.splits - 1) / p.splits;
-                const int c_begin = (int)blockIdx.z * share, c_end = min(cols, c_begin + share);
+                // FOLD_COLS columns at a time: their partials from every rank (and the residual values they are added
+                // to) are asked for together, so that a column costs one trip through distributed shared memory and
+                // one through global memory per batch, not per column
                 const int n = a_row0 + row;                        // output feature
-                for (int c = c_begin; c < c_end; c++) {
-                    float pg[MAX_RANKS], pu[MAX_RANKS];
+                for (int c0 = c_begin; c0 < c_end; c0 += FOLD_COLS) {
+                    float old[FOLD_COLS];
+                    if (EPI == EPI_ACCUMULATE) {
 #pragma unroll
-                    for (int r = 0; r < MAX_RANKS; r++) {          // all loads first: they do not wait for each other
-                        const bool in = r < p.splits;
-                        pg[r] = in ? ld_cluster_f32(tiles + (c * TILE_M + row) * 4, r) : 0.f;
-                        pu[r] = (in && EPI == EPI_SWIGLU) ? ld_cluster_f32(tiles + ((BN + c) * TILE_M + row) * 4, r) : 0.f;
+                        for (int q = 0; q < FOLD_COLS; q++) {
+                            if (c0 == c_begin) old[q] = old_first[q];
+                            else old[q] = (c0 + q < c_end && n < p.N) ? to_float(C[(size_t)(b_row0 + c0 + q) * p.ldc + n]) : 0.f;
+                        }
                     }
-                    float g = 0.f, u = 0.f;
+                    float g[FOLD_COLS], u[FOLD_COLS];
+                    {
+                        float pg[FOLD_COLS][MAX_RANKS], pu[FOLD_COLS][MAX_RANKS];
 #pragma unroll
-                    for (int r = 0; r < MAX_RANKS; r++) { g += pg[r]; u += pu[r]; }
-                    if (scaled) { g *= scale_s[c]; u *= scale_s[c]; }
+                        for (int q = 0; q < FOLD_COLS; q++)
+#pragma unroll
+                            for (int r = 0; r < MAX_RANKS; r++) {      // all loads first: they do not wait for each other
+                                const bool in = r < p.splits && c0 + q < c_end;
+                                pg[q][r] = in ? ld_cluster_f32(tiles + ((c0 + q) * TILE_M + row) * 4, r) : 0.f;
+                                pu[q][r] = (in && EPI == EPI_SWIGLU) ? ld_cluster_f32(tiles + ((BN + c0 + q) * TILE_M + row) * 4, r) : 0.f;
+                            }
+#pragma unroll
+                        for (int q = 0; q < FOLD_COLS; q++) {
+                            g[q] = 0.f; u[q] = 0.f;
+#pragma unroll
+                            for (int r = 0; r < MAX_RANKS; r++) { g[q] += pg[q][r]; u[q] += pu[q][r]; }   // rank order
+                            if (scaled && c0 + q < c_end) { g[q] *= scale_s[c0 + q]; u[q] *= scale_s[c0 + q]; }
+                        }
+                    }
                     if constexpr (EPI == EPI_ROPE_KV) {
-                        // this tile is head blockIdx.x of token b_row0 + c, this thread its value d = row
+                        // this tile is head blockIdx.x of the tokens b_row0 + c, this thread its value d = row
                         const RopeEpilogue& rp = p.rope;
-                        const int t = b_row0 + c, head = blockIdx.x, d = row;
-                        const float x = __bfloat162float(__float2bfloat16_rn(g));   // what the projection would have stored
-                        const int pos = rp.token_pos[t], slot = rp.slot_ids[rp.token_seq[t]];
+                        const int head = blockIdx.x, d = row;
                         const bool is_q = head < rp.nh, is_k = !is_q && head < rp.nh + rp.nkv;
-                        size_t cache_at = 0;
-                        const bool write_kv = !is_q && rp.write_kv && slot >= 0;
-                        if (write_kv) {
-                            const int block = rp.block_table[(size_t)slot * rp.table_stride + pos / rp.block_tokens];
-                            const int kvh = is_k ? head - rp.nh : head - rp.nh - rp.nkv;
-                            cache_at = (((size_t)block * rp.nkv + kvh) * rp.block_tokens + (pos % rp.block_tokens)) * TILE_M + d;
+                        const uint32_t ex = tiles + ACC_COLS * TILE_M * 4;   // per column: 128 values to trade partners, then 4 sums
+                        constexpr uint32_t EX_BYTES = (TILE_M + 4) * 4;
+                        float x[FOLD_COLS], y[FOLD_COLS];
+                        int pos[FOLD_COLS];
+                        size_t cache_at[FOLD_COLS];
+                        bool write_kv[FOLD_COLS];
+#pragma unroll
+                        for (int q = 0; q < FOLD_COLS; q++) {
+                            const bool in = c0 + q < c_end;
+                            const int t = b_row0 + c0 + q;
+                            x[q] = __bfloat162float(__float2bfloat16_rn(g[q]));   // what the projection would have stored
+                            pos[q] = in ? rp.token_pos[t] : 0;
+                            const int slot = in ? rp.slot_ids[rp.token_seq[t]] : -1;
+                            write_kv[q] = in && !is_q && rp.write_kv && slot >= 0;
+                            cache_at[q] = 0;
+                            if (write_kv[q]) {
+                                const int block = rp.block_table[(size_t)slot * rp.table_stride + pos[q] / rp.block_tokens];
+                                const int kvh = is_k ? head - rp.nh : head - rp.nh - rp.nkv;
+                                cache_at[q] = (((size_t)block * rp.nkv + kvh) * rp.block_tokens + (pos[q] % rp.block_tokens)) * TILE_M + d;
+                            }
                         }
                         if (!is_q && !is_k) {   // a value head: as it is (the whole CTA is this head: no barrier is missed)
-                            if (write_kv) rp.v_cache[cache_at] = __float2bfloat16_rn(x);
+#pragma unroll
+                            for (int q = 0; q < FOLD_COLS; q++)
+                                if (write_kv[q]) rp.v_cache[cache_at[q]] = __float2bfloat16_rn(x[q]);
                         } else {
-                            const uint32_t ex = tiles + ACC_COLS * TILE_M * 4;   // 128 values to trade partners, then 4 sums
-                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + d * 4), "f"(x) : "memory");
+#pragma unroll
+                            for (int q = 0; q < FOLD_COLS; q++)
+                                asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + q * EX_BYTES + d * 4), "f"(x[q]) : "memory");
                             asm volatile("bar.sync 1, 128;" ::: "memory");
                             const int half = rp.rope_dim / 2;
-                            float y = x;
-                            if (d < rp.rope_dim) {
-                                const bool low = d < half;
-                                float other, sn, cs;
-                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(ex + (low ? d + half : d - half) * 4) : "memory");
-                                sincosf((float)pos * rp.inv_freq[low ? d : d - half], &sn, &cs);
-                                y = low ? x * cs - other * sn : other * sn + x * cs;
-                            }
                             const void* gain = is_q ? rp.q_gain : rp.k_gain;
-                            if (gain) {
-                                const float ss = warp_sum(y * y);
-                                if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + (TILE_M + quarter) * 4), "f"(ss) : "memory");
-                                asm volatile("bar.sync 1, 128;" ::: "memory");
-                                float s0, s1, s2, s3;
-                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s0) : "r"(ex + (TILE_M + 0) * 4) : "memory");
-                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s1) : "r"(ex + (TILE_M + 1) * 4) : "memory");
-                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s2) : "r"(ex + (TILE_M + 2) * 4) : "memory");
-                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s3) : "r"(ex + (TILE_M + 3) * 4) : "memory");
-                                const float scale = 1.0f / sqrtf((((s0 + s1) + s2) + s3) / (float)TILE_M + rp.eps);
-                                const float gv = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[d]) : ((const float*)gain)[d];
-                                y = y * scale * gv;
+#pragma unroll
+                            for (int q = 0; q < FOLD_COLS; q++) {
+                                y[q] = x[q];
+                                if (d < rp.rope_dim && c0 + q < c_end) {
+                                    const bool low = d < half;
+                                    float other, sn, cs;
+                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(ex + q * EX_BYTES + (low ? d + half : d - half) * 4) : "memory");
+                                    sincos_once((float)pos[q] * rp.inv_freq[low ? d : d - half], &sn, &cs);
+                                    y[q] = low ? x[q] * cs - other * sn : other * sn + x[q] * cs;
+                                }
+                                if (gain) {
+                                    const float ss = warp_sum(y[q] * y[q]);
+                                    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + q * EX_BYTES + (TILE_M + quarter) * 4), "f"(ss) : "memory");
+                                }
                             }
-                            if (is_q) rp.q_out[((size_t)t * rp.nh + head) * TILE_M + d] = __float2bfloat16_rn(y);
-                            else if (write_kv) rp.k_cache[cache_at] = __float2bfloat16_rn(y);
-                            asm volatile("bar.sync 1, 128;" ::: "memory");   // the next column trades through the same words
+                            if (gain) {
+                                asm volatile("bar.sync 1, 128;" ::: "memory");
+                                const float gv = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[d]) : ((const float*)gain)[d];
+#pragma unroll
+                                for (int q = 0; q < FOLD_COLS; q++) {
+                                    float s0, s1, s2, s3;
+                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s0) : "r"(ex + q * EX_BYTES + (TILE_M + 0) * 4) : "memory");
+                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s1) : "r"(ex + q * EX_BYTES + (TILE_M + 1) * 4) : "memory");
+                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s2) : "r"(ex + q * EX_BYTES + (TILE_M + 2) * 4) : "memory");
+                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s3) : "r"(ex + q * EX_BYTES + (TILE_M + 3) * 4) : "memory");
+                                    const float scale = 1.0f / sqrtf((((s0 + s1) + s2) + s3) / (float)TILE_M + rp.eps);
+                                    y[q] = y[q] * scale * gv;
+                                }
+                            }
+#pragma unroll
+                            for (int q = 0; q < FOLD_COLS; q++) {
+                                if (c0 + q >= c_end) continue;
+                                if (is_q) rp.q_out[((size_t)(b_row0 + c0 + q) * rp.nh + head) * TILE_M + d] = __float2bfloat16_rn(y[q]);
+                                else if (write_kv[q]) rp.k_cache[cache_at[q]] = __float2bfloat16_rn(y[q]);
+                            }
+                            asm volatile("bar.sync 1, 128;" ::: "memory");   // the next batch trades through the same words
                         }
                     } else if (EPI == EPI_ACCUMULATE && p.norm.out) {
-                        // the residual's new value, and for the norm that follows: bf16(value * gain) and the sum of squares
-                        // of this token over the tile's 128 features
-                        float v = 0.f;
-                        if (n < p.N) {
-                            TC* dst = C + (size_t)(b_row0 + c) * p.ldc + n;
-                            v = to_float(*dst) + g;
-                            *dst = from_float<TC>(v);
-                            p.norm.out[(size_t)(b_row0 + c) * p.N + n] = __float2bfloat16_rn(v * norm_gain_at(p.norm, n));
+                        // the residual's new values, and for the norm that follows: bf16(value * gain) and the sums of squares
+                        // of these tokens over the tile's 128 features
+                        const float gn = n < p.N ? norm_gain_at(p.norm, n) : 0.f;
+#pragma unroll
+                        for (int q = 0; q < FOLD_COLS; q++) {
+                            float v = 0.f;
+                            if (n < p.N && c0 + q < c_end) {
+                                v = old[q] + g[q];
+                                C[(size_t)(b_row0 + c0 + q) * p.ldc + n] = from_float<TC>(v);
+                                p.norm.out[(size_t)(b_row0 + c0 + q) * p.N + n] = __float2bfloat16_rn(v * gn);
+                            }
+                            const float sq = warp_sum(v * v);
+                            if (lane == 0) norm_red_s[q * 4 + quarter] = sq;
                         }
-                        const float sq = warp_sum(v * v);
-                        if (lane == 0) norm_red_s[quarter] = sq;
                         asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (threadIdx.x == 64)
-                            p.norm.ss_out[(size_t)(b_row0 + c) * p.norm.ss_out_tiles + blockIdx.x] = (norm_red_s[0] + norm_red_s[1]) + (norm_red_s[2] + norm_red_s[3]);
+                        const int tl = threadIdx.x - 64;
+                        if (tl < FOLD_COLS && c0 + tl < c_end)
+                            p.norm.ss_out[(size_t)(b_row0 + c0 + tl) * p.norm.ss_out_tiles + blockIdx.x] =
+                                (norm_red_s[tl * 4] + norm_red_s[tl * 4 + 1]) + (norm_red_s[tl * 4 + 2] + norm_red_s[tl * 4 + 3]);
                         asm volatile("bar.sync 1, 128;" ::: "memory");
                     } else if (n < p.N) {
-                        TC* dst = C + (size_t)(b_row0 + c) * p.ldc + n;
-                        if (EPI == EPI_STORE) *dst = from_float<TC>(g);
-                        else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(to_float(*dst) + g);
-                        else *dst = from_float<TC>(silu_mul(g, u));
+#pragma unroll
+                        for (int q = 0; q < FOLD_COLS; q++) {
+                            if (c0 + q >= c_end) continue;
+                            TC* dst = C + (size_t)(b_row0 + c0 + q) * p.ldc + n;
+                            if (EPI == EPI_STORE) *dst = from_float<TC>(g[q]);
+                            else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[q] + g[q]);
+                            else *dst = from_float<TC>(silu_mul(g[q], u[q]));
+                        }
                     }
                 }
             }
@@ -726,7 +798,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float g[CH], u[CH];
 #pragma unroll
                     for (int j = 0; j < CH; j++) { g[j] = 0.f; u[j] = 0.f; }
-                    constexpr int SB = CH == 16 ? 4 : 1;       // splits whose loads are in flight together
+                    constexpr int SB = CH == 16 ? 4 : 2;       // splits whose loads are in flight together
                     for (int s0 = 0; s0 < p.splits; s0 += SB) {  // split order: the sum is the same every time
                         float pg[SB][CH], pu[SB][CH];
 #pragma unroll
@@ -1059,7 +1131,14 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
             while (want > 1 && num_k_blocks / want < 2) want--;
             pl.splits = want;
         }
-        pl.tiles = tiles;
+        // 128 token columns of split partials no longer fold inside a cluster (the ring of two CTAs on an SM gets too
+        // shallow) and fold slowly through memory; two tiles of 64 columns do fold as clusters, and the second reading of
+        // a weight tile, by the CTA beside the first, comes from L2
+        if (T > 64 && pl.splits > 1 && num_acc == 1) {
+            pl.bn = 64;
+            pl.grid.y = (T + 63) / 64;
+        }
+        pl.tiles = tiles * (int)pl.grid.y;
     } else {
         // The persistent kernel (one CTA per SM, wide tiles, epilogue hidden behind the next tile) wherever the output
         // is written once; where it is added to the float32 residual (twice the epilogue traffic), only when there is a
@@ -1295,7 +1374,7 @@ HYMT2_API int hymt2_gemm_tc_rope_kv_supported(int T, int N, int K, int rope_dim)
     if (T <= 0 || N <= 0 || N % TILE_M || K <= 0 || K % 8) return 0;
     Plan pl;
     make_plan(T, N, K, EPI_ROPE_KV, sm_count_of_current_device(), &pl);
-    if (pl.swapped) return (T <= 64 && pl.cluster && pl.bn <= 64) ? 1 : 0;
+    if (pl.swapped) return (pl.cluster && pl.bn <= 64) ? 1 : 0;
     return (rope_dim == 0 || rope_dim == TILE_M) ? 1 : 0;   // tokens as rows: a thread rotates its token's whole head
 }
 

@@ -72,6 +72,7 @@ class DecodeSession:
         self.rows = len(slots)
         self.live = [live_rows is None or r in live_rows for r in range(self.rows)]
         self.use_graph = use_graph and engine.model.graph_safe
+        self._timed_graph, self._timed_events, self._timed_layout = None, [], None
         B = self.rows
         lens = [self.cache.length(s) if alive else 0 for s, alive in zip(slots, self.live)]
         dev_slots = [s if alive else -1 for s, alive in zip(slots, self.live)]
@@ -164,6 +165,8 @@ class DecodeSession:
                 self._reserve()
             if not self.use_graph:
                 self._launch()
+            elif ops.profile_active():
+                self._step_profiled()
             elif self.buf.graph is None or self.buf.graph_layout != self.cache.layout_version:
                 self._capture()
             else:
@@ -212,7 +215,23 @@ class DecodeSession:
         self.buf.copied[ticket].synchronize()
         return self.buf.host_tokens[ticket].tolist()
 
+    def _step_profiled(self) -> None:
+        """The step while kernels are being timed: a graph of this session's own, captured with a clock stamp behind every
+        kernel, replayed and read.  The graph that unprofiled steps share is left alone."""
+        if self._timed_graph is None or self._timed_layout != self.cache.layout_version:
+            self._timed_graph, self._timed_events = self._capture_graph(timed=True)
+            self._timed_layout = self.cache.layout_version
+        self._timed_graph.replay()
+        ops.launches += self.buf.kernels_per_step
+        ops.book_captured(self._timed_events)
+
     def _capture(self) -> None:
+        b = self.buf
+        b.graph, _ = self._capture_graph(timed=False)
+        b.graph_layout = self.cache.layout_version
+        b.graph.replay()
+
+    def _capture_graph(self, timed: bool):
         # one eager step first (it also sets up what kernels set up at their first launch), then
         # the capture, which runs nothing: the state that the eager step changed is put back
         b = self.buf
@@ -220,15 +239,19 @@ class DecodeSession:
         rng = self.sampler.snapshot()
         stream = torch.cuda.Stream(device=self.engine.device)
         stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
+        with torch.cuda.stream(stream), ops.profile_suspended():
             self._launch()
         torch.cuda.current_stream().wait_stream(stream)
         b.meta.copy_(saved)
         self.sampler.restore(rng)
         before = ops.launches
-        b.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(b.graph, stream=stream):
-            self._launch()
+        graph, events = torch.cuda.CUDAGraph(), []
+        with torch.cuda.graph(graph, stream=stream):
+            if timed:
+                ops.capture_begin(self.engine.device)
+            try:
+                self._launch()
+            finally:
+                events = ops.capture_end() if timed else []
         b.kernels_per_step = ops.launches - before
-        b.graph_layout = self.cache.layout_version
-        b.graph.replay()
+        return graph, events

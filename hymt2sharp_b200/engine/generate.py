@@ -287,8 +287,9 @@ def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_tok
     all requests or a list with one per request; the default is greedy.  Returns the kept
     tokens and the finish reason of every request, in the order of `prompts`.  `profile`: every
     kernel is timed by a pair of CUDA events and booked by name in stats.profile (the counterpart of
-    HunyuanDenseModel.ProfileEnabled, src/HyMT2Sharp/HunyuanDenseModel.cs:48-78); steps then run
-    uncaptured and kernel after kernel, so the total is slower than an unprofiled run."""
+    HunyuanDenseModel.ProfileEnabled, src/HyMT2Sharp/HunyuanDenseModel.cs:48-78); kernels then run
+    one after the other and the host waits for every decode step (whose graph holds the events), so the
+    total is slower than an unprofiled run."""
     prompts = [list(map(int, p)) for p in prompts]
     if sampling is None:
         sampling = GREEDY
@@ -310,8 +311,6 @@ def generate(engine, prompts, max_new_tokens: int = 256, sampling=None, stop_tok
     profiler = None
     if profile:
         from ..kernels import ops as profiler
-        if stepper_factory is None:
-            factory = lambda *a: EngineStepper(*a, use_graph=False)
     stats = GenerationStats()
     results = [None] * len(prompts)
     for ids in batches:

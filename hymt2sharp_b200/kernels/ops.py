@@ -46,27 +46,98 @@ launches = 0  # kernels of this library launched (or captured into a graph) so f
 # stream is followed by a CUDA event, and the time between two events is booked under the launch's name, or under
 # `tag` where a caller set one (a Linear names the product it is: "qkv", "o_proj", ...).  Kernels then run one after
 # the other (an event between two launches keeps the second from starting early), so the sum is more than an
-# unprofiled step takes; the shares are what it is for.  Not for captured steps.
+# unprofiled step takes; the shares are what it is for.  A step that is launched kernel by kernel from the host is
+# timed truly only where its kernels outlast the host's work per launch (prompts); a decode step is therefore captured
+# with a kernel between every two of its kernels that writes the device's clock (capture_begin/capture_end), and the
+# stamps are read after each replay.
 tag: str | None = None
-_profile: list | None = None
+_profile: list | None = None      # (name, event) in launch order, eager launches
+_booked: dict | None = None       # {name: ms} already read from captured steps
+_capturing: list | None = None    # the capture that is being made: [stamps, None, name, name, ...]
+_suspended = False
 
 
 def profile_begin() -> None:
-    global _profile
+    global _profile, _booked
     e = torch.cuda.Event(enable_timing=True)
     e.record()
     _profile = [(None, e)]
+    _booked = {}
+
+
+def profile_active() -> bool:
+    return _profile is not None
 
 
 def profile_end() -> dict:
     """{name: milliseconds} of everything launched since profile_begin(), in the order of first appearance."""
-    global _profile
+    global _profile, _booked
     events, _profile = _profile or [], None
+    booked, _booked = _booked or {}, None
     torch.cuda.synchronize()
     out: dict = {}
     for (_, before), (name, after) in zip(events, events[1:]):
-        out[name] = out.get(name, 0.0) + before.elapsed_time(after)
+        if name is not None:
+            out[name] = out.get(name, 0.0) + before.elapsed_time(after)
+    for name, ms in booked.items():
+        out[name] = out.get(name, 0.0) + ms
     return out
+
+
+class profile_suspended:
+    """Launches inside are not timed (a warm-up step in front of a capture)."""
+
+    def __enter__(self):
+        global _suspended
+        self.was, _suspended = _suspended, True
+
+    def __exit__(self, *exc):
+        global _suspended
+        _suspended = self.was
+        if _profile is not None:   # what ran meanwhile is not booked to the next launch
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            _profile.append((None, e))
+
+
+STAMPS = 8192   # kernels of one captured step that can be timed
+
+
+def _stamp(stamps: torch.Tensor, index: int) -> None:
+    rc = _lib().hymt2_stamp(ctypes.c_void_p(stamps.data_ptr() + 8 * index), _stream())
+    if rc != 0:
+        raise KernelError(f"stamp failed ({rc}): {_lib().hymt2_last_error().decode(errors='replace')}")
+
+
+def capture_begin(device) -> None:
+    """Inside a graph capture: from here on every launch is followed by a kernel that writes the device's clock."""
+    global _capturing
+    stamps = torch.zeros(STAMPS, dtype=torch.int64, device=device)
+    _capturing = [stamps, None]
+    _stamp(stamps, STAMPS - 2)   # two stamps with nothing between them: what a stamp itself costs
+    _stamp(stamps, STAMPS - 1)
+    _stamp(stamps, 0)
+
+
+def capture_end() -> list:
+    """[the stamps' tensor, None, name of launch 1, name of launch 2, ...]: what book_captured() wants."""
+    global _capturing
+    record, _capturing = _capturing or [], None
+    return record
+
+
+def book_captured(record: list) -> None:
+    """After a replay of a graph captured between capture_begin() and capture_end(): waits for it and adds its kernels'
+    times to the running profile (the time from the stamp in front of a kernel to the stamp behind it, less what a
+    stamp costs)."""
+    torch.cuda.synchronize()
+    if _booked is None or not record:
+        return
+    names = record[2:]
+    at = record[0].cpu().tolist()
+    own = max(0, at[STAMPS - 1] - at[STAMPS - 2])
+    for i, name in enumerate(names):
+        _booked[name] = _booked.get(name, 0.0) + max(0, at[i + 1] - at[i] - own) * 1e-6
 
 
 def profile_line(phase: str, times: dict) -> str:
@@ -81,10 +152,16 @@ def _check(rc: int, what: str, kernels: int = 1, timed: bool = True) -> None:
     if rc != 0:
         msg = _lib().hymt2_last_error().decode(errors="replace")
         raise KernelError(f"{what} failed ({rc}): {msg}")
-    if _profile is not None and timed and kernels > 0:
-        e = torch.cuda.Event(enable_timing=True)
-        e.record()
-        _profile.append((tag or what, e))
+    if timed and kernels > 0 and not _suspended:
+        if _capturing is not None:
+            if len(_capturing) - 1 >= STAMPS - 2:
+                raise KernelError(f"a captured step of more than {STAMPS - 3} kernels cannot be timed")
+            _stamp(_capturing[0], len(_capturing) - 1)
+            _capturing.append(tag or what)
+        elif _profile is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            _profile.append((tag or what, e))
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:

@@ -51,6 +51,16 @@ def test_a_product_with_few_tiles_is_cut_to_about_one_wave(describe):
     assert head["k_splits"] == 1 and head["tiles"] == 944
 
 
+def test_65_to_128_tokens_of_a_split_product_are_two_tiles_of_64_that_fold_as_clusters(describe):
+    for N, K, epi in ((2048, 2048, ADD), (2048, 6144, ADD), (3072, 2048, STORE), (3072, 2048, QKV)):
+        at64, at100 = describe(64, N, K, epi), describe(100, N, K, epi)
+        assert at64["tile_width"] == 64 and at64["cluster"]
+        assert at100["tile_width"] == 64 and at100["cluster"] and at100["tiles"] == 2 * at64["tiles"]
+        assert at100["k_splits"] == at64["k_splits"]
+    assert describe(100, 120818, 2048, STORE)["tile_width"] == 128      # enough tiles: the weights are read once
+    assert describe(100, 6144, 2048, SWIGLU)["tile_width"] == 128       # two accumulators: folds through memory anyway
+
+
 def test_prompt_sized_products_fill_whole_waves(describe):
     # the sizes of the 1.8B model at 2,048 tokens
     gate_up = describe(2048, 6144, 2048, SWIGLU)

@@ -146,3 +146,28 @@ def test_command_line(model_dirs, plain_models):
     assert "Assistant: " + ",".join(map(str, want)) in r.stdout  # --max-tokens 5: the first token + 5 decode steps
     assert "prefill tokens=6" in r.stdout and "decode tokens=5" in r.stdout
     assert "arch=HunYuanDenseV1ForCausalLM layers=2 hidden=64 heads=4/2 vocab=256" in r.stdout
+
+
+@pytest.mark.parametrize("name,dtype", [("H", "bfloat16"), ("A", "float32")])
+def test_profiled_generation_books_every_kernel_and_changes_no_token(name, dtype, engines, plain_models):
+    """The profiling switch: decode steps are replayed from a graph that holds an event behind every kernel; the tokens are
+    those of an unprofiled run, both phases are booked by product and kernel, and unprofiled steps afterwards still work."""
+    eng = engines(name, dtype)
+    vocab = plain_models(name).cfg.vocab
+    prompts = [helpers.random_tokens(vocab, n, 70 + i) for i, n in enumerate(PROMPT_LENS[name])]
+    plain_run = eng.generate(prompts, max_new_tokens=9)
+    timed = eng.generate(prompts, max_new_tokens=9, profile=True)
+    assert [r.tokens for r in timed.results] == [r.tokens for r in plain_run.results]
+    assert set(timed.stats.profile) == {"prefill", "decode"}
+    for phase, times in timed.stats.profile.items():
+        assert {"qkv", "o_proj", "gate_up", "down", "head"} <= set(times) or {"qkv+rope", "o_proj", "gate_up", "down", "head"} <= set(times), times
+        assert any(k.startswith("attention") for k in times), times
+        assert all(v > 0 for v in times.values()), times
+    # a decode kernel of these sizes takes microseconds: eight steps of a few layers stay far below what a host-bound
+    # measurement (tens of microseconds per launch) would book
+    layers = eng.config.num_hidden_layers
+    assert timed.stats.profile["decode"]["o_proj"] < 8 * layers * 0.030
+    assert plain_run.stats.profile == {}
+    again = eng.generate(prompts, max_new_tokens=9)
+    assert [r.tokens for r in again.results] == [r.tokens for r in plain_run.results]
+    eng.cache.book.audit()
