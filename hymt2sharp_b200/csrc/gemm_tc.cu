@@ -34,7 +34,8 @@
 namespace {
 
 constexpr int BLOCK_K = 64, UMMA_K = 16, TILE_M = 128, MAX_STAGES = 8;
-constexpr int NUM_THREADS = 192;          // persistent kernel: warp 0 TMA, warp 1 MMAs, warps 2-5 epilogue
+constexpr int EPILOGUE_GROUPS = 2;        // persistent kernel: groups of four epilogue warps, one per accumulator
+constexpr int NUM_THREADS = 64 + 128 * EPILOGUE_GROUPS;   // warp 0 TMA, warp 1 MMAs, then the epilogue groups
 // one-tile kernel: with few accumulator columns a second warp issues MMAs too (warp 6), see ISSUERS in the kernel
 __host__ __device__ constexpr int tile_issuers(int bn, bool swapped, int epi) {
     return (swapped && bn * ((swapped && epi == 2) ? 2 : 1) <= 32) ? 2 : 1;   // measured: no gain with 64 columns and more
@@ -954,14 +955,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         }
     } else if (warp >= 2) {
         // ---- epilogue ---------------------------------------------------------------------------------
-        const int quarter = warp & 3, row = quarter * 32 + lane;
+        // Two groups of four warps, one per accumulator: group 0 takes this CTA's tiles 0, 2, 4, ..., group 1 the tiles
+        // 1, 3, 5, ...  An epilogue that reads and writes memory (the add into the residual, the rotation) lasts longer
+        // than a short tile's MMAs; with a group per accumulator two epilogues run at the same time.
+        const int quarter = warp & 3, row = quarter * 32 + lane, group = (warp - 2) >> 2;
         pdl_wait();   // C may still be in use by the kernel before
         // the kernel after this one may read the cache before its own wait; it must not start while the kernel
         // before this one still runs: wait first, release after
         if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();
         TC* C = (TC*)p.C;
-        int j = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, j++) {
+        int j = group;
+        static_assert(EPILOGUE_GROUPS == 2, "a group serves the accumulator of its number");
+        for (int tile = blockIdx.x + group * gridDim.x; tile < num_tiles; tile += EPILOGUE_GROUPS * gridDim.x, j += EPILOGUE_GROUPS) {
             const int buf = j & 1;
             const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
             if (!mbar_wait(acc_full0 + 8 * buf, (uint32_t)((j >> 1) & 1), abort_flag, p.status, 103)) break;
@@ -1229,9 +1234,10 @@ int sm_count_of_current_device() {
 }  // namespace
 
 // The numbers of the kernels' barrier protocols: out[0] the most stages of a ring, [1] accumulators of the persistent
-// kernel that alternate, [2] the most MMA issuers of the one-tile kernel, [3] 1: issuer j owns the stages j, j + issuers, ...
+// kernel that alternate, [2] the most MMA issuers of the one-tile kernel, [3] 1: issuer j owns the stages j, j + issuers, ...,
+// [4] epilogue groups of the persistent kernel (group g drains the tiles g, g + groups, ... of its CTA)
 HYMT2_API int hymt2_gemm_tc_protocol(int* out) {
-    out[0] = MAX_STAGES; out[1] = 2; out[2] = tile_issuers(16, true, EPI_STORE); out[3] = 1;
+    out[0] = MAX_STAGES; out[1] = 2; out[2] = tile_issuers(16, true, EPI_STORE); out[3] = 1; out[4] = EPILOGUE_GROUPS;
     return HYMT2_OK;
 }
 

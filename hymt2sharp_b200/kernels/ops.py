@@ -475,7 +475,7 @@ def protocol_numbers() -> dict:
         return dict(zip(names, out))
     return {"prefill": ask("hymt2_attention_prefill_tc_protocol", ("kv_stages", "k_slots", "p_bars", "o_bars", "stage_holders", "s_buffers")),
             "decode": ask("hymt2_attention_decode_tc_protocol", ("stages", "accumulators")),
-            "gemm": ask("hymt2_gemm_tc_protocol", ("max_stages", "accumulators", "issuers", "issuers_own_stages"))}
+            "gemm": ask("hymt2_gemm_tc_protocol", ("max_stages", "accumulators", "issuers", "issuers_own_stages", "epilogue_groups"))}
 
 
 def gemm_tc_rope_kv_wants_angles(tokens: int, rope_dim: int) -> bool:

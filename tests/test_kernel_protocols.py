@@ -185,10 +185,11 @@ def test_no_interleaving_of_the_decode_attentions_protocol_goes_wrong(items):
 #   producer   for every k block: wait "stage free" (the block a ring earlier), copy the stage
 #   issuer     for every tile j: wait "accumulator j mod 2 drained" (tile j - 2); for its k blocks: wait the stage, issue the
 #              MMAs (their completion frees the stage); then the tile's completion fills the accumulator's barrier
-#   epilogue   for every tile: wait the accumulator, drain it, announce it empty
+#   epilogue   group g, for the tiles g, g + groups, ...: wait the accumulator, drain it, announce it empty
 # (the looks ahead at the next stage's barrier are reads of the same reader in the same order: nothing new for this model)
-def persistent_gemm(tiles, k_blocks, stages):
-    producer, issuer, epilogue = [], [], []
+def persistent_gemm(tiles, k_blocks, stages, groups=None):
+    groups = groups or NUMBERS["gemm"]["epilogue_groups"]
+    producer, issuer, epilogues = [], [], [[] for _ in range(groups)]
     block = 0
     for j in range(tiles):
         if j >= 2:
@@ -201,15 +202,17 @@ def persistent_gemm(tiles, k_blocks, stages):
             issuer += [("wait", "full", s, use), ("issue", "MMA", [("empty", s)])]
             block += 1
         issuer.append(("issue", "MMA", [("acc_full", j & 1)]))
-        epilogue += [("wait", "acc_full", j & 1, j >> 1), ("arrive", "acc_empty", j & 1)]
-    return explore((producer, issuer, epilogue), {"full": stages, "empty": stages, "acc_full": 2, "acc_empty": 2})
+        epilogues[j % groups] += [("wait", "acc_full", j & 1, j >> 1), ("arrive", "acc_empty", j & 1)]
+    return explore((producer, issuer, *epilogues), {"full": stages, "empty": stages, "acc_full": 2, "acc_empty": 2})
 
 
 @pytest.mark.parametrize("tiles, k_blocks, stages", [(1, 1, 4), (3, 2, 4), (5, 3, 2), (6, 4, 5), (4, 9, 4),
                                                      (3, 10, NUMBERS["gemm"]["max_stages"])])
 def test_no_interleaving_of_the_persistent_products_protocol_goes_wrong(tiles, k_blocks, stages):
     assert NUMBERS["gemm"]["accumulators"] == 2 and 2 <= stages <= NUMBERS["gemm"]["max_stages"]
+    assert NUMBERS["gemm"]["epilogue_groups"] in (1, 2)   # a group per accumulator, or one group for both
     assert persistent_gemm(tiles, k_blocks, stages) is None
+    assert persistent_gemm(tiles, k_blocks, stages, groups=1) is None
 
 
 # ---- the tile kernel of the matrix product with several MMA issuers (few tokens): who may read which stage's barrier ----
