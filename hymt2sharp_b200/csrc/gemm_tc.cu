@@ -1146,11 +1146,14 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         pl.tiles = tiles * (int)pl.grid.y;
     } else {
         // The persistent kernel (one CTA per SM, wide tiles, epilogue hidden behind the next tile) wherever the output
-        // is written once; where it is added to the float32 residual (twice the epilogue traffic), only when there is a
-        // 256-wide tile for every SM: below that, 128-wide tiles with two CTAs per SM measured faster.
+        // is written once.  Where it is added to the float32 residual (twice the epilogue traffic): when there is a
+        // 256-wide tile for every SM, or when 128 x 128 tiles would not put two CTAs on most SMs anyway (up to 1.5 tiles
+        // an SM; measured at 256 to 1,536 tokens: the persistent kernel's ring is the better pipeline, down projection at
+        // 1,536 tokens 54 -> 45 us); between the two, 128-wide tiles with two CTAs per SM measured faster.
         const int row_tiles = (T + TILE_M - 1) / TILE_M;
         const long wide_tiles = (long)row_tiles * ((N + PERSISTENT_BN - 1) / PERSISTENT_BN);
-        pl.persistent = epilogue != EPI_ACCUMULATE || wide_tiles >= sm_count;
+        const long tiles_128 = (long)row_tiles * ((N + 127) / 128);
+        pl.persistent = epilogue != EPI_ACCUMULATE || wide_tiles >= sm_count || 2 * tiles_128 <= 3 * sm_count;
         pl.bn = 128;
         if (pl.persistent) {
             // The tile's width: the one whose tiles fill whole waves of SMs best.  A k block of a tile bn wide

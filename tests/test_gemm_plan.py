@@ -51,6 +51,15 @@ def test_a_product_with_few_tiles_is_cut_to_about_one_wave(describe):
     assert head["k_splits"] == 1 and head["tiles"] == 944
 
 
+def test_products_that_add_into_the_residual_take_the_tile_kernel_only_between_the_two_persistent_ranges(describe):
+    # few tiles (two CTAs an SM would not come about anyway) and many tiles (a 256-wide tile for every SM): persistent
+    assert describe(300, 2048, 2048, ADD)["persistent"] and describe(1536, 2048, 6144, ADD)["persistent"]
+    assert describe(4096, 2048, 2048, ADD)["persistent"]
+    # between: 128 x 128 tiles, two CTAs an SM
+    mid = describe(2048, 2048, 2048, ADD)
+    assert not mid["persistent"] and mid["tile_width"] == 128 and mid["ctas"] == 256
+
+
 def test_65_to_128_tokens_of_a_split_product_are_two_tiles_of_64_that_fold_as_clusters(describe):
     for N, K, epi in ((2048, 2048, ADD), (2048, 6144, ADD), (3072, 2048, STORE), (3072, 2048, QKV)):
         at64, at100 = describe(64, N, K, epi), describe(100, N, K, epi)
