@@ -1,7 +1,7 @@
 // bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
 //   C = epilogue(X[T,K] · W[N,K]^T), float32 accumulation in tensor memory (TMEM).
 //
-// One CTA computes one 128 x BN tile with `tcgen05.mma` (cta_group::1, M = 128, K = 16 per
+// A CTA computes 128 x BN tiles with `tcgen05.mma` (cta_group::1, M = 128, K = 16 per
 // instruction).  Operand tiles of 64 K-elements (128 bytes a row, 128-byte swizzle) are brought
 // into shared memory by TMA (`cp.async.bulk.tensor.2d`) through a ring of stages guarded by
 // mbarriers; one thread issues the TMA loads, one thread issues the MMAs, four warps read the
@@ -10,7 +10,7 @@
 // Two orientations:
 //   normal   the 128-row side holds tokens, the BN side holds output features (more than 128 tokens): a
 //            persistent kernel with one CTA per SM that walks tiles of a width chosen to fill whole waves
-//            (see gemm_tc_persistent_kernel and make_plan), or 128 x 128 tiles with two CTAs per SM;
+//            (see gemm_tc_persistent_kernel and make_plan);
 //   swapped  the 128-row side holds output features (weight rows), the BN side holds tokens
 //            (BN = 16..128): a decode step streams every weight tile once at full tile height
 //            whatever the batch is.  With `splits` > 1 the K range is cut over gridDim.z.  The
@@ -37,10 +37,10 @@ constexpr int BLOCK_K = 64, UMMA_K = 16, TILE_M = 128, MAX_STAGES = 8;
 constexpr int EPILOGUE_GROUPS = 2;        // persistent kernel: groups of four epilogue warps, one per accumulator
 constexpr int NUM_THREADS = 64 + 128 * EPILOGUE_GROUPS;   // warp 0 TMA, warp 1 MMAs, then the epilogue groups
 // one-tile kernel: with few accumulator columns a second warp issues MMAs too (warp 6), see ISSUERS in the kernel
-__host__ __device__ constexpr int tile_issuers(int bn, bool swapped, int epi) {
-    return (swapped && bn * ((swapped && epi == 2) ? 2 : 1) <= 32) ? 2 : 1;   // measured: no gain with 64 columns and more
+__host__ __device__ constexpr int tile_issuers(int bn, int epi) {
+    return bn * (epi == 2 ? 2 : 1) <= 32 ? 2 : 1;   // measured: no gain with 64 columns and more
 }
-__host__ __device__ constexpr int tile_threads(int bn, bool swapped, int epi) { return tile_issuers(bn, swapped, epi) > 1 ? 224 : 192; }
+__host__ __device__ constexpr int tile_threads(int bn, int epi) { return tile_issuers(bn, epi) > 1 ? 224 : 192; }
 constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 2;
 constexpr int PERSISTENT_BN = 256;   // tile width of the persistent kernel for many tokens
 
@@ -271,11 +271,10 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
 // carry a copy for each
 __device__ __noinline__ void sincos_once(float angle, float* sn, float* cs) { sincosf(angle, sn, cs); }
 
-template <int BN, bool SWAPPED, int EPI, typename TC>
-__global__ void __launch_bounds__(tile_threads(BN, SWAPPED, EPI), SWAPPED ? 1 : 2)   // tokens as rows: two CTAs share an SM
+template <int BN, int EPI, typename TC>
+__global__ void __launch_bounds__(tile_threads(BN, EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
-    constexpr int NUM_ACC = (SWAPPED && EPI == EPI_SWIGLU) ? 2 : 1;   // accumulators = A tiles per stage
-    constexpr bool SPLIT_B = !SWAPPED && EPI == EPI_SWIGLU;           // B tile = gate rows, then up rows
+    constexpr int NUM_ACC = EPI == EPI_SWIGLU ? 2 : 1;   // accumulators = A tiles per stage (gate rows, up rows)
     constexpr int B_TILE_BYTES = BN * BLOCK_K * 2;
     constexpr int STAGE_BYTES = NUM_ACC * A_TILE_BYTES + B_TILE_BYTES;
     constexpr int ACC_COLS = NUM_ACC * BN;
@@ -284,12 +283,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // issuer j takes the k blocks that land in the stages j, j + 2, ... of the ring (so each stage's barrier has one
     // reader, who sees every phase of it) and adds them up in an accumulator of its own; the epilogue adds the
     // accumulators, always in the same order.
-    constexpr int ISSUERS = tile_issuers(BN, SWAPPED, EPI);
+    constexpr int ISSUERS = tile_issuers(BN, EPI);
     static_assert(ISSUERS == 1 || ACC_COLS <= 32, "two issuers are for narrow accumulators");
     constexpr int PHYS_COLS = ACC_COLS * ISSUERS;   // accumulator a of issuer j: columns (a * ISSUERS + j) * BN ..
     constexpr int TMEM_COLS = PHYS_COLS <= 32 ? 32 : PHYS_COLS <= 64 ? 64 : PHYS_COLS <= 128 ? 128 : PHYS_COLS <= 256 ? 256 : 512;
     constexpr int CH = BN >= 32 ? 32 : 16;                            // accumulator columns per epilogue chunk
-    constexpr int OUT_COLS = SPLIT_B ? BN / 2 : BN;                   // output columns that the tile covers
+    constexpr int OUT_COLS = BN;                                      // token columns that the tile covers
     // instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 
@@ -300,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (EPI != EPI_ROPE_KV) pdl_launch_dependents();
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
-    __shared__ float scale_s[SWAPPED ? BN : 1], norm_red_s[16];
+    __shared__ float scale_s[BN], norm_red_s[16];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
@@ -312,7 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb_end = min(num_k_blocks, kb_begin + p.k_blocks_per_split);
     const int my_blocks = max(0, kb_end - kb_begin);
     const int a_row0 = blockIdx.x * TILE_M;
-    const int b_row0 = blockIdx.y * OUT_COLS;   // swapped: first token; normal: first output feature
+    const int b_row0 = blockIdx.y * OUT_COLS;   // first token of the tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
@@ -337,27 +336,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---- TMA producer -------------------------------------------------------------------
         // Weights do not depend on the kernel before this one: the first ring of weight tiles is
         // requested at once, then the producer waits for that kernel and requests the activations.
-        const bool weights_are_a = SWAPPED;
         auto load_weights = [&](int i) {
             const int s = i % stages;
-            const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + NUM_ACC * A_TILE_BYTES;
+            const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES;
             const int k = (kb_begin + i) * BLOCK_K;
-            if (weights_are_a) {
-                tma_load_2d(a_dst, &map_a, bar, k, a_row0);
-                if (NUM_ACC == 2) tma_load_2d(a_dst + A_TILE_BYTES, &map_a, bar, k, p.N + a_row0);
-            } else if (SPLIT_B) {
-                tma_load_2d(b_dst, &map_b, bar, k, b_row0);
-                tma_load_2d(b_dst + B_TILE_BYTES / 2, &map_b, bar, k, p.N + b_row0);
-            } else {
-                tma_load_2d(b_dst, &map_b, bar, k, b_row0);
-            }
+            tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+            if (NUM_ACC == 2) tma_load_2d(a_dst + A_TILE_BYTES, &map_a, bar, k, p.N + a_row0);
         };
         auto load_activations = [&](int i) {
             const int s = i % stages;
-            const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + NUM_ACC * A_TILE_BYTES;
-            const int k = (kb_begin + i) * BLOCK_K;
-            if (weights_are_a) tma_load_2d(b_dst, &map_b, bar, k, b_row0);
-            else tma_load_2d(a_dst, &map_a, bar, k, a_row0);
+            const uint32_t bar = full0 + 8 * s, b_dst = tiles + s * STAGE_BYTES + NUM_ACC * A_TILE_BYTES;
+            tma_load_2d(b_dst, &map_b, bar, (kb_begin + i) * BLOCK_K, b_row0);
         };
         // (p.withhold_block, -1 in every ordinary launch: the debug entry makes the producer announce that block's
         // bytes and never copy them, so that the wait for them runs out; see hymt2_gemm_tc_debug)
@@ -421,14 +410,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         pdl_wait();   // C, the workspace and the counters may still be in use by the kernel before
         if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();   // wait first, release after
-        if (SWAPPED && EPI != EPI_ACCUMULATE && p.norm.ss_in) {
+        if (EPI != EPI_ACCUMULATE && p.norm.ss_in) {
             // the row scale of the norm in front of this product, for the tile's tokens (see NormSide)
             const int tl = threadIdx.x - 64;
             if (tl < BN) scale_s[tl] = b_row0 + tl < p.T ? norm_row_scale(p.norm, b_row0 + tl) : 0.f;
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        const bool scaled = SWAPPED && EPI != EPI_ACCUMULATE && p.norm.ss_in != nullptr;
-        float ss_acc = 0.f;   // normal orientation, producer of a norm: this thread's token row, summed over the tile's features
+        const bool scaled = EPI != EPI_ACCUMULATE && p.norm.ss_in != nullptr;
         TC* C = (TC*)p.C;
         // The cluster's fold: this CTA's share of the token columns that exist in the tile.  Where the fold adds into C,
         // the old values of the first batch of columns are asked for now, under the MMAs.
@@ -436,7 +424,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         constexpr int FOLD_COLS = BN <= 16 ? 2 : 4;            // columns whose partials are in flight together
         int c_begin = 0, c_end = 0;
         float old_first[FOLD_COLS] = {};
-        if (SWAPPED && p.cluster && p.splits > 1) {
+        if (p.cluster && p.splits > 1) {
             const int cols = min(BN, p.T - b_row0);
             const int share = (cols + p.splits - 1) / p.splits;
             c_begin = (int)blockIdx.z * share;
@@ -469,147 +457,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
         // one chunk of CH accumulator columns: g (and u for SwiGLU) -> C
         auto emit = [&](int c, const float* g, const float* u) {
-            if (SWAPPED) {
-                const int n = a_row0 + row;                    // output feature
-                if (n >= p.N) return;
-                float old[CH];
-                if (EPI == EPI_ACCUMULATE) {                   // all loads first: they do not wait for each other
-#pragma unroll
-                    for (int j = 0; j < CH; j++) {
-                        const int t = b_row0 + c + j;
-                        old[j] = t < p.T ? to_float(C[(size_t)t * p.ldc + n]) : 0.f;
-                    }
-                }
+            const int n = a_row0 + row;                    // output feature
+            if (n >= p.N) return;
+            float old[CH];
+            if (EPI == EPI_ACCUMULATE) {                   // all loads first: they do not wait for each other
 #pragma unroll
                 for (int j = 0; j < CH; j++) {
-                    const int t = b_row0 + c + j;              // token
-                    if (t >= p.T) break;
-                    TC* dst = C + (size_t)t * p.ldc + n;
-                    const float r = scaled ? scale_s[c + j] : 1.0f;
-                    if (EPI == EPI_STORE) *dst = from_float<TC>(g[j] * r);
-                    else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[j] + g[j]);
-                    else *dst = from_float<TC>(silu_mul(g[j] * r, u[j] * r));
+                    const int t = b_row0 + c + j;
+                    old[j] = t < p.T ? to_float(C[(size_t)t * p.ldc + n]) : 0.f;
                 }
-            } else if constexpr (!SWAPPED && EPI == EPI_ACCUMULATE && sizeof(TC) == 4) {
-                // Adding into the float32 residual, tokens as rows.  A thread holds 32 columns of ITS token's row; touching C
-                // that way, every load and store of a warp would hit 32 different 128-byte lines (32 rows, 8 KB apart), and
-                // the memory pipe, one line a cycle, made this epilogue as long as the tile's MMAs.  So the warp turns its
-                // 32 x 32 piece around through shared memory (the stage ring is free: every MMA of the tile is complete):
-                // then a lane owns a COLUMN, and a warp's access is one whole line of one token's row.
-                static_assert(CH == 32, "a warp turns 32 x 32 pieces around");
-                float* piece = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw))) + quarter * (32 * 33);
+            }
 #pragma unroll
-                for (int j = 0; j < 32; j++) piece[lane * 33 + j] = g[j];
-                __syncwarp();
-                const int n = b_row0 + c + lane;               // this lane's output feature
-                const bool n_ok = n < p.N;
-                const float gn = (p.norm.out && n_ok) ? norm_gain_at(p.norm, n) : 0.f;
-                const int m0 = a_row0 + quarter * 32;
-#pragma unroll
-                for (int r0 = 0; r0 < 32; r0 += 16) {          // sixteen tokens at a time: their loads are in flight together
-                    float oldv[16];
-#pragma unroll
-                    for (int r = 0; r < 16; r++) oldv[r] = (n_ok && m0 + r0 + r < p.T) ? C[(size_t)(m0 + r0 + r) * p.ldc + n] : 0.f;
-#pragma unroll
-                    for (int r = 0; r < 16; r++) {
-                        float v = 0.f;
-                        if (n_ok && m0 + r0 + r < p.T) {
-                            v = oldv[r] + piece[(r0 + r) * 33 + lane];
-                            C[(size_t)(m0 + r0 + r) * p.ldc + n] = v;
-                            if (p.norm.out) p.norm.out[(size_t)(m0 + r0 + r) * p.N + n] = __float2bfloat16_rn(v * gn);
-                        }
-                        if (p.norm.out) piece[(r0 + r) * 33 + lane] = v;   // back, for the row's sum of squares
-                    }
-                }
-                __syncwarp();
-                if (p.norm.out) {   // the thread is its token's row again
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const float v = piece[lane * 33 + j];
-                        ss_acc = fmaf(v, v, ss_acc);
-                    }
-                }
-                __syncwarp();
-            } else {
-                const int m = a_row0 + row;                    // token
-                if (m >= p.T) return;
-                const int n0 = b_row0 + c;                     // first output feature of the chunk
-                TC* dst = C + (size_t)m * p.ldc + n0;
-                const bool vec = n0 + CH <= p.N && (((uintptr_t)dst) & 15) == 0;
-                // eight outputs at a time: few values are live at once, one 16-byte store each (bfloat16)
-#pragma unroll 1
-                for (int j8 = 0; j8 < CH; j8 += 8) {
-                    float o[8];
-#pragma unroll
-                    for (int j = 0; j < 8; j++) o[j] = EPI == EPI_SWIGLU ? silu_mul(g[j8 + j], u[j8 + j]) : g[j8 + j];
-                    if (vec) {
-                        if constexpr (sizeof(TC) == 4) {
-                            float4* d4 = reinterpret_cast<float4*>(dst + j8);
-#pragma unroll
-                            for (int q = 0; q < 2; q++) {
-                                float4 v = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-                                if (EPI == EPI_ACCUMULATE) {
-                                    const float4 old = d4[q];
-                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                                    o[4 * q] = v.x; o[4 * q + 1] = v.y; o[4 * q + 2] = v.z; o[4 * q + 3] = v.w;
-                                }
-                                d4[q] = v;
-                            }
-                            if (EPI == EPI_ACCUMULATE && p.norm.out) {   // the new residual values, times the gain, as the next product's input
-                                __nv_bfloat162 h[4];
-#pragma unroll
-                                for (int q = 0; q < 4; q++) {
-                                    const float a = o[2 * q], b = o[2 * q + 1];
-                                    ss_acc = fmaf(a, a, ss_acc); ss_acc = fmaf(b, b, ss_acc);
-                                    h[q] = __floats2bfloat162_rn(a * norm_gain_at(p.norm, n0 + j8 + 2 * q), b * norm_gain_at(p.norm, n0 + j8 + 2 * q + 1));
-                                }
-                                *reinterpret_cast<uint4*>(p.norm.out + (size_t)m * p.N + n0 + j8) = *reinterpret_cast<uint4*>(h);
-                            }
-                        } else {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst + j8);
-                            if (EPI == EPI_ACCUMULATE) {
-                                const uint4 oldv = *d4;
-                                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&oldv);
-#pragma unroll
-                                for (int q = 0; q < 4; q++) { o[2 * q] += __low2float(oh[q]); o[2 * q + 1] += __high2float(oh[q]); }
-                            }
-                            __nv_bfloat162 h[4];
-#pragma unroll
-                            for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
-                            *d4 = *reinterpret_cast<uint4*>(h);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            if (n0 + j8 + j >= p.N) break;
-                            const float v = EPI == EPI_ACCUMULATE ? to_float(dst[j8 + j]) + o[j] : o[j];
-                            dst[j8 + j] = from_float<TC>(v);
-                            if (EPI == EPI_ACCUMULATE && p.norm.out) {
-                                ss_acc = fmaf(v, v, ss_acc);
-                                p.norm.out[(size_t)m * p.N + n0 + j8 + j] = __float2bfloat16_rn(v * norm_gain_at(p.norm, n0 + j8 + j));
-                            }
-                        }
-                    }
-                }
+            for (int j = 0; j < CH; j++) {
+                const int t = b_row0 + c + j;              // token
+                if (t >= p.T) break;
+                TC* dst = C + (size_t)t * p.ldc + n;
+                const float r = scaled ? scale_s[c + j] : 1.0f;
+                if (EPI == EPI_STORE) *dst = from_float<TC>(g[j] * r);
+                else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[j] + g[j]);
+                else *dst = from_float<TC>(silu_mul(g[j] * r, u[j] * r));
             }
         };
 
-        if (!SWAPPED || p.splits == 1) {   // K is only split in the swapped orientation
+        if (p.splits == 1) {
             if (ok) {
                 for (int c = 0; c < OUT_COLS; c += CH) {
                     float g[CH], u[CH];
                     acc_load(c, g);
-                    if (EPI == EPI_SWIGLU) {
-                        if (SWAPPED) acc_load(BN + c, u);
-                        else tmem_load<CH>(lane_addr + BN / 2 + c, u);
-                    }
+                    if (EPI == EPI_SWIGLU) acc_load(BN + c, u);
                     emit(c, g, u);
                 }
-                // a norm's producer in the normal orientation: this thread's token, this tile's features
-                if (!SWAPPED && EPI == EPI_ACCUMULATE && p.norm.out && a_row0 + row < p.T)
-                    p.norm.ss_out[(size_t)(a_row0 + row) * p.norm.ss_out_tiles + blockIdx.y] = ss_acc;
             }
-        } else if (SWAPPED && p.cluster) {
+        } else if (p.cluster) {
             // partial tile -> this CTA's shared memory (the stage ring is free now), [column][row].  After the
             // cluster's barrier every CTA of the cluster takes a share of the token columns that exist, adds the
             // partials of all ranks for them through distributed shared memory (in rank order: the sum is the
@@ -770,7 +649,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             __syncwarp();
             cluster_sync_all();   // every CTA keeps its shared memory until its peers have read it
-        } else if (SWAPPED) {
+        } else {
             // partial tile -> workspace [tile][split][acc][column][row]; the last arrival reduces
             const int tile = blockIdx.y * gridDim.x + blockIdx.x;
             float* ws_tile = p.workspace + (size_t)tile * p.splits * (ACC_COLS * TILE_M);
@@ -964,12 +843,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         // before this one still runs: wait first, release after
         if (EPI == EPI_ROPE_KV && threadIdx.x == 64) pdl_launch_dependents();
         TC* C = (TC*)p.C;
-        int j = group;
         static_assert(EPILOGUE_GROUPS == 2, "a group serves the accumulator of its number");
-        for (int tile = blockIdx.x + group * gridDim.x; tile < num_tiles; tile += EPILOGUE_GROUPS * gridDim.x, j += EPILOGUE_GROUPS) {
+        // The CTA's LAST tile has nothing behind it that would hide its epilogue, so both groups take it: its owner the
+        // lower half of its columns (`part` 0), the other group, once through with its own tiles, the upper half (part 1).
+        // (The helper reads a barrier it has not followed.  When it gets there it has drained tile last - 1, whose
+        // MMAs were issued after those of tile last - 2 were complete, so the barrier of the last tile's accumulator is in
+        // the last tile's own phase or past it, never one behind: the parity cannot be taken for an older one.)
+        const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        const int last = my_tiles - 1;
+        const int split_at = EPI == EPI_ROPE_KV ? (bn / TILE_M / 2) * TILE_M : ((OUT_COLS / 16 + 1) / 2) * 16;   // whole heads, whole chunks
+        const bool can_share = split_at > 0 && split_at < OUT_COLS;
+        for (int item = 0;; item++) {
+            // this group's own tiles first, then (where the last tile is the other group's) the upper half of that one
+            int j, c_begin = 0, c_end = OUT_COLS, part = 0;
+            bool own = true;
+            if (group + EPILOGUE_GROUPS * item < my_tiles) {
+                j = group + EPILOGUE_GROUPS * item;
+                if (j == last && can_share) c_end = split_at;
+            } else if (my_tiles > 0 && can_share && (last & 1) != group && group + EPILOGUE_GROUPS * (item - 1) < my_tiles && !*abort_flag) {
+                j = last; own = false; c_begin = split_at; part = 1;
+            } else break;
+            const int tile = blockIdx.x + j * gridDim.x;
             const int buf = j & 1;
             const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
-            if (!mbar_wait(acc_full0 + 8 * buf, (uint32_t)((j >> 1) & 1), abort_flag, p.status, 103)) break;
+            // (the threads of a warp leave the wait at different times; what follows reads tensor memory warp-wide, so the
+            // warp comes together first, and gives up together)
+            const bool landed = mbar_wait(acc_full0 + 8 * buf, (uint32_t)((j >> 1) & 1), abort_flag, p.status, 103);
+            if (!__all_sync(0xffffffffu, landed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
             const int m = a_row0 + row;
@@ -980,13 +880,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 // the tile holds BN / 128 heads of 128 tokens: this thread's token, head after head
                 const int heads = p.rope.nh + 2 * p.rope.nkv;
 #pragma unroll 1
-                for (int h = 0; h < bn / TILE_M; h++) {
+                for (int h = c_begin / TILE_M; h < c_end / TILE_M; h++) {
                     const int head = b_row0 / TILE_M + h;
                     if (head < heads) rope_head_from_tmem(lane_addr + h * TILE_M, m, head, m < p.T, p.rope, row_scale);
                 }
             } else
 #pragma unroll 1
-            for (int c = 0; c < OUT_COLS; c += 16) {
+            for (int c = c_begin; c < c_end; c += 16) {
                 float g[16], u[16];
                 tmem_load<16>(lane_addr + c, g);
                 if (EPI == EPI_SWIGLU) tmem_load<16>(lane_addr + bn / 2 + c, u);
@@ -1044,7 +944,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     }
                 }
             }
-            if (EPI == EPI_ACCUMULATE && p.norm.out && m < p.T) p.norm.ss_out[(size_t)m * p.norm.ss_out_tiles + tile / tiles_m] = ss_acc;
+            // two partial sums a tile: the lower and the upper half of its columns (the upper one is 0 where one group had it all)
+            if (EPI == EPI_ACCUMULATE && p.norm.out && m < p.T) {
+                float* ss = p.norm.ss_out + (size_t)m * p.norm.ss_out_tiles + (tile / tiles_m) * 2;
+                ss[part] = ss_acc;
+                if (part == 0 && c_end == OUT_COLS) ss[1] = 0.f;
+            }
+            if (!own) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(acc_empty0 + 8 * buf);   // this thread has taken its row out of the accumulator
         }
@@ -1061,9 +967,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // --------------------------------------------------------------------------------------------
 // host side
 // --------------------------------------------------------------------------------------------
-template <int BN, bool SWAPPED, int EPI, typename TC>
+template <int BN, int EPI, typename TC>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kernel = gemm_tc_kernel<BN, SWAPPED, EPI, TC>;
+    auto kernel = gemm_tc_kernel<BN, EPI, TC>;
     static bool configured = false;   // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
@@ -1074,7 +980,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, 
     if (p.cluster && p.splits > 1) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
-        cfg.blockDim = dim3(tile_threads(BN, SWAPPED, EPI));
+        cfg.blockDim = dim3(tile_threads(BN, EPI));
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
@@ -1088,19 +994,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, 
         cfg.numAttrs = 2;
         e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, p);
     } else {
-        e = launch_pdl(kernel, grid, dim3(tile_threads(BN, SWAPPED, EPI)), smem, stream, ma, mb, p);
+        e = launch_pdl(kernel, grid, dim3(tile_threads(BN, EPI)), smem, stream, ma, mb, p);
     }
     if (e != cudaSuccess) { hymt2_set_error("gemm_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
     return hymt2_check_launch("gemm_tc");
 }
 
-template <int BN, bool SWAPPED>
+template <int BN>
 int dispatch_epilogue(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, dim3 grid, size_t smem,
                       int epilogue, int c_dtype, cudaStream_t stream) {
-    if (epilogue == EPI_STORE && c_dtype == HYMT2_BF16) return launch<BN, SWAPPED, EPI_STORE, __nv_bfloat16>(ma, mb, p, grid, smem, stream);
-    if (epilogue == EPI_STORE && c_dtype == HYMT2_F32) return launch<BN, SWAPPED, EPI_STORE, float>(ma, mb, p, grid, smem, stream);
-    if (epilogue == EPI_ACCUMULATE && c_dtype == HYMT2_F32) return launch<BN, SWAPPED, EPI_ACCUMULATE, float>(ma, mb, p, grid, smem, stream);
-    if (epilogue == EPI_SWIGLU && c_dtype == HYMT2_BF16) return launch<BN, SWAPPED, EPI_SWIGLU, __nv_bfloat16>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_STORE && c_dtype == HYMT2_BF16) return launch<BN, EPI_STORE, __nv_bfloat16>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_STORE && c_dtype == HYMT2_F32) return launch<BN, EPI_STORE, float>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_ACCUMULATE && c_dtype == HYMT2_F32) return launch<BN, EPI_ACCUMULATE, float>(ma, mb, p, grid, smem, stream);
+    if (epilogue == EPI_SWIGLU && c_dtype == HYMT2_BF16) return launch<BN, EPI_SWIGLU, __nv_bfloat16>(ma, mb, p, grid, smem, stream);
     hymt2_set_error("gemm_tc: epilogue %d with output type %d is not built", epilogue, c_dtype);
     return HYMT2_ERR_ARGUMENT;
 }
@@ -1145,17 +1051,14 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
         }
         pl.tiles = tiles * (int)pl.grid.y;
     } else {
-        // The persistent kernel (one CTA per SM, wide tiles, epilogue hidden behind the next tile) wherever the output
-        // is written once.  Where it is added to the float32 residual (twice the epilogue traffic): when there is a
-        // 256-wide tile for every SM, or when 128 x 128 tiles would not put two CTAs on most SMs anyway (up to 1.5 tiles
-        // an SM; measured at 256 to 1,536 tokens: the persistent kernel's ring is the better pipeline, down projection at
-        // 1,536 tokens 54 -> 45 us); between the two, 128-wide tiles with two CTAs per SM measured faster.
+        // More than 128 tokens: the persistent kernel (one CTA per SM, wide tiles, a tile's epilogue hidden behind the
+        // next tile's MMAs, the last one shared by both epilogue groups).  Tiles of 128 x 128 with two CTAs per SM were
+        // measured against it for the products that add into the residual: slower at every size once the last tile's
+        // epilogue was shared (down projection at 2,048 tokens 56 -> 49 us, at 1,536 tokens 54 -> 45 us).
         const int row_tiles = (T + TILE_M - 1) / TILE_M;
-        const long wide_tiles = (long)row_tiles * ((N + PERSISTENT_BN - 1) / PERSISTENT_BN);
-        const long tiles_128 = (long)row_tiles * ((N + 127) / 128);
-        pl.persistent = epilogue != EPI_ACCUMULATE || wide_tiles >= sm_count || 2 * tiles_128 <= 3 * sm_count;
+        pl.persistent = true;
         pl.bn = 128;
-        if (pl.persistent) {
+        {
             // The tile's width: the one whose tiles fill whole waves of SMs best.  A k block of a tile bn wide
             // costs about 350 + 1.84 bn cycles (measured at 192 to 256), and a wave lasts as long as one tile; behind
             // the last wave one epilogue stands alone, which costs about 60 cycles a column where it rotates and
@@ -1188,7 +1091,8 @@ bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && CLUSTER_RING_BYTES / stage_bytes >= 4 &&
                  (size_t)num_acc * pl.bn * TILE_M * 4 <= 96 * 1024;
     // one wave of CTAs: each takes what an SM has; more: two CTAs share an SM, one's epilogue hides behind the other's loads
-    const int ring_bytes = pl.cluster ? CLUSTER_RING_BYTES : pl.persistent ? 224 * 1024 : ctas <= sm_count ? 200 * 1024 : 100 * 1024;   // persistent: one CTA per SM, all it has
+    // (the persistent kernel: one CTA per SM, all it has)
+    const int ring_bytes = pl.cluster ? CLUSTER_RING_BYTES : pl.persistent ? 224 * 1024 : ctas <= sm_count ? 200 * 1024 : 100 * 1024;
     int stages = ring_bytes / stage_bytes;
     stages = stages > MAX_STAGES ? MAX_STAGES : stages < 2 ? 2 : stages;
     if (pl.swapped && stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
@@ -1240,7 +1144,7 @@ int sm_count_of_current_device() {
 // kernel that alternate, [2] the most MMA issuers of the one-tile kernel, [3] 1: issuer j owns the stages j, j + issuers, ...,
 // [4] epilogue groups of the persistent kernel (group g drains the tiles g, g + groups, ... of its CTA)
 HYMT2_API int hymt2_gemm_tc_protocol(int* out) {
-    out[0] = MAX_STAGES; out[1] = 2; out[2] = tile_issuers(16, true, EPI_STORE); out[3] = 1; out[4] = EPILOGUE_GROUPS;
+    out[0] = MAX_STAGES; out[1] = 2; out[2] = tile_issuers(16, EPI_STORE); out[3] = 1; out[4] = EPILOGUE_GROUPS;
     return HYMT2_OK;
 }
 
@@ -1279,7 +1183,7 @@ namespace {
 int norm_out_tiles(const Plan& pl, int epilogue) {
     if (epilogue != EPI_ACCUMULATE) return 0;
     if (pl.swapped) return (pl.splits > 1 && pl.cluster) ? (int)pl.grid.x : 0;   // the cluster's fold holds (token, tile) whole
-    return (int)pl.grid.y;                                                        // a thread owns a token's row of the tile
+    return 2 * (int)pl.grid.y;   // the persistent kernel: two partial sums a tile (a thread owns a token's row of half a tile)
 }
 
 int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw, long ldc,
@@ -1319,14 +1223,13 @@ int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N
                       "(T=%d N=%d K=%d gives swapped=%d splits=%d)", T, N, K, (int)pl.swapped, pl.splits);
     if (pl.swapped) {
         switch (pl.bn) {
-            case 16: return dispatch_epilogue<16, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
-            case 32: return dispatch_epilogue<32, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
-            case 64: return dispatch_epilogue<64, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
-            default: return dispatch_epilogue<128, true>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            case 16: return dispatch_epilogue<16>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            case 32: return dispatch_epilogue<32>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            case 64: return dispatch_epilogue<64>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+            default: return dispatch_epilogue<128>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
         }
     }
-    if (pl.persistent) return launch_persistent(ma, mb, p, pl, epilogue, c_dtype, stream);
-    return dispatch_epilogue<128, false>(ma, mb, p, pl.grid, pl.smem, epilogue, c_dtype, stream);
+    return launch_persistent(ma, mb, p, pl, epilogue, c_dtype, stream);
 }
 }  // namespace
 
@@ -1431,8 +1334,8 @@ HYMT2_API int hymt2_gemm_tc_rope_kv(const void* X, const void* W, int T, int K, 
         return launch_persistent_one<PERSISTENT_BN, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, ctas, pl.smem, stream);
     }
     switch (pl.bn) {
-        case 16: return launch<16, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
-        case 32: return launch<32, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
-        default: return launch<64, true, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
+        case 16: return launch<16, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
+        case 32: return launch<32, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
+        default: return launch<64, EPI_ROPE_KV, __nv_bfloat16>(ma, mb, p, pl.grid, pl.smem, stream);
     }
 }

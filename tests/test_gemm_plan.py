@@ -51,13 +51,12 @@ def test_a_product_with_few_tiles_is_cut_to_about_one_wave(describe):
     assert head["k_splits"] == 1 and head["tiles"] == 944
 
 
-def test_products_that_add_into_the_residual_take_the_tile_kernel_only_between_the_two_persistent_ranges(describe):
-    # few tiles (two CTAs an SM would not come about anyway) and many tiles (a 256-wide tile for every SM): persistent
-    assert describe(300, 2048, 2048, ADD)["persistent"] and describe(1536, 2048, 6144, ADD)["persistent"]
-    assert describe(4096, 2048, 2048, ADD)["persistent"]
-    # between: 128 x 128 tiles, two CTAs an SM
-    mid = describe(2048, 2048, 2048, ADD)
-    assert not mid["persistent"] and mid["tile_width"] == 128 and mid["ctas"] == 256
+def test_more_than_128_tokens_always_run_the_persistent_kernel(describe):
+    for T in (129, 300, 1536, 2048, 4096, 16384):
+        for N, K, epi in ((2048, 2048, ADD), (2048, 6144, ADD), (6144, 2048, SWIGLU), (3072, 2048, STORE), (3072, 2048, QKV)):
+            plan = describe(T, N, K, epi)
+            assert plan["persistent"] and not plan["swapped"] and plan["k_splits"] == 1
+            assert plan["ctas"] == min(plan["tiles"], SMS)
 
 
 def test_65_to_128_tokens_of_a_split_product_are_two_tiles_of_64_that_fold_as_clusters(describe):
@@ -77,10 +76,10 @@ def test_prompt_sized_products_fill_whole_waves(describe):
     qkv = describe(2048, 3072, 2048, QKV)
     assert qkv["persistent"] and qkv["tile_width"] == 128          # one head a tile up to a few thousand tokens
     assert describe(8192, 3072, 2048, QKV)["tile_width"] == 256    # two heads beyond
-    # adding into the residual: 128 x 128 tiles, two CTAs per SM, until there is a 256-wide tile for every SM
+    # adding into the residual: one wave of 240-wide tiles at 2,048 tokens (144 of them), every SM busy at 4,096
     for K in (2048, 6144):
         small, large = describe(2048, 2048, K, ADD), describe(4096, 2048, K, ADD)
-        assert not small["persistent"] and small["tile_width"] == 128 and small["ctas"] == 256
+        assert small["persistent"] and small["tile_width"] == 240 and small["ctas"] == 144
         assert large["persistent"] and large["ctas"] == SMS
 
 

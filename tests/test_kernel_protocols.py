@@ -185,7 +185,8 @@ def test_no_interleaving_of_the_decode_attentions_protocol_goes_wrong(items):
 #   producer   for every k block: wait "stage free" (the block a ring earlier), copy the stage
 #   issuer     for every tile j: wait "accumulator j mod 2 drained" (tile j - 2); for its k blocks: wait the stage, issue the
 #              MMAs (their completion frees the stage); then the tile's completion fills the accumulator's barrier
-#   epilogue   group g, for the tiles g, g + groups, ...: wait the accumulator, drain it, announce it empty
+#   epilogue   group g, for the tiles g, g + groups, ...: wait the accumulator, drain it, announce it empty; then help with
+#              the last tile if it is the other group's
 # (the looks ahead at the next stage's barrier are reads of the same reader in the same order: nothing new for this model)
 def persistent_gemm(tiles, k_blocks, stages, groups=None):
     groups = groups or NUMBERS["gemm"]["epilogue_groups"]
@@ -203,6 +204,11 @@ def persistent_gemm(tiles, k_blocks, stages, groups=None):
             block += 1
         issuer.append(("issue", "MMA", [("acc_full", j & 1)]))
         epilogues[j % groups] += [("wait", "acc_full", j & 1, j >> 1), ("arrive", "acc_empty", j & 1)]
+    if groups == 2:
+        # the CTA's last tile is drained by both groups: the group that does not own it waits for its accumulator too,
+        # on a barrier whose earlier phases it has not followed, once it is through with its own tiles
+        last = tiles - 1
+        epilogues[1 - last % 2].append(("wait", "acc_full", last & 1, last >> 1))
     return explore((producer, issuer, *epilogues), {"full": stages, "empty": stages, "acc_full": 2, "acc_empty": 2})
 
 
