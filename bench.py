@@ -186,10 +186,15 @@ def kernel_fractions(cfg, batch: int, prefill_tokens: int, context: int, pk: dic
     runs = {
         "gate_up_decode": ("hbm", lambda: mb.measure_gemm(batch, F, H, "swiglu", copies=8)),
         "down_decode": ("hbm", lambda: mb.measure_gemm(batch, H, F, "accumulate", copies=8)),
-        "qkv_decode": ("hbm", lambda: mb.measure_gemm(batch, cfg.q_size + 2 * cfg.kv_size, H, "store", copies=16)),
+        # q/k/v with rotation, per-head norm and cache append, the kernel the engine runs (heads of 128), else the plain product
+        "qkv_decode": ("hbm", (lambda: mb.measure_qkv_rope(batch, nh, nkv, H, copies=16)) if d == 128 else
+                       (lambda: mb.measure_gemm(batch, cfg.q_size + 2 * cfg.kv_size, H, "store", copies=16))),
         "o_proj_decode": ("hbm", lambda: mb.measure_gemm(batch, H, cfg.q_size, "accumulate", copies=16)),
         "lm_head_decode": ("hbm", lambda: mb.measure_gemm(batch, V, H, "store", float_out=True, copies=big, iters=8)),
         "attention_decode": ("hbm", lambda: mb.measure_attention_decode(batch, context, nh, nkv, d, copies=8)),
+        "qkv_prefill": ("tensor", (lambda: mb.measure_qkv_rope(prefill_tokens, nh, nkv, H, copies=4)) if d == 128 else
+                        (lambda: mb.measure_gemm(prefill_tokens, cfg.q_size + 2 * cfg.kv_size, H, "store", copies=4))),
+        "o_proj_prefill": ("tensor", lambda: mb.measure_gemm(prefill_tokens, H, cfg.q_size, "accumulate", copies=4)),
         "gate_up_prefill": ("tensor", lambda: mb.measure_gemm(prefill_tokens, F, H, "swiglu", copies=4)),
         "down_prefill": ("tensor", lambda: mb.measure_gemm(prefill_tokens, H, F, "accumulate", copies=4)),
         "attention_prefill": ("tensor", lambda: mb.measure_attention_prefill(prefill_tokens, nh, nkv, d)),

@@ -300,6 +300,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
     __shared__ float scale_s[BN], norm_red_s[16];
+    __shared__ int rope_pos_s[EPI == EPI_ROPE_KV ? BN : 1];
+    __shared__ long long rope_at_s[EPI == EPI_ROPE_KV ? BN : 1];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
@@ -435,6 +437,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (c_begin + q < c_end) old_first[q] = to_float(C[(size_t)(b_row0 + c_begin + q) * p.ldc + a_row0 + row]);
             }
         }
+        // The rotation epilogue: where each of this CTA's tokens stands and where its k or v row lies in the cache is
+        // a chain of three loads (position, slot, block).  It is walked now, under the MMAs, one thread a token.
+        float rope_inv_freq = 0.f, rope_gain = 1.f;
+        if constexpr (EPI == EPI_ROPE_KV) {
+            const RopeEpilogue& rp = p.rope;
+            const int head = blockIdx.x, tl = threadIdx.x - 64;
+            const bool is_q = head < rp.nh, is_k = !is_q && head < rp.nh + rp.nkv;
+            if (tl < c_end - c_begin && tl < BN) {
+                const int t = b_row0 + c_begin + tl;
+                const int pos = rp.token_pos[t], slot = rp.slot_ids[rp.token_seq[t]];
+                long long at = -1;
+                if (!is_q && rp.write_kv && slot >= 0) {
+                    const int block = rp.block_table[(size_t)slot * rp.table_stride + pos / rp.block_tokens];
+                    const int kvh = is_k ? head - rp.nh : head - rp.nh - rp.nkv;
+                    at = (((long long)block * rp.nkv + kvh) * rp.block_tokens + (pos % rp.block_tokens)) * TILE_M;
+                }
+                rope_pos_s[tl] = pos;
+                rope_at_s[tl] = at;
+            }
+            const int half = rp.rope_dim / 2;
+            if (row < rp.rope_dim && (is_q || is_k)) rope_inv_freq = rp.inv_freq[row < half ? row : row - half];
+            const void* gain = is_q ? rp.q_gain : is_k ? rp.k_gain : nullptr;
+            if (gain) rope_gain = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[row]) : ((const float*)gain)[row];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
 
         bool ok = my_blocks > 0 ? mbar_wait(done_bar, 0, abort_flag, p.status, 103, p.wait_limit) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -554,17 +581,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int q = 0; q < FOLD_COLS; q++) {
                             const bool in = c0 + q < c_end;
-                            const int t = b_row0 + c0 + q;
                             x[q] = __bfloat162float(__float2bfloat16_rn(g[q]));   // what the projection would have stored
-                            pos[q] = in ? rp.token_pos[t] : 0;
-                            const int slot = in ? rp.slot_ids[rp.token_seq[t]] : -1;
-                            write_kv[q] = in && !is_q && rp.write_kv && slot >= 0;
-                            cache_at[q] = 0;
-                            if (write_kv[q]) {
-                                const int block = rp.block_table[(size_t)slot * rp.table_stride + pos[q] / rp.block_tokens];
-                                const int kvh = is_k ? head - rp.nh : head - rp.nh - rp.nkv;
-                                cache_at[q] = (((size_t)block * rp.nkv + kvh) * rp.block_tokens + (pos[q] % rp.block_tokens)) * TILE_M + d;
-                            }
+                            pos[q] = in ? rope_pos_s[c0 + q - c_begin] : 0;
+                            const long long at = in ? rope_at_s[c0 + q - c_begin] : -1;
+                            write_kv[q] = at >= 0;
+                            cache_at[q] = write_kv[q] ? (size_t)at + d : 0;
                         }
                         if (!is_q && !is_k) {   // a value head: as it is (the whole CTA is this head: no barrier is missed)
 #pragma unroll
@@ -584,7 +605,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                     const bool low = d < half;
                                     float other, sn, cs;
                                     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(ex + q * EX_BYTES + (low ? d + half : d - half) * 4) : "memory");
-                                    sincos_once((float)pos[q] * rp.inv_freq[low ? d : d - half], &sn, &cs);
+                                    sincos_once((float)pos[q] * rope_inv_freq, &sn, &cs);
                                     y[q] = low ? x[q] * cs - other * sn : other * sn + x[q] * cs;
                                 }
                                 if (gain) {
@@ -594,7 +615,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             }
                             if (gain) {
                                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                                const float gv = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[d]) : ((const float*)gain)[d];
+                                const float gv = rope_gain;
 #pragma unroll
                                 for (int q = 0; q < FOLD_COLS; q++) {
                                     float s0, s1, s2, s3;

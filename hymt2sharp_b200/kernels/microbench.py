@@ -57,6 +57,39 @@ def _time(fn, warmup: int, iters: int, graph: bool) -> float:
     return e0.elapsed_time(e1) / calls * 1000.0
 
 
+def measure_qkv_rope(tokens: int, heads: int, kv_heads: int, inner: int, copies: int = 8, warmup: int = 3, iters: int = 20,
+                     graph: bool = True) -> dict:
+    """The fused q/k/v projection with rotation, per-head norm and cache append alone (heads of 128).  Up to 128 tokens
+    are one token each of as many sequences (a decode step), more are one prompt."""
+    d, bt = 128, 64
+    N = (heads + 2 * kv_heads) * d
+    ws = [(torch.randn(N, inner, device=DEV) / math.sqrt(inner)).to(BF) for _ in range(copies)]
+    x = torch.randn(tokens, inner, device=DEV).to(BF)
+    decode = tokens <= 128
+    seqs, per_seq = (tokens, 1) if decode else (1, tokens)
+    first = 2100 if decode else 0                                   # a decode step appends at position 2,100
+    blocks_per_seq = (first + per_seq + bt - 1) // bt
+    table = torch.arange(seqs * blocks_per_seq, dtype=torch.int32, device=DEV).view(seqs, blocks_per_seq).contiguous()
+    kp = torch.zeros(seqs * blocks_per_seq, kv_heads, bt, d, dtype=BF, device=DEV)
+    vp = torch.zeros_like(kp)
+    token_seq = torch.arange(tokens, dtype=torch.int32, device=DEV) // per_seq
+    token_pos = (first + torch.arange(tokens, dtype=torch.int32, device=DEV) % per_seq).to(torch.int32)
+    slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+    inv = (1.0 / (10000.0 ** (torch.arange(d // 2, dtype=torch.float32) / (d // 2)))).to(DEV)
+    gain = torch.ones(d, device=DEV, dtype=BF)
+    q_out = torch.empty(tokens, heads * d, dtype=BF, device=DEV)
+    status = ops.device_status(DEV)
+    angles = ops.rope_angles(token_pos, inv) if ops.gemm_tc_rope_kv_wants_angles(tokens, d) else None
+    i = [0]
+
+    def fn():
+        ops.gemm_tc_rope_kv(x, ws[i[0] % copies], q_out, kp, vp, table, bt, token_seq, token_pos, slots, inv, d, gain, gain, 1e-5,
+                            heads, kv_heads, status, angles=angles)
+        i[0] += 1
+    us = _time(fn, warmup, iters, graph)
+    return {"us": us, "flops": 2.0 * tokens * N * inner, "bytes": N * inner * 2.0}
+
+
 def measure_gemm(tokens: int, out_features: int, inner: int, epilogue: str = "store", float_out: bool = False,
                  copies: int = 8, warmup: int = 3, iters: int = 20, graph: bool = True) -> dict:
     """One tensor-core product alone: microseconds a call, its flops and the bytes of weights it streams."""
@@ -77,7 +110,11 @@ def measure_gemm(tokens: int, out_features: int, inner: int, epilogue: str = "st
 
 
 def gemm(a) -> None:
-    m = measure_gemm(a.tokens, a.out, a.inner, a.epilogue, a.float_out, a.copies, a.warmup, a.iters, a.graph)
+    if a.epilogue == "rope":   # --out is (heads + 2 kv heads) * 128
+        m = measure_qkv_rope(a.tokens, a.heads, a.kv_heads, a.inner, a.copies, a.warmup, a.iters, a.graph)
+        a.out = (a.heads + 2 * a.kv_heads) * 128
+    else:
+        m = measure_gemm(a.tokens, a.out, a.inner, a.epilogue, a.float_out, a.copies, a.warmup, a.iters, a.graph)
     print(f"gemm_tc tokens={a.tokens} out={a.out} inner={a.inner} epilogue={a.epilogue}: {m['us']:.1f} us  "
           f"{m['flops'] / m['us'] / 1e6:.1f} TFLOP/s  weights {m['bytes'] / m['us'] / 1e3:.0f} GB/s")
 
@@ -208,7 +245,8 @@ def main(argv=None) -> int:
     g.add_argument("--tokens", type=int, default=8)
     g.add_argument("--out", type=int, default=6144)
     g.add_argument("--inner", type=int, default=2048)
-    g.add_argument("--epilogue", default="store", choices=["store", "accumulate", "swiglu"])
+    g.add_argument("--epilogue", default="store", choices=["store", "accumulate", "swiglu", "rope"],
+                   help="rope: the fused q/k/v projection with rotation, norm and cache append (--heads, --kv-heads; --out is not used)")
     g.add_argument("--float-out", action="store_true")
     g.add_argument("--copies", type=int, default=8)
     d = sub.add_parser("attention-decode")
