@@ -437,6 +437,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (c_begin + q < c_end) old_first[q] = to_float(C[(size_t)(b_row0 + c_begin + q) * p.ldc + a_row0 + row]);
             }
         }
+        // (the gain of the norm that this product's output feeds, for this thread's feature: asked for now as well)
+        const float gain_ahead = (EPI == EPI_ACCUMULATE && p.norm.out && a_row0 + row < p.N) ? norm_gain_at(p.norm, a_row0 + row) : 0.f;
         // The rotation epilogue: where each of this CTA's tokens stands and where its k or v row lies in the cache is
         // a chain of three loads (position, slot, block).  It is walked now, under the MMAs, one thread a token.
         float rope_inv_freq = 0.f, rope_gain = 1.f;
@@ -638,7 +640,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else if (EPI == EPI_ACCUMULATE && p.norm.out) {
                         // the residual's new values, and for the norm that follows: bf16(value * gain) and the sums of squares
                         // of these tokens over the tile's 128 features
-                        const float gn = n < p.N ? norm_gain_at(p.norm, n) : 0.f;
+                        const float gn = gain_ahead;
 #pragma unroll
                         for (int q = 0; q < FOLD_COLS; q++) {
                             float v = 0.f;
