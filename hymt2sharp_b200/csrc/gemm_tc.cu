@@ -271,6 +271,10 @@ __device__ __forceinline__ void rope_head_from_tmem(uint32_t head_at, int t, int
 // carry a copy for each
 __device__ __noinline__ void sincos_once(float angle, float* sn, float* cs) { sincosf(angle, sn, cs); }
 
+// --------------------------------------------------------------------------------------------
+// The kernel for up to 128 tokens (swapped orientation): one CTA computes the tile of 128 output features x BN token
+// columns over its cut of K, and the cuts of a tile fold as a cluster or through the workspace (see the top of the file).
+// --------------------------------------------------------------------------------------------
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(tile_threads(BN, EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmTcParams p) {
