@@ -5,14 +5,15 @@ from __future__ import annotations
 
 import torch
 
+from . import ops
+
 
 def try_matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int, row_scale: tuple | None = None) -> bool:
     """bfloat16 operands with 16-byte aligned rows go to the tcgen05 kernel; anything else is refused.  `row_scale`: see
     ops.gemm_tc (the activations are a norm's input times its gain; the row scale is applied to the sums)."""
-    from . import ops
     if not ops.gemm_tc_supported(out, x, w, epilogue):
         return False
-    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device), row_scale=row_scale)
+    ops.gemm_tc(out, x, w, epilogue, ops.device_status(out.device), row_scale=row_scale, checked=True)
     return True
 
 
@@ -20,7 +21,6 @@ def try_matmul_then_norm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, ga
     """out += x @ w^T on the tcgen05 kernel, which also leaves behind what the RMSNorm after it needs: returns
     (bf16(out_new * gain) [T, N], partial sums of squares [T, tiles]); or None (nothing ran) where the kernel or this
     shape's plan cannot do that."""
-    from . import ops
     T, N = out.shape
     if gain.dtype not in (torch.bfloat16, torch.float32) or out.dtype != torch.float32 or not out.is_contiguous() or N % 8:
         return None
@@ -31,7 +31,7 @@ def try_matmul_then_norm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, ga
         return None
     normed = torch.empty((T, N), dtype=torch.bfloat16, device=out.device)
     ss = torch.empty((T, tiles), dtype=torch.float32, device=out.device)
-    ops.gemm_tc(out, x, w, ops.EPILOGUE_ACCUMULATE, ops.device_status(out.device), norm_after=(normed, gain, ss))
+    ops.gemm_tc(out, x, w, ops.EPILOGUE_ACCUMULATE, ops.device_status(out.device), norm_after=(normed, gain, ss), checked=True)
     return normed, ss
 
 
@@ -40,7 +40,6 @@ def try_project_rope_kv(x, weight, epilogue, ctx, planes, cache_dtype, block_tab
     """The fused q/k/v projection whose epilogue rotates, norms and appends to the cache (tcgen05, heads of 128,
     rotate-half pairs): returns q [T, nh * d], or None when that kernel does not take the operands and the caller
     goes the two-kernel way.  `planes` = (k_plane, v_plane), or (None, None) for a run that writes no keys."""
-    from . import ops
     if epilogue.pairing != "half" or x.dtype != torch.bfloat16:
         return None
     if not ops.gemm_tc_rope_kv_supported(x, weight, nh, nkv, d, cache_dtype, epilogue.rope_dim):
@@ -58,7 +57,7 @@ def try_project_rope_kv(x, weight, epilogue, ctx, planes, cache_dtype, block_tab
     try:
         ops.gemm_tc_rope_kv(x, weight, q, planes[0], planes[1], block_table, ctx.cache.block_tokens, ctx.token_seq,
                             ctx.token_pos, ctx.slot_ids, epilogue.inv_freq, epilogue.rope_dim, q_gain, k_gain, eps, nh, nkv,
-                            ops.device_status(x.device), angles=angles, row_scale=row_scale)
+                            ops.device_status(x.device), angles=angles, row_scale=row_scale, checked=True)
     finally:
         ops.tag = None
     return q
@@ -73,7 +72,6 @@ DECODE_TC_MAX_CHUNKS = 2048  # chunks of one sequence that it takes
 def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale, window) -> bool:
     """bfloat16 with head_dim 64 or 128: decode steps go to the streaming decode kernel, steps with
     longer pieces to the tcgen05 flash-attention kernel (cache blocks of 64 tokens)."""
-    from . import ops
     bt = k_plane.shape[2]
     if out.dtype != torch.bfloat16 or d not in (64, 128) or bt & (bt - 1):
         return False

@@ -27,12 +27,19 @@ def dtype_code(t: torch.dtype) -> int:
     raise KernelError(f"dtype {t} is not supported by the kernels (float32 and bfloat16 are)")
 
 
+_library = None
+
+
 def _lib():
-    return load_library()
+    global _library
+    if _library is None:
+        _library = load_library()
+    return _library
 
 
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # (the raw handle: torch.cuda.current_stream() builds a Stream object for it, ten times the cost, once per launch)
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _ptr(t: torch.Tensor | None) -> c_void_p:
@@ -274,6 +281,7 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int
 
 
 _status: dict = {}
+_status_of: dict = {}   # the same by what callers pass (a torch.device with an index)
 
 
 def device_status(device) -> torch.Tensor:
@@ -281,10 +289,15 @@ def device_status(device) -> torch.Tensor:
     bounded wait gives up (1: token id outside the table; 2: a sequence longer than the split attention was given
     room for; 101-105: a wait of the tensor-core GEMM; 108-119: of the prompt attention; 120-129: of the decode
     attention)."""
-    device = torch.device(device)
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    hit = _status_of.get(device)
+    if hit is not None:
+        return hit
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _status:
-        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=dev)
+    if dev.index is not None:          # ("cuda" without an index means the current device, which may change)
+        _status_of[device] = _status[key]
     return _status[key]
 
 
@@ -325,30 +338,52 @@ def gemm_tc_supported(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilo
 def gemm_tc_norm_tiles(tokens: int, out_features: int, inner: int, epilogue: int) -> int:
     """How many partial sums of squares per token gemm_tc leaves behind when it is asked to prepare the norm that follows it
     (`norm_after`); 0: this shape's plan cannot, and the norm runs as a kernel of its own."""
-    return int(_lib().hymt2_gemm_tc_norm_tiles(c_int(tokens), c_int(out_features), c_int(inner), c_int(epilogue)))
+    key = (tokens, out_features, inner, epilogue)
+    hit = _norm_tiles.get(key)
+    if hit is None:
+        hit = _norm_tiles[key] = int(_lib().hymt2_gemm_tc_norm_tiles(c_int(tokens), c_int(out_features), c_int(inner), c_int(epilogue)))
+    return hit
+
+
+# What the library answered about a shape (its plan depends on the sizes and the device's SMs only): asked once a shape,
+# since a step asks the same questions layer after layer.
+_norm_tiles: dict = {}
+_plans: dict = {}
+_rope_plans: dict = {}
+
+
+def _plan_scratch(T: int, N: int, K: int, epilogue: int) -> tuple:
+    """(floats of workspace, counters) that the tensor-core product of this shape wants."""
+    key = (T, N, K, epilogue)
+    hit = _plans.get(key)
+    if hit is None:
+        floats, counters = ctypes.c_long(0), c_int(0)
+        _check(_lib().hymt2_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(epilogue), ctypes.byref(floats),
+                                         ctypes.byref(counters)), "gemm_tc_plan", 0)
+        hit = _plans[key] = (floats.value, counters.value)
+    return hit
 
 
 def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, status: torch.Tensor,
-            row_scale: tuple | None = None, norm_after: tuple | None = None) -> None:
+            row_scale: tuple | None = None, norm_after: tuple | None = None, checked: bool = False) -> None:
     """out[T, N] = epilogue(a[T, K] @ w[N, K]^T) on the tcgen05 tensor cores (bfloat16 operands,
     float32 accumulation in tensor memory).  With EPILOGUE_SWIGLU w has 2N rows.
 
     An RMSNorm can be folded into the products around it.  `row_scale` = (ss [T, tiles] float32, width, eps): `a` holds
     bf16(x * gain) and the sums are multiplied by 1 / sqrt(sum(ss[t]) / width + eps) (store and SwiGLU epilogues).
     `norm_after` = (normed [T, N] bfloat16, gain [N], ss [T, gemm_tc_norm_tiles(...)] float32), accumulate epilogue only:
-    bf16(out_new * gain) and the partial sums of squares of the new rows are written for the product that comes next."""
+    bf16(out_new * gain) and the partial sums of squares of the new rows are written for the product that comes next.
+    `checked`: the caller has just asked gemm_tc_supported about these very operands."""
     T, N = out.shape
     K = a.shape[1]
     rows_w = 2 * N if epilogue == EPILOGUE_SWIGLU else N
-    if a.shape[0] != T or w.shape != (rows_w, K) or not gemm_tc_supported(out, a, w, epilogue):
+    if a.shape[0] != T or w.shape != (rows_w, K) or not (checked or gemm_tc_supported(out, a, w, epilogue)):
         raise KernelError(f"gemm_tc: operands out {tuple(out.shape)} {out.dtype} a {tuple(a.shape)} {a.dtype} "
                           f"w {tuple(w.shape)} {w.dtype} epilogue {epilogue} are not taken")
-    floats, counters = ctypes.c_long(0), c_int(0)
-    _check(_lib().hymt2_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(epilogue), ctypes.byref(floats),
-                                     ctypes.byref(counters)), "gemm_tc_plan", 0)
+    floats, counters = _plan_scratch(T, N, K, epilogue)
     ws = cnt = None
-    if floats.value:
-        ws, cnt = _tc_workspace(out.device, floats.value, counters.value)
+    if floats:
+        ws, cnt = _tc_workspace(out.device, floats, counters)
     ss_in = normed = gain = ss_out = None
     tiles_in, width, eps = 0, 0, 0.0
     if row_scale is not None:
@@ -396,20 +431,25 @@ def gemm_tc_rope_kv_supported(x: torch.Tensor, w: torch.Tensor, nh: int, nkv: in
     K = x.shape[1]
     if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         return False
-    return bool(_lib().hymt2_gemm_tc_rope_kv_supported(c_int(x.shape[0]), c_int(w.shape[0]), c_int(K), c_int(rope_dim)))
+    key = (x.shape[0], w.shape[0], K, rope_dim)
+    hit = _rope_plans.get(key)
+    if hit is None:
+        hit = _rope_plans[key] = bool(_lib().hymt2_gemm_tc_rope_kv_supported(c_int(key[0]), c_int(key[1]), c_int(K), c_int(rope_dim)))
+    return hit
 
 
 def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None,
                     v_plane: torch.Tensor | None, block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor,
                     token_pos: torch.Tensor, slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int,
                     q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float, nh: int, nkv: int,
-                    status: torch.Tensor, angles: torch.Tensor | None = None, row_scale: tuple | None = None) -> None:
+                    status: torch.Tensor, angles: torch.Tensor | None = None, row_scale: tuple | None = None,
+                    checked: bool = False) -> None:
     """q_out[T, nh*128] = rotation and per-head norm of the query part of x @ w^T; the key part, rotated and
     normed, and the value part go to the rows of the cache planes that (slot, position) of every token name
     (k_plane None: nothing is written).  One tcgen05 kernel; head_dim 128; see rope_kv for the arguments.
     `angles`: what rope_angles(token_pos, inv_freq) gave, where gemm_tc_rope_kv_wants_angles says so.
     `row_scale` = (ss [T, tiles] float32, width, eps): x holds bf16(h * gain) of an RMSNorm whose row scale is applied to the
-    projection's sums here (see gemm_tc)."""
+    projection's sums here (see gemm_tc).  `checked`: the caller has just asked gemm_tc_rope_kv_supported about these operands."""
     d = 128
     T = x.shape[0]
     if gemm_tc_rope_kv_wants_angles(T, rope_dim):
@@ -420,7 +460,7 @@ def gemm_tc_rope_kv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pla
             raise KernelError(f"gemm_tc_rope_kv: angles is {tuple(angles.shape)}, expected {(T, rope_dim // 2, 2)}")
     else:
         angles = None
-    if not gemm_tc_rope_kv_supported(x, w, nh, nkv, d, (k_plane if k_plane is not None else q_out).dtype, rope_dim):
+    if not (checked or gemm_tc_rope_kv_supported(x, w, nh, nkv, d, (k_plane if k_plane is not None else q_out).dtype, rope_dim)):
         raise KernelError(f"gemm_tc_rope_kv: operands x {tuple(x.shape)} {x.dtype} w {tuple(w.shape)} {w.dtype} are not taken")
     _need(q_out, "q_out", torch.bfloat16, 2)
     if q_out.shape != (T, nh * d) or not q_out.is_contiguous():
@@ -481,7 +521,11 @@ def protocol_numbers() -> dict:
 def gemm_tc_rope_kv_wants_angles(tokens: int, rope_dim: int) -> bool:
     """Whether gemm_tc_rope_kv of this many tokens wants the table of their angles: where tokens are the
     accumulator's rows, a thread owns a whole token and would compute every angle once per head."""
-    return bool(_lib().hymt2_gemm_tc_rope_kv_wants_angles(c_int(tokens), c_int(rope_dim)))
+    key = ("angles", tokens, rope_dim)
+    hit = _rope_plans.get(key)
+    if hit is None:
+        hit = _rope_plans[key] = bool(_lib().hymt2_gemm_tc_rope_kv_wants_angles(c_int(tokens), c_int(rope_dim)))
+    return hit
 
 
 def rope_angles(token_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:

@@ -3,7 +3,8 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import fast, ops
+from .base import Prenormed
 
 
 def compute_form(t: torch.Tensor, device, dtype: torch.dtype) -> torch.Tensor:
@@ -35,13 +36,11 @@ class Linear:
     def __call__(self, x, out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, ctx=None):
         """x: the activations, or a Prenormed (a norm's output in two pieces; `ctx` is then needed for the case that the
         kernel at hand cannot apply the row scale and the norm has to run after all)."""
-        from .base import Prenormed
         if out is None:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
         ops.tag = self.role
         try:
             if isinstance(x, Prenormed):
-                from ..kernels import fast
                 if self.epilogue != ops.EPILOGUE_ACCUMULATE and fast.try_matmul(out, x.normed, self.weight, self.epilogue, x.row_scale()):
                     return out
                 x = x.materialize(ctx)
@@ -53,10 +52,8 @@ class Linear:
     def add_then_norm(self, x: torch.Tensor, residual: torch.Tensor, norm, ctx) -> None:
         """residual += x @ W^T.  `norm` (or None) is the norm that will be applied to the residual rows next: where the
         kernel can, it also leaves that norm's input behind (ctx.prenormed), and the norm will not run."""
-        from .base import Prenormed
         if fold_norms and ctx is not None and norm is not None and getattr(norm, "foldable", False) and getattr(norm, "gain", None) is not None \
                 and norm.dim == residual.shape[1] and residual.shape[0] == x.shape[0]:
-            from ..kernels import fast
             ops.tag = self.role
             try:
                 left = fast.try_matmul_then_norm(residual, x, self.weight, norm.gain)
@@ -72,7 +69,6 @@ class Linear:
 
 def matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int) -> None:
     """Picks the kernel: tensor-core kernels where they take the shape and types, else CUDA cores."""
-    from ..kernels import fast
     if fast.try_matmul(out, x, w, epilogue):
         return
     ops.gemm_simt(out, x, w, epilogue)
