@@ -507,6 +507,10 @@ HYMT2_API int hymt2_attention_decode_tc(void* out, const void* q, const void* k_
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
+    // Not quite every SM: behind the q/k/v projection (clusters of CTAs, placed whole inside GPCs) the CTAs numbered past
+    // the last multiple of 8 were placed 5 to 8 us after the others, on SMs that had been idle all along (B200, 148 SMs,
+    // stamps of the device clock at each CTA's entry), and the rows they held chunks of were folded that much later.
+    if (sms >= 16) sms -= sms % 8;
     const long ctas = total < sms ? total : sms;
     cudaError_t e = launch_pdl(kernel, dim3((unsigned)ctas), dim3(NUM_THREADS), smem, stream, mq, mk, mv, p);
     if (e != cudaSuccess) { hymt2_set_error("attention_decode_tc: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
