@@ -108,6 +108,7 @@ struct GemmTcParams {
     uint32_t wait_limit;     // tries of a bounded wait in the one-tile kernel (WAIT_LIMIT, less in the debug entry)
     int withhold_block;      // -1; the debug entry names a k block whose copies the producer does NOT issue
     NormSide norm;
+    int together = 0;        // splits through the workspace: every CTA of a tile folds a share of its columns (all of them are resident)
 };
 
 // The copies of one stage (activations, weights, and for a split weight tile its second half) with, in front of them, a
@@ -693,6 +694,78 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            bool together = false;
+            if constexpr (BN >= 64) together = p.together != 0;   // (compiled for wide tiles only: the narrow ones keep their registers, and with them their place beside other kernels' CTAs)
+            if (together) {
+              if constexpr (BN >= 64) {
+                // Every CTA of the tile is on an SM at this time (the launch has no more CTAs than there are SMs).  Each
+                // waits, with a limit, until all the partials are in memory, then adds them up for its share of the token
+                // columns, in split order, and writes those: a third of the work each instead of all of it for the CTA
+                // that happened to come last, whose fold stood between this kernel and the next (20 us at 64 tokens).
+                if (warp == 2 && lane == 0) {
+                    atomicAdd(&p.counters[tile], 1);
+                    int seen = 0;
+                    for (uint32_t tries = 0; tries < p.wait_limit; tries++) {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
+                        if (seen >= p.splits || *abort_flag) break;
+                        __nanosleep(32);
+                    }
+                    if (seen < p.splits) { *abort_flag = 1; atomicExch(p.status, 106); }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!*abort_flag) {
+                    __threadfence();
+                    constexpr int FC = 8, SG = 4;              // columns and splits whose loads are in flight together
+                    const int n = a_row0 + row;
+                    const int cols = min(BN, p.T - b_row0);
+                    const int share = (cols + p.splits - 1) / p.splits;
+                    const int mine_begin = (int)blockIdx.z * share, mine_end = min(cols, mine_begin + share);
+                    for (int c0 = mine_begin; c0 < mine_end; c0 += FC) {
+                        float g[FC], u[FC], old[FC];
+#pragma unroll
+                        for (int q = 0; q < FC; q++) {
+                            g[q] = 0.f; u[q] = 0.f;
+                            old[q] = (EPI == EPI_ACCUMULATE && c0 + q < mine_end && n < p.N) ? to_float(C[(size_t)(b_row0 + c0 + q) * p.ldc + n]) : 0.f;
+                        }
+                        for (int s0 = 0; s0 < p.splits; s0 += SG) {   // split order: the sum is the same every time
+                            float pg[SG][FC], pu[SG][FC];
+#pragma unroll
+                            for (int k = 0; k < SG; k++) {
+                                const bool in_s = s0 + k < p.splits;
+                                const float* part = ws_tile + (size_t)(in_s ? s0 + k : 0) * (ACC_COLS * TILE_M);
+#pragma unroll
+                                for (int q = 0; q < FC; q++) {
+                                    const bool in = in_s && c0 + q < mine_end;
+                                    pg[k][q] = in ? __ldcg(part + (size_t)(c0 + q) * TILE_M + row) : 0.f;
+                                    pu[k][q] = (in && EPI == EPI_SWIGLU) ? __ldcg(part + (size_t)(BN + c0 + q) * TILE_M + row) : 0.f;
+                                }
+                            }
+#pragma unroll
+                            for (int k = 0; k < SG; k++)
+#pragma unroll
+                                for (int q = 0; q < FC; q++) { g[q] += pg[k][q]; u[q] += pu[k][q]; }
+                        }
+                        if (n < p.N) {
+#pragma unroll
+                            for (int q = 0; q < FC; q++) {
+                                if (c0 + q >= mine_end) continue;
+                                TC* dst = C + (size_t)(b_row0 + c0 + q) * p.ldc + n;
+                                const float r = scaled ? scale_s[c0 + q] : 1.0f;
+                                if (EPI == EPI_STORE) *dst = from_float<TC>(g[q] * r);
+                                else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[q] + g[q]);
+                                else *dst = from_float<TC>(silu_mul(g[q] * r, u[q] * r));
+                            }
+                        }
+                    }
+                }
+                // the CTA that leaves last puts the counter back to zero for the next launch
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0 && !*abort_flag) {
+                    const int left = atomicAdd(&p.counters[tile], 1);
+                    if (left == 2 * p.splits - 1) p.counters[tile] = 0;
+                }
+              }
+            } else {
             if (warp == 2 && lane == 0) {
                 const int arrived = atomicAdd(&p.counters[tile], 1);
                 last_s = arrived == p.splits - 1;
@@ -728,6 +801,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     emit(c, g, u);
                 }
+            }
             }
         }
     }
@@ -1245,6 +1319,9 @@ int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N
     if (norm.ss_in) HYMT2_REQUIRE(epilogue != EPI_ACCUMULATE && norm.ss_in_tiles > 0 && norm.ss_width > 0, "gemm_tc: bad row-scale arguments");
     GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
                    RopeEpilogue{}, wait_limit, withhold_block, norm};
+    // (from 64 token columns on: below that the fold is short, and two thirds of the CTAs leaving early, so that the next
+    // kernel's CTAs find room, is worth more; batch 8: 1.63 against 1.82 ms a step, batch 64: 4.05 against 3.95)
+    p.together = (pl.swapped && pl.splits > 1 && !pl.cluster && pl.bn >= 64 && (long)pl.grid.x * pl.grid.y * pl.splits <= pl.sm_count) ? 1 : 0;
     if (withhold_block >= 0)
         HYMT2_REQUIRE(pl.swapped && pl.splits == 1, "gemm_tc_debug: only the one-tile kernel without a cut of K can withhold a block "
                       "(T=%d N=%d K=%d gives swapped=%d splits=%d)", T, N, K, (int)pl.swapped, pl.splits);

@@ -287,7 +287,7 @@ _status_of: dict = {}   # the same by what callers pass (a torch.device with an 
 def device_status(device) -> torch.Tensor:
     """The int32[4] status word of a device: kernels set [0] when a device-side check fails or a
     bounded wait gives up (1: token id outside the table; 2: a sequence longer than the split attention was given
-    room for; 101-105: a wait of the tensor-core GEMM; 108-119: of the prompt attention; 120-129: of the decode
+    room for; 101-106: a wait of the tensor-core GEMM (106: for the partial sums of a tile's other CTAs); 108-119: of the prompt attention; 120-129: of the decode
     attention)."""
     hit = _status_of.get(device)
     if hit is not None:
