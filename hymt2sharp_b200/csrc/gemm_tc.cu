@@ -184,6 +184,13 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float v;
@@ -304,7 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (EPI != EPI_ROPE_KV) pdl_launch_dependents();
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
-    __shared__ float scale_s[BN], norm_red_s[16];
+    __shared__ float scale_s[BN];
     __shared__ int rope_pos_s[EPI == EPI_ROPE_KV ? BN : 1];
     __shared__ long long rope_at_s[EPI == EPI_ROPE_KV ? BN : 1];
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;     // 1024-byte aligned stage ring
@@ -428,25 +435,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // The cluster's fold: this CTA's share of the token columns that exist in the tile.  Where the fold adds into C,
         // the old values of the first batch of columns are asked for now, under the MMAs.
         constexpr int MAX_RANKS = 8;                           // a portable cluster
-        constexpr int FOLD_COLS = BN <= 16 ? 2 : 4;            // columns whose partials are in flight together
+        // In the fold a warp owns a column (a token) and a lane four neighbouring rows (features): 16-byte loads from the
+        // ranks' shared memory, a column's 128 features inside one warp (sums of squares and rotation partners need
+        // no barrier), the four warps on four columns at a time, FOLD_COLS of each warp's columns in flight.
+        constexpr int FOLD_COLS = (EPI == EPI_SWIGLU || BN < 64) ? 1 : 2;   // (narrow tiles: a warp rarely has a second column, and the registers are worth more)
+        const int n4 = a_row0 + 4 * lane;                      // this lane's first feature in the fold
         int c_begin = 0, c_end = 0;
-        float old_first[FOLD_COLS] = {};
+        float4 old_first[FOLD_COLS];
+#pragma unroll
+        for (int q = 0; q < FOLD_COLS; q++) old_first[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const bool c_vec = (p.ldc & 3) == 0 && (((uintptr_t)C) & (4 * sizeof(TC) - 1)) == 0 && (a_row0 & 3) == 0 && n4 + 4 <= p.N;
         if (p.cluster && p.splits > 1) {
             const int cols = min(BN, p.T - b_row0);
             const int share = (cols + p.splits - 1) / p.splits;
             c_begin = (int)blockIdx.z * share;
             c_end = min(cols, c_begin + share);
-            if (EPI == EPI_ACCUMULATE && a_row0 + row < p.N) {
+            if constexpr (EPI == EPI_ACCUMULATE && sizeof(TC) == 4) {
 #pragma unroll
-                for (int q = 0; q < FOLD_COLS; q++)
-                    if (c_begin + q < c_end) old_first[q] = to_float(C[(size_t)(b_row0 + c_begin + q) * p.ldc + a_row0 + row]);
+                for (int q = 0; q < FOLD_COLS; q++) {
+                    const int c = c_begin + quarter + 4 * q;
+                    if (c < c_end && c_vec) old_first[q] = *reinterpret_cast<const float4*>(C + (size_t)(b_row0 + c) * p.ldc + n4);
+                }
             }
         }
-        // (the gain of the norm that this product's output feeds, for this thread's feature: asked for now as well)
-        const float gain_ahead = (EPI == EPI_ACCUMULATE && p.norm.out && a_row0 + row < p.N) ? norm_gain_at(p.norm, a_row0 + row) : 0.f;
+        // (the gains of the norm that this product's output feeds, for this lane's features: asked for now as well)
+        float gain_ahead[4] = {0.f, 0.f, 0.f, 0.f};
+        if (EPI == EPI_ACCUMULATE && p.norm.out) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) if (n4 + i < p.N) gain_ahead[i] = norm_gain_at(p.norm, n4 + i);
+        }
         // The rotation epilogue: where each of this CTA's tokens stands and where its k or v row lies in the cache is
         // a chain of three loads (position, slot, block).  It is walked now, under the MMAs, one thread a token.
-        float rope_inv_freq = 0.f, rope_gain = 1.f;
+        float rope_inv_freq[4] = {0.f, 0.f, 0.f, 0.f}, rope_gain[4] = {1.f, 1.f, 1.f, 1.f};
         if constexpr (EPI == EPI_ROPE_KV) {
             const RopeEpilogue& rp = p.rope;
             const int head = blockIdx.x, tl = threadIdx.x - 64;
@@ -464,9 +484,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 rope_at_s[tl] = at;
             }
             const int half = rp.rope_dim / 2;
-            if (row < rp.rope_dim && (is_q || is_k)) rope_inv_freq = rp.inv_freq[row < half ? row : row - half];
             const void* gain = is_q ? rp.q_gain : is_k ? rp.k_gain : nullptr;
-            if (gain) rope_gain = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[row]) : ((const float*)gain)[row];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int d = 4 * lane + i;
+                if (d < rp.rope_dim && (is_q || is_k)) rope_inv_freq[i] = rp.inv_freq[d < half ? d : d - half];
+                if (gain) rope_gain[i] = rp.gain_bf16 ? __bfloat162float(((const __nv_bfloat16*)gain)[d]) : ((const float*)gain)[d];
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
 
@@ -541,136 +565,136 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             __syncwarp();
             cluster_sync_all();
-            {
-                // FOLD_COLS columns at a time: their partials from every rank (and the residual values they are added
-                // to) are asked for together, so that a column costs one trip through distributed shared memory and
-                // one through global memory per batch, not per column
-                const int n = a_row0 + row;                        // output feature
-                for (int c0 = c_begin; c0 < c_end; c0 += FOLD_COLS) {
-                    float old[FOLD_COLS];
-                    if (EPI == EPI_ACCUMULATE) {
+            for (int c0 = c_begin + quarter; c0 < c_end; c0 += 4 * FOLD_COLS) {
+                // all loads first (they do not wait for each other): the residual's old values, then every rank's partials
+                float4 old[FOLD_COLS];
+                if constexpr (EPI == EPI_ACCUMULATE && sizeof(TC) == 4) {
 #pragma unroll
-                        for (int q = 0; q < FOLD_COLS; q++) {
-                            if (c0 == c_begin) old[q] = old_first[q];
-                            else old[q] = (c0 + q < c_end && n < p.N) ? to_float(C[(size_t)(b_row0 + c0 + q) * p.ldc + n]) : 0.f;
+                    for (int q = 0; q < FOLD_COLS; q++) {
+                        const int c = c0 + 4 * q;
+                        if (c0 == c_begin + quarter) old[q] = old_first[q];
+                        else old[q] = (c < c_end && c_vec) ? *reinterpret_cast<const float4*>(C + (size_t)(b_row0 + c) * p.ldc + n4)
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                float4 g[FOLD_COLS], u[FOLD_COLS];
+                {
+                    float4 pg[FOLD_COLS][MAX_RANKS], pu[FOLD_COLS][MAX_RANKS];
+#pragma unroll
+                    for (int q = 0; q < FOLD_COLS; q++)
+#pragma unroll
+                        for (int r = 0; r < MAX_RANKS; r++) {
+                            const int c = c0 + 4 * q;
+                            const bool in = r < p.splits && c < c_end;
+                            pg[q][r] = in ? ld_cluster_f32x4(tiles + (c * TILE_M + 4 * lane) * 4, r) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            pu[q][r] = (in && EPI == EPI_SWIGLU) ? ld_cluster_f32x4(tiles + ((BN + c) * TILE_M + 4 * lane) * 4, r)
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                    for (int q = 0; q < FOLD_COLS; q++) {
+                        g[q] = make_float4(0.f, 0.f, 0.f, 0.f); u[q] = g[q];
+#pragma unroll
+                        for (int r = 0; r < MAX_RANKS; r++) {   // rank order
+                            g[q].x += pg[q][r].x; g[q].y += pg[q][r].y; g[q].z += pg[q][r].z; g[q].w += pg[q][r].w;
+                            u[q].x += pu[q][r].x; u[q].y += pu[q][r].y; u[q].z += pu[q][r].z; u[q].w += pu[q][r].w;
                         }
                     }
-                    float g[FOLD_COLS], u[FOLD_COLS];
-                    {
-                        float pg[FOLD_COLS][MAX_RANKS], pu[FOLD_COLS][MAX_RANKS];
+                }
 #pragma unroll
-                        for (int q = 0; q < FOLD_COLS; q++)
-#pragma unroll
-                            for (int r = 0; r < MAX_RANKS; r++) {      // all loads first: they do not wait for each other
-                                const bool in = r < p.splits && c0 + q < c_end;
-                                pg[q][r] = in ? ld_cluster_f32(tiles + ((c0 + q) * TILE_M + row) * 4, r) : 0.f;
-                                pu[q][r] = (in && EPI == EPI_SWIGLU) ? ld_cluster_f32(tiles + ((BN + c0 + q) * TILE_M + row) * 4, r) : 0.f;
-                            }
-#pragma unroll
-                        for (int q = 0; q < FOLD_COLS; q++) {
-                            g[q] = 0.f; u[q] = 0.f;
-#pragma unroll
-                            for (int r = 0; r < MAX_RANKS; r++) { g[q] += pg[q][r]; u[q] += pu[q][r]; }   // rank order
-                            if (scaled && c0 + q < c_end) { g[q] *= scale_s[c0 + q]; u[q] *= scale_s[c0 + q]; }
-                        }
-                    }
+                for (int q = 0; q < FOLD_COLS; q++) {
+                    const int c = c0 + 4 * q;                      // warp-uniform
+                    if (c >= c_end) continue;
+                    const int t = b_row0 + c;                      // the token
+                    const float r = scaled ? scale_s[c] : 1.0f;
+                    float gv[4] = {g[q].x * r, g[q].y * r, g[q].z * r, g[q].w * r};
                     if constexpr (EPI == EPI_ROPE_KV) {
-                        // this tile is head blockIdx.x of the tokens b_row0 + c, this thread its value d = row
+                        // this tile is head blockIdx.x of token t; this lane holds its values d = 4 lane .. 4 lane + 3
                         const RopeEpilogue& rp = p.rope;
-                        const int head = blockIdx.x, d = row;
+                        const int head = blockIdx.x;
                         const bool is_q = head < rp.nh, is_k = !is_q && head < rp.nh + rp.nkv;
-                        const uint32_t ex = tiles + ACC_COLS * TILE_M * 4;   // per column: 128 values to trade partners, then 4 sums
-                        constexpr uint32_t EX_BYTES = (TILE_M + 4) * 4;
-                        float x[FOLD_COLS], y[FOLD_COLS];
-                        int pos[FOLD_COLS];
-                        size_t cache_at[FOLD_COLS];
-                        bool write_kv[FOLD_COLS];
+                        const int pos = rope_pos_s[c - c_begin];
+                        const long long at = rope_at_s[c - c_begin];
+                        float x[4], y[4];
 #pragma unroll
-                        for (int q = 0; q < FOLD_COLS; q++) {
-                            const bool in = c0 + q < c_end;
-                            x[q] = __bfloat162float(__float2bfloat16_rn(g[q]));   // what the projection would have stored
-                            pos[q] = in ? rope_pos_s[c0 + q - c_begin] : 0;
-                            const long long at = in ? rope_at_s[c0 + q - c_begin] : -1;
-                            write_kv[q] = at >= 0;
-                            cache_at[q] = write_kv[q] ? (size_t)at + d : 0;
+                        for (int i = 0; i < 4; i++) x[i] = __bfloat162float(__float2bfloat16_rn(gv[i]));   // what the projection would have stored
+                        if (!is_q && !is_k) {   // a value head: as it is
+                            if (at >= 0) {
+                                __nv_bfloat162 h[2] = {__floats2bfloat162_rn(x[0], x[1]), __floats2bfloat162_rn(x[2], x[3])};
+                                *reinterpret_cast<uint2*>(rp.v_cache + at + 4 * lane) = *reinterpret_cast<const uint2*>(h);
+                            }
+                            continue;
                         }
-                        if (!is_q && !is_k) {   // a value head: as it is (the whole CTA is this head: no barrier is missed)
+                        // rotation partners d and d +- rope_dim / 2 trade through this warp's 128 words behind the partials
+                        const uint32_t ex = tiles + ACC_COLS * TILE_M * 4 + quarter * (TILE_M * 4);
+                        const int half = rp.rope_dim / 2;
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(ex + lane * 16), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+                        __syncwarp();
+                        float ss = 0.f;
 #pragma unroll
-                            for (int q = 0; q < FOLD_COLS; q++)
-                                if (write_kv[q]) rp.v_cache[cache_at[q]] = __float2bfloat16_rn(x[q]);
+                        for (int i = 0; i < 4; i++) {
+                            const int d = 4 * lane + i;
+                            y[i] = x[i];
+                            if (d < rp.rope_dim) {
+                                const bool low = d < half;
+                                float other, sn, cs;
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(ex + (low ? d + half : d - half) * 4) : "memory");
+                                sincos_once((float)pos * rope_inv_freq[i], &sn, &cs);
+                                y[i] = low ? x[i] * cs - other * sn : other * sn + x[i] * cs;
+                            }
+                            ss = fmaf(y[i], y[i], ss);
+                        }
+                        __syncwarp();                              // the warp's next column trades through the same words
+                        if ((is_q ? rp.q_gain : rp.k_gain) != nullptr) {
+                            const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)TILE_M + rp.eps);
+#pragma unroll
+                            for (int i = 0; i < 4; i++) y[i] = y[i] * scale * rope_gain[i];
+                        }
+                        __nv_bfloat162 h[2] = {__floats2bfloat162_rn(y[0], y[1]), __floats2bfloat162_rn(y[2], y[3])};
+                        if (is_q) *reinterpret_cast<uint2*>(rp.q_out + ((size_t)t * rp.nh + head) * TILE_M + 4 * lane) = *reinterpret_cast<const uint2*>(h);
+                        else if (at >= 0) *reinterpret_cast<uint2*>(rp.k_cache + at + 4 * lane) = *reinterpret_cast<const uint2*>(h);
+                    } else {
+                        const float uv[4] = {u[q].x * r, u[q].y * r, u[q].z * r, u[q].w * r};
+                        TC* dst = C + (size_t)t * p.ldc + n4;
+                        float o[4];
+                        if constexpr (EPI == EPI_ACCUMULATE) {
+                            if (c_vec) { o[0] = old[q].x + gv[0]; o[1] = old[q].y + gv[1]; o[2] = old[q].z + gv[2]; o[3] = old[q].w + gv[3]; }
+                            else {
+#pragma unroll
+                                for (int i = 0; i < 4; i++) o[i] = n4 + i < p.N ? to_float(dst[i]) + gv[i] : 0.f;
+                            }
                         } else {
 #pragma unroll
-                            for (int q = 0; q < FOLD_COLS; q++)
-                                asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + q * EX_BYTES + d * 4), "f"(x[q]) : "memory");
-                            asm volatile("bar.sync 1, 128;" ::: "memory");
-                            const int half = rp.rope_dim / 2;
-                            const void* gain = is_q ? rp.q_gain : rp.k_gain;
-#pragma unroll
-                            for (int q = 0; q < FOLD_COLS; q++) {
-                                y[q] = x[q];
-                                if (d < rp.rope_dim && c0 + q < c_end) {
-                                    const bool low = d < half;
-                                    float other, sn, cs;
-                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(ex + q * EX_BYTES + (low ? d + half : d - half) * 4) : "memory");
-                                    sincos_once((float)pos[q] * rope_inv_freq, &sn, &cs);
-                                    y[q] = low ? x[q] * cs - other * sn : other * sn + x[q] * cs;
-                                }
-                                if (gain) {
-                                    const float ss = warp_sum(y[q] * y[q]);
-                                    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(ex + q * EX_BYTES + (TILE_M + quarter) * 4), "f"(ss) : "memory");
-                                }
-                            }
-                            if (gain) {
-                                asm volatile("bar.sync 1, 128;" ::: "memory");
-                                const float gv = rope_gain;
-#pragma unroll
-                                for (int q = 0; q < FOLD_COLS; q++) {
-                                    float s0, s1, s2, s3;
-                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s0) : "r"(ex + q * EX_BYTES + (TILE_M + 0) * 4) : "memory");
-                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s1) : "r"(ex + q * EX_BYTES + (TILE_M + 1) * 4) : "memory");
-                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s2) : "r"(ex + q * EX_BYTES + (TILE_M + 2) * 4) : "memory");
-                                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(s3) : "r"(ex + q * EX_BYTES + (TILE_M + 3) * 4) : "memory");
-                                    const float scale = 1.0f / sqrtf((((s0 + s1) + s2) + s3) / (float)TILE_M + rp.eps);
-                                    y[q] = y[q] * scale * gv;
-                                }
-                            }
-#pragma unroll
-                            for (int q = 0; q < FOLD_COLS; q++) {
-                                if (c0 + q >= c_end) continue;
-                                if (is_q) rp.q_out[((size_t)(b_row0 + c0 + q) * rp.nh + head) * TILE_M + d] = __float2bfloat16_rn(y[q]);
-                                else if (write_kv[q]) rp.k_cache[cache_at[q]] = __float2bfloat16_rn(y[q]);
-                            }
-                            asm volatile("bar.sync 1, 128;" ::: "memory");   // the next batch trades through the same words
+                            for (int i = 0; i < 4; i++) o[i] = EPI == EPI_STORE ? gv[i] : silu_mul(gv[i], uv[i]);
                         }
-                    } else if (EPI == EPI_ACCUMULATE && p.norm.out) {
-                        // the residual's new values, and for the norm that follows: bf16(value * gain) and the sums of squares
-                        // of these tokens over the tile's 128 features
-                        const float gn = gain_ahead;
-#pragma unroll
-                        for (int q = 0; q < FOLD_COLS; q++) {
-                            float v = 0.f;
-                            if (n < p.N && c0 + q < c_end) {
-                                v = old[q] + g[q];
-                                C[(size_t)(b_row0 + c0 + q) * p.ldc + n] = from_float<TC>(v);
-                                p.norm.out[(size_t)(b_row0 + c0 + q) * p.N + n] = __float2bfloat16_rn(v * gn);
+                        if (c_vec) {
+                            if constexpr (sizeof(TC) == 4) *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                            else {
+                                __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+                                *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(h);
                             }
-                            const float sq = warp_sum(v * v);
-                            if (lane == 0) norm_red_s[q * 4 + quarter] = sq;
-                        }
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        const int tl = threadIdx.x - 64;
-                        if (tl < FOLD_COLS && c0 + tl < c_end)
-                            p.norm.ss_out[(size_t)(b_row0 + c0 + tl) * p.norm.ss_out_tiles + blockIdx.x] =
-                                (norm_red_s[tl * 4] + norm_red_s[tl * 4 + 1]) + (norm_red_s[tl * 4 + 2] + norm_red_s[tl * 4 + 3]);
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                    } else if (n < p.N) {
+                        } else {
 #pragma unroll
-                        for (int q = 0; q < FOLD_COLS; q++) {
-                            if (c0 + q >= c_end) continue;
-                            TC* dst = C + (size_t)(b_row0 + c0 + q) * p.ldc + n;
-                            if (EPI == EPI_STORE) *dst = from_float<TC>(g[q]);
-                            else if (EPI == EPI_ACCUMULATE) *dst = from_float<TC>(old[q] + g[q]);
-                            else *dst = from_float<TC>(silu_mul(g[q], u[q]));
+                            for (int i = 0; i < 4; i++) if (n4 + i < p.N) dst[i] = from_float<TC>(o[i]);
+                        }
+                        if (EPI == EPI_ACCUMULATE && p.norm.out) {
+                            // for the norm that follows: bf16(value * gain), and the token's sum of squares over the tile's
+                            // 128 features, which all lie in this warp
+                            float sq = 0.f;
+                            __nv_bfloat16 nb[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const float v = n4 + i < p.N ? o[i] : 0.f;
+                                sq = fmaf(v, v, sq);
+                                nb[i] = __float2bfloat16_rn(v * gain_ahead[i]);
+                            }
+                            __nv_bfloat16* nd = p.norm.out + (size_t)t * p.N + n4;
+                            if (n4 + 4 <= p.N && (p.N & 3) == 0) *reinterpret_cast<uint2*>(nd) = *reinterpret_cast<const uint2*>(nb);
+                            else {
+#pragma unroll
+                                for (int i = 0; i < 4; i++) if (n4 + i < p.N) nd[i] = nb[i];
+                            }
+                            sq = warp_sum(sq);
+                            if (lane == 0) p.norm.ss_out[(size_t)t * p.norm.ss_out_tiles + blockIdx.x] = sq;
                         }
                     }
                 }
