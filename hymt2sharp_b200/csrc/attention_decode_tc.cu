@@ -38,7 +38,8 @@ struct DecodeTcParams {
 constexpr int STAGES = 3;        // chunks whose keys and values are in shared memory or on their way
 constexpr int MAX_ITEMS = 64;    // chunks that one CTA holds in shared memory at a time (one round)
 constexpr int MAX_ROWS = 512;    // sequences in one launch
-constexpr int MAX_CHUNKS = 2048; // chunks of one sequence (262,144 positions)
+constexpr int MAX_CHUNKS = 2048; // chunks of one sequence (262,144 positions); an item keeps chunk numbers in 16 bits
+static_assert(MAX_CHUNKS <= 32767, "an item keeps chunk numbers in 16 bits");
 constexpr int FOLD_BATCH = 20;   // chunks whose partials are loaded together when a row is folded
 
 template <int G>   // query heads per kv head that the softmax loops cover (the group size rounded up)
@@ -84,7 +85,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // Only chunks that hold visible keys are items: warp 2 counts them row by row (a running sum in shared
     // memory), so w = blockIdx.x, + gridDim.x, ... below the total is always a real chunk and every CTA
     // gets the same number of them, give or take one.
-    struct Item { int b, kvh, split, kv_len, pos, lo, chunk_begin, blocks_here, first_block, row0, row1; };
+    struct Item { int b, kvh, kv_len, pos, lo, chunk_begin, blocks_here, first_block, row0, row1; short split, folder; };
     __shared__ Item items[MAX_ITEMS];
     __shared__ int row_first[MAX_ROWS + 1], row_slot[MAX_ROWS], row_len[MAX_ROWS];
     if (warp == 1) {
@@ -153,6 +154,17 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 const int chunks = it.pos / CHUNK + 1 - it.lo / CHUNK, rem = w - row_first[b];
                 it.kvh = rem / chunks;
                 it.split = it.lo / CHUNK + rem % chunks;
+                // Who folds the row: the holder of its last chunk, unless the rows' chunks fall on the same CTAs again and
+                // again (the number of chunks and of CTAs share a divisor: 18 chunks a row on 144 CTAs would leave all the
+                // folding to 8 CTAs, measured 57 against 34 us); then the holder of a chunk that differs from row to row.
+                // With more items than a CTA holds at once (rounds) it stays the last chunk: its holder never waits
+                // for a chunk of a later round.
+                {
+                    int gcd = (int)gridDim.x, rest = chunks;
+                    while (rest) { const int x = gcd % rest; gcd = rest; rest = x; }
+                    const bool one_round = total <= MAX_ITEMS * (int)gridDim.x;
+                    it.folder = (one_round && gcd > 2) ? it.lo / CHUNK + (b * p.nkv + it.kvh) % chunks : it.pos / CHUNK;
+                }
                 it.chunk_begin = it.split * CHUNK;
                 it.blocks_here = min(2, (it.pos - it.chunk_begin) / BLOCK_KEYS + 1);
                 // With a window, the chunk's first block may lie wholly below the oldest visible key; the cache has
@@ -379,9 +391,9 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             }
             // All partials of this warp are written.  One counter per (sequence, kv head, quarter of d) counts the
             // chunks whose partials are in memory; a warp raises the counters of all its items at once (lane l the
-            // l-th item of the group).  A row is folded, in chunk order, by the warps that computed the row's LAST
-            // chunk, each for its quarter of d (so the folding is spread evenly over the CTAs): the warp waits, with
-            // a limit, until its counter shows that all chunks are in.
+            // l-th item of the group).  A row is folded, in chunk order, by the warps that computed ONE of the row's
+            // chunks (which one: below), each for its quarter of d, so that the folding is spread over the CTAs: the
+            // warp waits, with a limit, until its counter shows that all chunks are in.
             __threadfence();
             __syncwarp();
             if (ok && grp + 2 * lane < n_items) {
@@ -390,8 +402,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             }
             for (int i = grp; ok && i < n_items; i += 2) {
                 const Item& it = items[i];
-                if (it.split != it.pos / CHUNK) continue;        // not the row's last chunk
                 const int s_begin = it.lo / CHUNK, n_chunks = it.pos / CHUNK + 1 - s_begin;
+                if (it.split != it.folder) continue;          // another CTA folds this row
                 int* counter = p.counters + ((size_t)it.b * p.nkv + it.kvh) * 4 + quarter;
                 int seen = 0;
                 if (lane == 0) {

@@ -697,6 +697,43 @@ def test_attention_decode_tcgen05_more_chunks_than_a_cta_holds():
     assert torch.allclose(far, vals[5][37, 1].float(), atol=0.05)
 
 
+def test_attention_decode_tcgen05_rows_whose_chunks_fall_on_the_same_ctas():
+    """Rows of 9 chunks each on a number of CTAs that 9 divides (or shares a divisor with): the chunk that folds a
+    row then differs from row to row instead of being the last.  A key in the first chunk and one in the last chunk
+    carry all the weight of their rows, so a fold that left a chunk out or took one twice shows."""
+    ops = _ops()
+    torch.manual_seed(21)
+    dtype, d, nh, nkv = torch.bfloat16, 128, 8, 2
+    rows = 16
+    lens = [1030 + 7 * i for i in range(rows)]
+    assert all(-(-L // 128) == 9 for L in lens)
+    keys = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    vals = [torch.randn(L, nkv, d, device=DEV).to(dtype) for L in lens]
+    qs = [torch.randn(1, nh, d, device=DEV).to(dtype) for _ in lens]
+    keys[4][5, 0] = (qs[4][0, 1].float() * 4).to(dtype)               # head 1 reads kv head 0
+    keys[11][lens[11] - 2, 1] = (qs[11][0, 6].float() * 4).to(dtype)  # head 6 reads kv head 1
+    kp, vp, table = _paged(keys, vals, 64, dtype, shuffle_seed=2)
+    q = torch.cat([x.reshape(1, nh * d) for x in qs])
+    slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    splits = 9
+    na, nm, nc = ops.attention_decode_tc_scratch(rows, nh, nkv, d, splits)
+    acc = torch.full((na,), float("nan"), device=DEV)
+    ml = torch.full((nm,), float("nan"), device=DEV)
+    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out = torch.full((rows, nh * d), 5.0, dtype=dtype, device=DEV)
+    for _ in range(3):
+        ops.attention_decode_tc(out, q, kp, vp, table, slots, kv, nh, nkv, d, scale, 0, splits, acc, ml, counters, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and int(counters.abs().sum()) == 0
+    ref = torch.cat([_ref_attention(qs[i].float(), keys[i].float(), vals[i].float(), 1, 0, scale) for i in range(rows)])
+    assert torch.allclose(out.double(), ref, **_tol(dtype))
+    assert torch.allclose(out[4].reshape(nh, d)[1].float(), vals[4][5, 0].float(), atol=0.05)
+    assert torch.allclose(out[11].reshape(nh, d)[6].float(), vals[11][lens[11] - 2, 1].float(), atol=0.05)
+
+
 @pytest.mark.parametrize("nh, nkv, window", [(16, 4, 0), (4, 4, 0), (32, 2, 0), (6, 2, 300), (10, 2, 70)])
 def test_attention_decode_tcgen05(nh, nkv, window):
     """The tensor-core decode kernel (keys on the 128-row side, head_dim 128) against the float64
