@@ -5,14 +5,16 @@ the dominant kernels alone with their own roofline fractions.  Prints ONE JSON l
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--config 1p8b|4b|7b|tinyA|tinyB] [--batch B] [--prefill N] [--decode N] [--dtype bf16|fp32] [--reps R]
-                    [--layers L] [--verify-split] [--profile] [--no-points] [--no-kernels] [--no-graph]
+                    [--layers L] [--settle S] [--verify-split] [--profile] [--no-points] [--no-kernels] [--no-graph]
 
 The default is the Hy-MT2 1.8B layer sizes in bfloat16: a batch of 8 sequences that each hold a 2,048-token
 prompt, a 2,048-token prefill, decode at batch 1 and 64.  `--config 4b` and `--config 7b` run the two larger
 families of sizes with their own workloads (16 prompts of 64 to 4,096 tokens and 256 decode steps; 64 prompts of
 16 to 2,048 tokens and 512 steps).  A "step" is one decode step of the whole batch.  `value` is timed on the device
 with CUDA events around K steps of the captured decode graph; `e2e` is the same batch through Engine.generate
-(host token ids in and out every step).  `--verify-split` adds, under `verify`, the comparison of logits between
+(host token ids in and out every step), the host's clock read at the call's token callback.  Both time K steps that
+come after `--settle` untimed steps (and the warm-up): the prompts of a batch run at the power cap, and for some tens
+of milliseconds after them the clocks are still low (the first steps take 2.05 ms instead of 1.62).  `--verify-split` adds, under `verify`, the comparison of logits between
 the ways of cutting the work, between the precisions and against the plain implementation of the tests
 (src/HyMT2Sharp.Benchmark/Program.cs:124-177); `--profile` adds per-kernel times of a prefill and of
 decode steps, kernel after kernel (:243-261).  The shape of the program follows src/HyMT2Sharp.Benchmark/Program.cs:179-241 (warm-up, timed
@@ -250,6 +252,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=None, help="timed decode steps (default: 64; the workload's own for 4b and 7b)")
     ap.add_argument("--decode", type=int, default=None, help="the same as --steps (src/HyMT2Sharp.Benchmark --bench-decode)")
     ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--settle", type=int, default=48,
+                    help="untimed decode steps between the prompts and the warm-up: the prompts of a batch run at the power cap and the "
+                         "clocks need some tens of ms to come back")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="1p8b", choices=sorted(CONFIGS))
     ap.add_argument("--batch", type=int, default=None)
@@ -272,6 +277,7 @@ def main() -> int:
     work = spec["workload"]
     warmup = max(3, args.warmup)
     steps = max(1, args.decode or args.steps or (64 if args.config == "1p8b" else work["steps"]))
+    settle = max(0, args.settle)
     batch = args.batch or work["batch"]
     layers = args.layers or spec["layers"]
     dtype = {"bf16": "bfloat16", "fp32": "float32"}[args.dtype]
@@ -303,7 +309,7 @@ def main() -> int:
 
     main_lengths = prompt_lengths(batch)
     point_batches = [] if (args.no_points or args.config != "1p8b") else [1, 64]
-    reserve = lambda lengths: sum(-(-(n + warmup + steps + 8) // 64) * 64 for n in lengths)
+    reserve = lambda lengths: sum(-(-(n + settle + warmup + steps + 8) // 64) * 64 for n in lengths)
     capacity = max([reserve(main_lengths), args.prefill + 64] + [reserve([lo] * b) for b in point_batches]) + 4096
     folder = make_model(args.config, layers)
     try:
@@ -350,8 +356,8 @@ def main() -> int:
         batch_prefill_ms = t0.elapsed_time(t1)
         sampler = BatchSampler([GREEDY] * n, engine.device)
         first = sampler.sample(torch.cat(firsts), None)
-        session = DecodeSession(engine, slots, sampler, first, max(lengths) + w + k + 2, use_graph=not args.no_graph)
-        for _ in range(w):
+        session = DecodeSession(engine, slots, sampler, first, max(lengths) + settle + w + k + 2, use_graph=not args.no_graph)
+        for _ in range(settle + w):
             session.step()
         torch.cuda.synchronize()
         clocks = ClockSampler()
@@ -367,7 +373,7 @@ def main() -> int:
         ms = t0.elapsed_time(t1)
         clk = clocks.stop() if sample_clocks else None
         launches = ops.launches - launches0
-        mean_tokens = sum(lengths) + n * (w + (k + 1) / 2.0)   # cached tokens that a timed step reads, on average
+        mean_tokens = sum(lengths) + n * (settle + w + (k + 1) / 2.0)   # cached tokens that a timed step reads, on average
         engine.check()
         engine.free_slots(slots)
         return ms, launches, mean_tokens, clk, batch_prefill_ms
@@ -399,12 +405,25 @@ def main() -> int:
     # warm-up of the entry point with the same batch shape: the decode graph of that shape is captured here,
     # as it is once in a serving process, not in the timed run
     engine.generate(prompts, max_new_tokens=4, max_batch=batch)
-    out = engine.generate(prompts, max_new_tokens=steps + 1, max_batch=batch)
-    e2e_tokens = out.stats.decode_tokens
-    e2e = {"value": e2e_tokens / max(out.stats.decode_ms, 1e-9) * 1000.0, "unit": "tokens/s",
+    # One call of the entry point for settle + K + 1 tokens a request.  The host's clock is read whenever a step's tokens
+    # have arrived on the host (the call's own token callback); the timed region is the last K steps of the call, each with
+    # its copies in both directions.  The steps before them are the same settling as in the device-timed run.
+    stamps, arrived = [], []
+
+    def on_tokens(pairs):
+        stamps.append(time.perf_counter())
+        arrived.append(len(pairs))
+
+    out = engine.generate(prompts, max_new_tokens=settle + steps + 1, max_batch=batch, on_tokens=on_tokens)
+    k_e2e = min(steps, len(stamps) - 1)
+    e2e_ms = (stamps[-1] - stamps[-1 - k_e2e]) * 1000.0
+    e2e_tokens = sum(arrived[-k_e2e:])
+    e2e = {"value": e2e_tokens / max(e2e_ms, 1e-9) * 1000.0, "unit": "tokens/s",
            # every step: which rows run (slot and row number of each, int32) from pinned memory; the sampled tokens back
            "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 4 * batch,
-           "decode_ms": out.stats.decode_ms, "prefill_ms": out.stats.prefill_ms}
+           "steps": k_e2e, "ms": e2e_ms, "settle_steps": len(stamps) - 1 - k_e2e,
+           "call": {"decode_tokens": out.stats.decode_tokens, "decode_ms": out.stats.decode_ms, "prefill_ms": out.stats.prefill_ms,
+                    "tokens_per_s": out.stats.decode_tokens / max(out.stats.decode_ms, 1e-9) * 1000.0}}
 
     profile = None
     if args.profile:
@@ -438,7 +457,7 @@ def main() -> int:
                    "layers_full": spec["layers"], "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
                    "vocab": cfg.vocab_size, "rope_alpha": cfg.rope_alpha, "qk_norm": cfg.use_qk_norm,
-                   "tied": cfg.tie_word_embeddings, "sampling": "greedy on the GPU",
+                   "tied": cfg.tie_word_embeddings, "sampling": "greedy on the GPU", "settle_steps": settle,
                    "l2": "inputs larger than L2: every step streams all weights (GBs) once" if step_bytes > 2 * 126e6 else
                          "model smaller than L2, nothing flushed: a tiny configuration times launches, not memory"},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
