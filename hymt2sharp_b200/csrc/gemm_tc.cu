@@ -70,7 +70,11 @@ struct RopeEpilogue {
 // norm commutes with the product that follows it: (r * (x * gain)) W^T = r * ((x * gain) W^T).  So a product that ADDS into the
 // residual (the only place where a residual row changes) can leave bf16(x * gain) and the row's sum of squares behind,
 // and the product after it multiplies its sums by r: no kernel of its own reads the row again.  The sums of squares are
-// partial, one per token and tile of output features of the producing launch; the consumer adds them in tile order.
+// partial, several per token; the consumer adds them in the order of the features.  The kernel for few tokens leaves one per
+// tile of 128 features.  The persistent kernel, whose tile width depends on the number of tokens of the step, leaves one per
+// 16 features, each summed in the order of the features: a prompt's rows then get the same sums bit for bit whatever else is
+// in the step (with one sum per tile the last bit depended on the tile width, and within two layers the roundings to
+// bfloat16 behind it had spread that bit to every logit: measured, 24 elements of one product differed, then all).
 struct NormSide {
     // producer (EPI_ACCUMULATE): null, or where bf16(C_new * gain) goes ([T, N] contiguous), with the gain and the partial sums
     __nv_bfloat16* out;
@@ -85,8 +89,20 @@ struct NormSide {
 };
 
 __device__ __forceinline__ float norm_row_scale(const NormSide& ns, int t) {
+    // always in the same order: the same partial sums give the same scale bit for bit
+    const float* row = ns.ss_in + (size_t)t * ns.ss_in_tiles;
     float ss = 0.f;
-    for (int m = 0; m < ns.ss_in_tiles; m++) ss += ns.ss_in[(size_t)t * ns.ss_in_tiles + m];
+    int m = 0;
+    if ((ns.ss_in_tiles & 3) == 0 && (((uintptr_t)ns.ss_in) & 15) == 0) {
+        // four running sums, one per place in a group of four, then (0 + 1) + (2 + 3): a fixed order with a quarter of the chain
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (; m < ns.ss_in_tiles; m += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + m);     // (written by the kernel in front: a plain load)
+            s4[0] += v.x; s4[1] += v.y; s4[2] += v.z; s4[3] += v.w;
+        }
+        ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+    }
+    for (; m < ns.ss_in_tiles; m++) ss += row[m];
     return 1.0f / sqrtf(ss / (float)ns.ss_width + ns.ss_eps);
 }
 __device__ __forceinline__ float norm_gain_at(const NormSide& ns, int n) {
@@ -974,7 +990,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         TC* C = (TC*)p.C;
         static_assert(EPILOGUE_GROUPS == 2, "a group serves the accumulator of its number");
         // The CTA's LAST tile has nothing behind it that would hide its epilogue, so both groups take it: its owner the
-        // lower half of its columns (`part` 0), the other group, once through with its own tiles, the upper half (part 1).
+        // lower half of its columns, the other group, once through with its own tiles, the upper half.
         // (The helper reads a barrier it has not followed.  When it gets there it has drained tile last - 1, whose
         // MMAs were issued after those of tile last - 2 were complete, so the barrier of the last tile's accumulator is in
         // the last tile's own phase or past it, never one behind: the parity cannot be taken for an older one.)
@@ -984,27 +1000,27 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         const bool can_share = split_at > 0 && split_at < OUT_COLS;
         for (int item = 0;; item++) {
             // this group's own tiles first, then (where the last tile is the other group's) the upper half of that one
-            int j, c_begin = 0, c_end = OUT_COLS, part = 0;
+            int j, c_begin = 0, c_end = OUT_COLS;
             bool own = true;
             if (group + EPILOGUE_GROUPS * item < my_tiles) {
                 j = group + EPILOGUE_GROUPS * item;
                 if (j == last && can_share) c_end = split_at;
             } else if (my_tiles > 0 && can_share && (last & 1) != group && group + EPILOGUE_GROUPS * (item - 1) < my_tiles && !*abort_flag) {
-                j = last; own = false; c_begin = split_at; part = 1;
+                j = last; own = false; c_begin = split_at;
             } else break;
             const int tile = blockIdx.x + j * gridDim.x;
             const int buf = j & 1;
             const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
             // (the threads of a warp leave the wait at different times; what follows reads tensor memory warp-wide, so the
             // warp comes together first, and gives up together)
+            const int m = a_row0 + row;
+            // a norm folded into this product (see NormSide): the row scale of this thread's token, added up from the row's
+            // partial sums while the tile's MMAs still run
+            const float row_scale = (EPI != EPI_ACCUMULATE && p.norm.ss_in && m < p.T) ? norm_row_scale(p.norm, m) : 1.0f;
             const bool landed = mbar_wait(acc_full0 + 8 * buf, (uint32_t)((j >> 1) & 1), abort_flag, p.status, 103);
             if (!__all_sync(0xffffffffu, landed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-            const int m = a_row0 + row;
-            // a norm folded into this product (see NormSide): the row scale of this thread's token, or its sum of squares
-            const float row_scale = (EPI != EPI_ACCUMULATE && p.norm.ss_in && m < p.T) ? norm_row_scale(p.norm, m) : 1.0f;
-            float ss_acc = 0.f;
             if constexpr (EPI == EPI_ROPE_KV) {
                 // the tile holds BN / 128 heads of 128 tokens: this thread's token, head after head
                 const int heads = p.rope.nh + 2 * p.rope.nkv;
@@ -1021,6 +1037,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 if (EPI == EPI_SWIGLU) tmem_load<16>(lane_addr + bn / 2 + c, u);
                 if (m >= p.T) continue;
                 const int n0 = b_row0 + c;
+                if (n0 >= p.N) continue;
+                float ss_acc = 0.f;     // of these 16 features: a tile starts at a multiple of 16, so the groups are the same for every tile width
                 TC* dst = C + (size_t)m * p.ldc + n0;
                 const bool vec = n0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0;
 #pragma unroll
@@ -1072,12 +1090,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                         }
                     }
                 }
-            }
-            // two partial sums a tile: the lower and the upper half of its columns (the upper one is 0 where one group had it all)
-            if (EPI == EPI_ACCUMULATE && p.norm.out && m < p.T) {
-                float* ss = p.norm.ss_out + (size_t)m * p.norm.ss_out_tiles + (tile / tiles_m) * 2;
-                ss[part] = ss_acc;
-                if (part == 0 && c_end == OUT_COLS) ss[1] = 0.f;
+                if (EPI == EPI_ACCUMULATE && p.norm.out) p.norm.ss_out[(size_t)m * p.norm.ss_out_tiles + (n0 >> 4)] = ss_acc;
             }
             if (!own) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1309,10 +1322,10 @@ HYMT2_API int hymt2_gemm_tc_describe(int T, int N, int K, int epilogue, int sm_c
 namespace {
 // How many partial sums of squares per token a product that adds into the residual leaves behind for the norm after it:
 // one per tile of output features (0: this plan cannot, and the norm runs as a kernel of its own).
-int norm_out_tiles(const Plan& pl, int epilogue) {
+int norm_out_tiles(const Plan& pl, int epilogue, int N) {
     if (epilogue != EPI_ACCUMULATE) return 0;
     if (pl.swapped) return (pl.splits > 1 && pl.cluster) ? (int)pl.grid.x : 0;   // the cluster's fold holds (token, tile) whole
-    return 2 * (int)pl.grid.y;   // the persistent kernel: two partial sums a tile (a thread owns a token's row of half a tile)
+    return (N + 15) / 16;   // the persistent kernel: one partial sum per 16 features, the same for every tile width
 }
 
 int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw, long ldc,
@@ -1340,9 +1353,9 @@ int run_gemm_tc(void* C, int c_dtype, const void* X, const void* W, int T, int N
     }
     HYMT2_REQUIRE(ok, "gemm_tc: cuTensorMapEncodeTiled refused the operands");
     if (norm.out) {
-        HYMT2_REQUIRE(c_dtype == HYMT2_F32 && norm_out_tiles(pl, epilogue) > 0 && norm.gain && norm.ss_out && N % 8 == 0 &&
+        HYMT2_REQUIRE(c_dtype == HYMT2_F32 && norm_out_tiles(pl, epilogue, N) > 0 && norm.gain && norm.ss_out && N % 8 == 0 &&
                       (uintptr_t)norm.out % 16 == 0, "gemm_tc: this product (T=%d N=%d K=%d epilogue %d) cannot leave a norm's input behind", T, N, K, epilogue);
-        norm.ss_out_tiles = norm_out_tiles(pl, epilogue);
+        norm.ss_out_tiles = norm_out_tiles(pl, epilogue, N);
     }
     if (norm.ss_in) HYMT2_REQUIRE(epilogue != EPI_ACCUMULATE && norm.ss_in_tiles > 0 && norm.ss_width > 0, "gemm_tc: bad row-scale arguments");
     GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.bn, pl.splits, pl.k_blocks_per_split, pl.cluster ? 1 : 0, workspace, counters, status,
@@ -1381,7 +1394,7 @@ HYMT2_API int hymt2_gemm_tc_norm_tiles(int T, int N, int K, int epilogue) {
     if (T <= 0 || N <= 0 || K <= 0 || N % 8) return 0;
     Plan pl;
     make_plan(T, N, K, epilogue, sm_count_of_current_device(), &pl);
-    return norm_out_tiles(pl, epilogue);
+    return norm_out_tiles(pl, epilogue, N);
 }
 
 HYMT2_API int hymt2_gemm_tc_norm(void* C, int c_dtype, const void* X, const void* W, int T, int N, int K, long lda, long ldw,

@@ -522,6 +522,41 @@ def test_gemm_tcgen05_with_a_norm_folded_in(T, H, K_in, F, gain_dtype):
     assert ops.gemm_tc_norm_tiles(8, 6144, 2048, ops.EPILOGUE_SWIGLU) == 0
 
 
+def test_gemm_tcgen05_sums_of_squares_do_not_depend_on_the_tile_width():
+    """The product that adds into the residual leaves the rows' sums of squares behind in pieces; 300 rows alone and the
+    same rows among 1,470 run with tiles of other widths.  The pieces are per 16 features, so the rows' pieces, their
+    sums in the consumer and with them the consumer's results are the same bit for bit."""
+    ops = _ops()
+    torch.manual_seed(0)
+    bf = torch.bfloat16
+    N = K = 2048
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    x = torch.randn(1470, K, device=DEV).to(bf)
+    w = (torch.randn(N, K, device=DEV) * 0.02).to(bf)
+    res0 = torch.randn(1470, N, device=DEV)
+    gain = (1 + 0.1 * torch.randn(N, device=DEV)).to(bf)
+    w2 = (torch.randn(2 * 1024, N, device=DEV) * 0.02).to(bf)
+    got = {}
+    widths = set()
+    for T in (300, 1470):
+        widths.add(ops.gemm_tc_describe(T, N, K, ops.EPILOGUE_ACCUMULATE)["tile_width"])
+        tiles = ops.gemm_tc_norm_tiles(T, N, K, ops.EPILOGUE_ACCUMULATE)
+        assert tiles == N // 16
+        res = res0[:T].clone()
+        normed = torch.empty(T, N, dtype=bf, device=DEV)
+        ss = torch.full((T, tiles), float("nan"), device=DEV)
+        ops.gemm_tc(res, x[:T].contiguous(), w, ops.EPILOGUE_ACCUMULATE, status, norm_after=(normed, gain, ss))
+        act = torch.empty(T, 1024, dtype=bf, device=DEV)
+        ops.gemm_tc(act, normed, w2, ops.EPILOGUE_SWIGLU, status, row_scale=(ss, N, 1e-5))
+        got[T] = (res[:300].clone(), normed[:300].clone(), ss[:300].clone(), act[:300].clone())
+    assert len(widths) == 2, widths          # the case is about two tile widths
+    for a, b in zip(got[300], got[1470]):
+        assert torch.equal(a, b)
+    assert torch.allclose(got[300][2].sum(1).double(), got[300][0].double().pow(2).sum(1), rtol=1e-5)
+    assert status.tolist() == [0, 0, 0, 0]
+
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_take():
     ops = _ops()
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
