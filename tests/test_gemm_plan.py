@@ -98,3 +98,20 @@ def test_the_width_of_a_persistent_tile_is_one_the_kernel_takes(describe, T, N, 
     # never more waves than the widest tile would need
     widest = -(-T // 128) * -(-N // (128 if epi == SWIGLU else 256))
     assert -(-plan["tiles"] // SMS) * plan["tile_width"] <= -(-widest // SMS) * 256 * 1.3
+
+
+def test_the_pieces_of_a_rows_sum_of_squares_do_not_follow_the_tile_width(describe):
+    """A product that adds into the residual leaves the rows' sums of squares behind in pieces for the norm after it.  For
+    prompts the pieces are per 16 features whatever tile width the step's tokens gave the plan (a piece per tile made the
+    last bit of a row's scale depend on what else was in the step); steps of few tokens leave one per tile of 128 weight
+    rows, and a product that does not add leaves none."""
+    from hymt2sharp_b200.kernels import ops
+    widths = set()
+    for T in (129, 300, 1470, 2048, 16384):
+        widths.add(describe(T, 2048, 6144, ADD)["tile_width"])
+        assert ops.gemm_tc_norm_tiles(T, 2048, 6144, ADD) == 2048 // 16
+        assert ops.gemm_tc_norm_tiles(T, 2056, 2048, ADD) == 129          # a last piece of 8 features
+    assert len(widths) >= 3, widths
+    for T in (1, 8, 64, 128):
+        assert ops.gemm_tc_norm_tiles(T, 2048, 6144, ADD) == 2048 // 128
+    assert ops.gemm_tc_norm_tiles(2048, 6144, 2048, SWIGLU) == 0
