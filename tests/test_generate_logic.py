@@ -144,3 +144,18 @@ def test_a_step_ahead_with_a_limit_of_two_and_an_immediate_stop():
     run_batch(ahead, state, GenerationStats())
     assert [(r.tokens, r.finish_reason) for r in state.results()] == [([1, 2], "length"), ([], "stop"), ([4], "stop")]
     assert ahead.calls == [("prefill", [0, 1, 2]), ("launch", [0, 2]), ("collect",)]   # one launch: both rows are at their limit
+
+
+def test_the_token_callback_comes_once_a_step_with_that_steps_tokens():
+    """The callback is called once after the prompts and once for every decode step, each time with the tokens that the
+    step gave to the rows still running, in both loops: the end-to-end figure of the benchmark reads the host's clock there
+    and counts the tokens of the last K calls."""
+    scripts = [[5, 6, 7, 8, 9, 10], [11, 12, 13, 14, 15, 16]]
+    for stepper in (ScriptedStepper(scripts), AheadStepper(scripts)):
+        state = BatchState(["a", "b"], [3, 9], max_new_tokens=6, stop_token_ids=[])
+        calls = []
+        run_batch(stepper, state, GenerationStats(), on_tokens=lambda pairs: calls.append(list(pairs)), clock=lambda: 0.0)
+        assert len(calls) == 6                                   # the prompts' first tokens, then five steps
+        assert all(len(c) == 2 for c in calls)
+        assert [t for c in calls for rid, t in c if rid == "a"] == scripts[0]
+        assert [t for c in calls for rid, t in c if rid == "b"] == scripts[1]
