@@ -1321,7 +1321,8 @@ HYMT2_API int hymt2_gemm_tc_describe(int T, int N, int K, int epilogue, int sm_c
 
 namespace {
 // How many partial sums of squares per token a product that adds into the residual leaves behind for the norm after it:
-// one per tile of output features (0: this plan cannot, and the norm runs as a kernel of its own).
+// one per tile of 128 output features in steps of few tokens, one per 16 features from the persistent kernel (0: this plan
+// cannot, and the norm runs as a kernel of its own).
 int norm_out_tiles(const Plan& pl, int epilogue, int N) {
     if (epilogue != EPI_ACCUMULATE) return 0;
     if (pl.swapped) return (pl.splits > 1 && pl.cluster) ? (int)pl.grid.x : 0;   // the cluster's fold holds (token, tile) whole
